@@ -1,0 +1,76 @@
+// Shared helpers of the mini_engine_b200 kernels (sm_100a only).
+//
+// Every exported function has C linkage, takes raw device pointers, sizes and the stream
+// to launch on, returns 0 on success and a non-zero code after storing a message that
+// me_last_error() returns.  No function allocates device memory.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <math.h>
+
+#define ME_API extern "C" __attribute__((visibility("default")))
+
+enum MeDtype { ME_F32 = 0, ME_BF16 = 1 };
+typedef __nv_bfloat16 bf16;
+
+void me_set_error(const char* fmt, ...);
+
+#define ME_REQUIRE(cond, ...)            \
+  do {                                   \
+    if (!(cond)) {                       \
+      me_set_error(__VA_ARGS__);         \
+      return 1;                          \
+    }                                    \
+  } while (0)
+
+#define ME_LAUNCH_CHECK(what)                                             \
+  do {                                                                    \
+    cudaError_t e_ = cudaGetLastError();                                  \
+    if (e_ != cudaSuccess) {                                              \
+      me_set_error("%s: launch failed: %s", what, cudaGetErrorString(e_)); \
+      return 2;                                                           \
+    }                                                                     \
+  } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  return x;
+}
+
+// Sum over a thread block in a fixed order (lanes by butterfly, then warps in index order),
+// so that the result does not depend on anything but the data and the block size.
+__device__ __forceinline__ float block_sum(float x, float* red /* >= 32 floats of shared memory */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  x = warp_sum(x);
+  __syncthreads();
+  if (lane == 0) red[warp] = x;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarps; ++w) total += red[w];
+  return total;
+}
+
+// Run `body` with T bound to the C type of a dtype code.
+#define ME_DISPATCH_DTYPE(code, T, ...)                                  \
+  do {                                                                   \
+    if ((code) == ME_F32) { typedef float T; __VA_ARGS__; }              \
+    else if ((code) == ME_BF16) { typedef bf16 T; __VA_ARGS__; }         \
+    else { me_set_error("unknown dtype code %d", (int)(code)); return 1; } \
+  } while (0)

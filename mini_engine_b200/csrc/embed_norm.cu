@@ -1,0 +1,94 @@
+// Embedding gather into the float32 residual stream; residual add + RMSNorm; SiLU-and-multiply.
+//
+// Reference formulas: layers/embed_head.py:11 (gather), layers/layernorm.py:11-23
+// (y = x * rsqrt(mean(x^2) + eps) in float32, then the weight; with a residual the sum
+// is normalised), layers/activation.py:4-7 (silu(gate) * up).
+#include "common.cuh"
+
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                             float* __restrict__ out, int H, int V, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < V;
+  if (!ok && threadIdx.x == 0) atomicOr(err, 1);
+  const TW* row = table + (int64_t)(ok ? id : 0) * H;
+  float* o = out + (int64_t)t * H;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) o[h] = ok ? to_f<TW>(row[h]) : 0.f;
+}
+
+ME_API int me_embed(const int* ids, const void* table, int table_dtype, float* out, int T, int H,
+                    int V, int* err, cudaStream_t stream) {
+  if (T == 0) return 0;
+  ME_REQUIRE(T > 0 && H > 0 && V > 0, "me_embed: bad sizes T=%d H=%d V=%d", T, H, V);
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  ME_DISPATCH_DTYPE(table_dtype, TW,
+                    embed_kernel<TW><<<T, threads, 0, stream>>>(ids, (const TW*)table, out, H, V, err));
+  ME_LAUNCH_CHECK("me_embed");
+  return 0;
+}
+
+// One block per output row.  Both passes read res (+ delta); the second writes.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ res, const TD* __restrict__ delta,
+                                   const float* __restrict__ w, float eps, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int H, int write_res) {
+  __shared__ float red[32];
+  const int r_out = blockIdx.x;
+  const int64_t r = rows ? rows[r_out] : r_out;
+  float* rr = res + r * H;
+  const TD* dd = delta ? delta + r * H : nullptr;
+  float ss = 0.f;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float v = rr[h];
+    if (dd) v += to_f<TD>(dd[h]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* oo = out + (int64_t)r_out * H;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float v = rr[h];
+    if (dd) v += to_f<TD>(dd[h]);
+    if (write_res) rr[h] = v;
+    oo[h] = from_f<TO>((v * inv) * w[h]);
+  }
+}
+
+ME_API int me_add_rmsnorm(float* res, const void* delta, int delta_dtype, const float* w, float eps,
+                          void* out, int out_dtype, const int* rows, int n_rows, int H,
+                          cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  ME_REQUIRE(n_rows > 0 && H > 0, "me_add_rmsnorm: bad sizes rows=%d H=%d", n_rows, H);
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : (H >= 128 ? 128 : 64));
+  const int write_res = rows == nullptr;     // gathered rows leave the residual as it is
+  ME_DISPATCH_DTYPE(delta_dtype, TD, ME_DISPATCH_DTYPE(out_dtype, TO,
+      (add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(
+          res, (const TD*)delta, w, eps, (TO*)out, rows, H, write_res))));
+  ME_LAUNCH_CHECK("me_add_rmsnorm");
+  return 0;
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int I) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t t = i / I;
+  const int c = (int)(i - t * I);
+  const float g = to_f<T>(x[t * 2 * I + c]);
+  const float u = to_f<T>(x[t * 2 * I + I + c]);
+  out[i] = from_f<T>(g / (1.0f + expf(-g)) * u);
+}
+
+ME_API int me_silu_mul(const void* x, void* out, int dtype, int T, int I, cudaStream_t stream) {
+  if (T == 0) return 0;
+  ME_REQUIRE(T > 0 && I > 0, "me_silu_mul: bad sizes T=%d I=%d", T, I);
+  const int64_t n = (int64_t)T * I;
+  const int threads = 256;
+  const int64_t blocks = (n + threads - 1) / threads;
+  ME_REQUIRE(blocks < 2147483647LL, "me_silu_mul: too many elements");
+  ME_DISPATCH_DTYPE(dtype, TT,
+                    silu_mul_kernel<TT><<<(unsigned)blocks, threads, 0, stream>>>((const TT*)x, (TT*)out, n, I));
+  ME_LAUNCH_CHECK("me_silu_mul");
+  return 0;
+}

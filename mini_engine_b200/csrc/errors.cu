@@ -1,0 +1,16 @@
+// Last-error text of the library (one per thread).
+#include "common.cuh"
+#include <string.h>
+
+static thread_local char g_error[1024] = "";
+
+void me_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+ME_API const char* me_last_error() { return g_error; }
+
+ME_API int me_abi_version() { return 1; }

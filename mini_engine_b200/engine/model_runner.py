@@ -1,0 +1,291 @@
+"""The model runner: weights, cache storage and ONE step function.
+
+Reference (engine/model_runner.py:24-145): ``run(seqs)`` flattens a ragged batch (single
+decoded tokens first, then portions of prompts), copies the metadata to the device, runs
+the model on exactly those tokens against the paged cache and computes logits only at the
+rows that sample.  Here ``step(items)`` does the same for any caller (the engine's
+scheduler, trace replay, tests): an item is (what the request holds of the cache, its next
+tokens, the position of the first, the places whose logits are wanted) and the result is
+the float32 logits of the wanted places, in the order of the items.  The metadata of a
+step is built with numpy into one pinned buffer and reaches the device in one copy.
+Steps that only decode replay a CUDA graph per batch-size bucket.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.manager import CacheHolder, CacheManager, GroupSpec
+from ..config.registry import get_architecture, load_model_config
+from ..parts.base import KVCacheNeed, StateNeed
+from ..parts.model import DecoderModel
+from ..weights.loader import load_weights
+from .step_context import AttnMeta, HostMeta, StepContext
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+@dataclass
+class StepItem:
+    holder: CacheHolder            # block tables (per group) and state slot of the request
+    tokens: Sequence[int]          # the request's next tokens
+    start: int                     # position of tokens[0] in the request
+    want: Sequence[int] = ()       # places among ``tokens`` whose logits are wanted
+
+
+def plan_cache_groups(model: DecoderModel) -> tuple[list[GroupSpec], dict[int, tuple[int, int]], dict[int, StateNeed]]:
+    """Group the model's cache slots by what they need; returns (groups, slot -> (group, index), slot -> state)."""
+    keyed: dict[tuple, list[int]] = {}
+    states: dict[int, StateNeed] = {}
+    for slot, needs in enumerate(model.slot_needs):
+        for need in needs:
+            if isinstance(need, KVCacheNeed):
+                keyed.setdefault((need.window, need.num_kv_heads, need.head_dim), []).append(slot)
+            elif isinstance(need, StateNeed):
+                states[slot] = need
+            else:
+                raise TypeError(f"cache slot {slot}: unknown kind of cache need {need!r}")
+    groups, location = [], {}
+    for (window, nkv, hd), slots in keyed.items():
+        for i, s in enumerate(slots):
+            location[s] = (len(groups), i)
+        groups.append(GroupSpec(window, nkv, hd, tuple(slots)))
+    return groups, location, states
+
+
+class ModelRunner:
+    def __init__(self, model_dir: str, dtype: str = "bfloat16", page_size: int = 16,
+                 num_pages: int = -1, max_num_seqs: int = 512, max_num_batched_tokens: int = 16384,
+                 max_model_len: int = 4096, gpu_memory_utilization: float = 0.9,
+                 use_cuda_graphs: bool = True, device: str = "cuda:0", model_config=None):
+        ops.require_extension()                      # fails loudly when the kernels cannot be had
+        self.device = torch.device(device)
+        self.act_dtype = _TORCH_DTYPE[dtype]
+        self.page_size = page_size
+        self.max_num_seqs = max_num_seqs
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self.model_config = model_config or load_model_config(model_dir)
+        self.max_model_len = min(max_model_len, self.model_config.max_position_embeddings)
+        arch = get_architecture(self.model_config.architecture)
+        self.model = DecoderModel(arch.plan(self.model_config))
+        load_weights(self.model, model_dir, self.act_dtype, self.device)
+        self.model.finalize_all(self.act_dtype, self.device)
+        self.vocab_size = self.model.plan.vocab_size
+
+        self.groups, self.slot_location, self.state_needs = plan_cache_groups(self.model)
+        self.error_flag = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.num_pages = num_pages if num_pages > 0 else self._size_pool(gpu_memory_utilization)
+        self.kv_pools = [torch.zeros(len(g.cache_slots), self.num_pages, 2, g.num_kv_heads, page_size,
+                                     g.head_dim, dtype=self.act_dtype, device=self.device)
+                         for g in self.groups]
+        self.num_state_slots = max_num_seqs if self.state_needs else 0
+        self.state_storage = {slot: torch.zeros(self.num_state_slots, *need.shape, dtype=torch.float32,
+                                                device=self.device)
+                              for slot, need in self.state_needs.items()}
+        self.ctx = StepContext(self)
+        self._staging: Optional[torch.Tensor] = None     # pinned host int32
+        self._staging_dev: Optional[torch.Tensor] = None
+        self.use_cuda_graphs = use_cuda_graphs
+        self._graphs: dict[int, Any] = {}
+        self.last_h2d_bytes = 0
+
+    # ---- sizes -----------------------------------------------------------------------
+    def page_bytes(self) -> int:
+        """Bytes of one page over all groups and their cache slots."""
+        return sum(len(g.cache_slots) * 2 * g.num_kv_heads * self.page_size * g.head_dim
+                   for g in self.groups) * self.act_dtype.itemsize
+
+    def _size_pool(self, utilization: float) -> int:
+        """Pages that fit into the share of device memory the engine may use, after the weights
+        and the work buffers of the largest step (the reference measures a warm-up step's peak,
+        engine/model_runner.py:59-80; here the work buffers are bounded by arithmetic)."""
+        free, total = torch.cuda.mem_get_info(self.device)
+        plan = self.model.plan
+        widest = max([plan.hidden_size * 4] + [self._widest_row_bytes()])
+        work = self.max_num_batched_tokens * widest * 3 + self.max_num_seqs * self.vocab_size * 4 * 2
+        budget = int(total * utilization) - (total - free) - work
+        per_page = max(self.page_bytes(), 1)
+        n = budget // per_page
+        # No request can use more than max_model_len tokens, so more pages than all requests
+        # could fill are never touched.
+        cap = self.max_num_seqs * ((self.max_model_len + self.page_size - 1) // self.page_size)
+        n = min(n, cap)
+        if n < 1:
+            raise RuntimeError("no device memory left for the cache pool: lower max_num_seqs / "
+                               "max_num_batched_tokens or raise gpu_memory_utilization")
+        return int(n)
+
+    def _widest_row_bytes(self) -> int:
+        w = 0
+        for _, part in self.model.walk():
+            for d in part.param_decls():
+                if len(d.shape) == 2:
+                    w = max(w, d.shape[0] * 4 if d.shape[0] < self.vocab_size else 0, d.shape[1] * 4)
+        return w
+
+    def make_cache_manager(self, enable_prefix_caching: bool = True) -> CacheManager:
+        return CacheManager(self.groups, self.num_pages, self.page_size,
+                            num_state_slots=self.num_state_slots,
+                            enable_prefix_caching=enable_prefix_caching,
+                            has_state=bool(self.state_needs))
+
+    # ---- the step --------------------------------------------------------------------
+    def _stage(self, n_ints: int) -> tuple[np.ndarray, torch.Tensor]:
+        if self._staging is None or self._staging.numel() < n_ints:
+            cap = max(n_ints * 2, 1 << 16)
+            self._staging = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._staging_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        return self._staging.numpy(), self._staging_dev
+
+    def build_batch(self, items: Sequence[StepItem], ctx: StepContext, *, pad_reqs: int = 0,
+                    table_width: int = 0) -> tuple[torch.Tensor, list[int]]:
+        """Lay the step's metadata out in pinned memory, copy it once, fill ``ctx``.
+
+        Requests that bring one token come first (as in engine/model_runner.py:88-89).
+        ``pad_reqs``/``table_width`` give a fixed shape to steps replayed from a graph: padding
+        requests have no keys and write nowhere.  Returns (token ids on the device, the batch
+        order as indices into ``items``)."""
+        order = [i for i, it in enumerate(items) if len(it.tokens) == 1] + \
+                [i for i, it in enumerate(items) if len(it.tokens) != 1]
+        D = sum(1 for it in items if len(it.tokens) == 1)
+        lens = [len(items[i].tokens) for i in order]
+        if any(n < 1 for n in lens):
+            raise ValueError("every item of a step must bring at least one token")
+        B_real = len(order)
+        B = max(B_real, pad_reqs)
+        pad = B - B_real
+        T_real = sum(lens)
+        T = T_real + pad
+        ps = self.page_size
+        G = len(self.groups)
+        starts = [items[i].start for i in order]
+        ends = [s + n for s, n in zip(starts, lens)]
+        if ends and max(ends) > self.model_config.max_position_embeddings:
+            raise ValueError(f"position {max(ends) - 1} is beyond max_position_embeddings")
+        widths = []
+        for g in range(G):
+            w = max([len(items[i].holder.block_tables[g]) for i in order] + [1, table_width])
+            widths.append(w)
+        want_rows: list[int] = []
+        offsets = {}
+        off = 0
+        for k, i in enumerate(order):
+            offsets[i] = off
+            off += lens[k]
+        for i, it in enumerate(items):
+            for w in it.want:
+                if not 0 <= w < len(it.tokens):
+                    raise ValueError(f"wanted place {w} is outside the item's {len(it.tokens)} tokens")
+                want_rows.append(offsets[i] + w)
+        S = len(want_rows)
+        BQ = ops.ATTN_TILE_Q
+        tiles = [(b, q0) for b in range(D, B_real) for q0 in range(0, lens[b], BQ)]
+        n_tiles = len(tiles)
+
+        def al(n):                       # keep every array 16-byte aligned on the device
+            return (n + 3) & ~3
+        sizes = dict(tok=al(T), pos=al(T), req=al(T), cu=al(B + 1), ctxlen=al(B), slot=al(B),
+                     rows=al(max(S, 1)), tiles=al(max(2 * n_tiles, 1)))
+        total = sum(sizes.values()) + sum(al(T) + al(B * widths[g]) for g in range(G))
+        host, dev = self._stage(total)
+        cur = 0
+
+        def take(n):
+            nonlocal cur
+            a, cur = cur, cur + n
+            return a
+        o_tok, o_pos, o_req = take(sizes["tok"]), take(sizes["pos"]), take(sizes["req"])
+        o_cu, o_ctx, o_slot = take(sizes["cu"]), take(sizes["ctxlen"]), take(sizes["slot"])
+        o_rows, o_tiles = take(sizes["rows"]), take(sizes["tiles"])
+        o_sm = [take(al(T)) for _ in range(G)]
+        o_bt = [take(al(B * widths[g])) for g in range(G)]
+
+        host[o_tok:o_tok + T] = 0
+        host[o_pos:o_pos + T] = 0
+        t = 0
+        cu = [0]
+        for k, i in enumerate(order):
+            n = lens[k]
+            host[o_tok + t:o_tok + t + n] = np.asarray(items[i].tokens, dtype=np.int32)
+            host[o_pos + t:o_pos + t + n] = np.arange(starts[k], ends[k], dtype=np.int32)
+            host[o_req + t:o_req + t + n] = k
+            t += n
+            cu.append(t)
+        for k in range(pad):
+            host[o_req + T_real + k] = B_real + k
+            cu.append(T_real + k + 1)
+        host[o_cu:o_cu + B + 1] = cu
+        host[o_ctx:o_ctx + B] = ends + [0] * pad
+        host[o_slot:o_slot + B] = [items[i].holder.state_slot for i in order] + [-1] * pad
+        if S:
+            host[o_rows:o_rows + S] = want_rows
+        if n_tiles:
+            host[o_tiles:o_tiles + 2 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+        for g in range(G):
+            w = widths[g]
+            bt = host[o_bt[g]:o_bt[g] + B * w].reshape(B, w)
+            bt[:] = -1
+            sm = host[o_sm[g]:o_sm[g] + T]
+            sm[:] = -1
+            t = 0
+            for k, i in enumerate(order):
+                table = np.asarray(items[i].holder.block_tables[g], dtype=np.int32)
+                bt[k, :len(table)] = table
+                pos = np.arange(starts[k], ends[k])
+                page = pos // ps
+                if len(table) <= int(page[-1]):
+                    raise ValueError("a request's block table does not cover its new tokens")
+                pages = table[page]
+                if (pages < 0).any():
+                    raise ValueError("a new token would be written to a page that was given back")
+                sm[t:t + lens[k]] = pages * ps + pos % ps
+                t += lens[k]
+        dev[:total].copy_(self._staging[:total], non_blocking=True)
+        self.last_h2d_bytes = total * 4
+
+        ctx.positions = dev[o_pos:o_pos + T]
+        ctx.token_req = dev[o_req:o_req + T]
+        ctx.state_slots = dev[o_slot:o_slot + B]
+        ctx.logits_rows = dev[o_rows:o_rows + S]
+        ctx._bt = [dev[o_bt[g]:o_bt[g] + B * widths[g]].view(B, widths[g]) for g in range(G)]
+        ctx._sm = [dev[o_sm[g]:o_sm[g] + T] for g in range(G)]
+        ctx.attn_meta = AttnMeta(
+            num_reqs=B, num_tokens=T, num_decodes=D + pad if pad_reqs else D,
+            cu_seqlens=dev[o_cu:o_cu + B + 1], context_lens=dev[o_ctx:o_ctx + B],
+            tiles=dev[o_tiles:o_tiles + 2 * max(n_tiles, 1)].view(-1, 2), num_tiles=n_tiles,
+            max_context_len=max(ends + [1]) if not table_width else table_width * ps,
+            workspace=ctx.buffer)
+        ctx.host = HostMeta(starts=starts, lengths=lens,
+                            state_slots=[items[i].holder.state_slot for i in order],
+                            holders=[items[i].holder for i in order])
+        return dev[o_tok:o_tok + T], order
+
+    @torch.inference_mode()
+    def step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
+        """Run exactly the tokens of ``items`` as one batch against the cache.
+
+        Returns float32 logits ``[wanted, vocab]`` in the order of the items and of each item's
+        ``want`` (None when nothing is wanted).  The tensor is a work buffer: it is overwritten
+        by the next step."""
+        if not items:
+            return None
+        if len(items) > self.max_num_seqs:
+            raise ValueError(f"{len(items)} requests in one step, max_num_seqs is {self.max_num_seqs}")
+        ctx = self.ctx
+        token_ids, _ = self.build_batch(items, ctx)
+        hidden = self.model.forward(token_ids, ctx)
+        if ctx.logits_rows.numel() == 0:
+            return None
+        return self.model.compute_logits(hidden, ctx)
+
+    def check_device_errors(self) -> None:
+        """Raise if a kernel flagged bad input (a token id outside the vocabulary)."""
+        flags = self.error_flag.tolist()
+        if any(flags):
+            self.error_flag.zero_()
+            raise RuntimeError(f"a kernel reported bad input: flags {flags} "
+                               "(flag 0: token id outside the vocabulary)")

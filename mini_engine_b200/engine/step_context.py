@@ -1,0 +1,88 @@
+"""Everything one step knows, handed to every part explicitly.
+
+The reference passes this through a module global (utils/context.py:3-27: cu_seqlens_q,
+slot_mapping, context_lens, block_tables, num_decodes, logits_indices, ...).  Here it is an
+object: device tensors that kernels read, the same numbers on the host for parts that
+decide in Python, the cache storage, and named work buffers that are reused from step to
+step (a CUDA graph keeps a context of its own, so its buffers never move).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+
+@dataclass
+class KVView:
+    """One cache slot's pages as the mixer sees them in this step."""
+    pool: torch.Tensor                 # [num_pages, 2, kv_heads, page_size, head_dim]
+    page_size: int
+    block_tables: torch.Tensor         # [B, max_pages] int32, -1 where there is no page
+    slot_mapping: torch.Tensor         # [T] int32: page * page_size + offset, -1 = do not write
+    group: int
+
+
+@dataclass
+class AttnMeta:
+    """Batch shape for the attention kernels.  Requests [0, num_decodes) bring one token each."""
+    num_reqs: int
+    num_tokens: int
+    num_decodes: int
+    cu_seqlens: torch.Tensor           # [B+1] int32
+    context_lens: torch.Tensor         # [B] int32: keys of the request after this step
+    tiles: torch.Tensor                # [num_tiles, 2] int32: (request, first local query) per query tile
+    num_tiles: int
+    max_context_len: int               # host upper bound of context_lens (sizes split-K scratch)
+    workspace: Any                     # callable (name, shape, dtype) -> tensor
+
+
+@dataclass
+class HostMeta:
+    """The step's shape on the host, in batch order."""
+    starts: list[int]                  # position of each request's first token in this step
+    lengths: list[int]                 # tokens of each request in this step
+    state_slots: list[int]
+    holders: list[Any]
+
+
+class StepContext:
+    def __init__(self, runner, arena: Optional[dict] = None):
+        self.runner = runner
+        self.act_dtype: torch.dtype = runner.act_dtype
+        self.device = runner.device
+        self.error_flag: torch.Tensor = runner.error_flag
+        self._arena: dict[str, torch.Tensor] = {} if arena is None else arena
+        self.frozen = False            # a captured graph's buffers must not be reallocated
+        # Filled per step:
+        self.positions: torch.Tensor = None
+        self.token_req: torch.Tensor = None
+        self.state_slots: torch.Tensor = None
+        self.logits_rows: torch.Tensor = None
+        self.attn_meta: AttnMeta = None
+        self.host: HostMeta = None
+        self._bt: list[torch.Tensor] = []
+        self._sm: list[torch.Tensor] = []
+
+    def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A work buffer by name: the same storage every step, grown when a step needs more."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = max(n * dtype.itemsize, 16)
+        flat = self._arena.get(name)
+        if flat is None or flat.numel() < nbytes:
+            if self.frozen:
+                raise RuntimeError(f"work buffer {name!r} would move under a captured graph")
+            flat = torch.empty(nbytes + (-nbytes) % 256, dtype=torch.uint8, device=self.device)
+            self._arena[name] = flat
+        return flat[:n * dtype.itemsize].view(dtype).view(*shape)
+
+    def kv_cache(self, cache_slot: int) -> KVView:
+        g, idx = self.runner.slot_location[cache_slot]
+        return KVView(self.runner.kv_pools[g][idx], self.runner.page_size, self._bt[g], self._sm[g], g)
+
+    def state(self, cache_slot: int) -> torch.Tensor:
+        """Storage of a mixer's per-request state: [num_state_slots, *shape] float32."""
+        return self.runner.state_storage[cache_slot]

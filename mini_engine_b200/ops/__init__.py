@@ -1,0 +1,228 @@
+"""Python side of the CUDA kernels: loads the library and checks arguments before a launch.
+
+Every function here runs a hand-written sm_100a kernel of ``csrc/`` on the current CUDA
+stream.  There is no other implementation behind them: without the library (no nvcc, no
+GPU) they raise.  The reference builds its kernels with torch's JIT at import
+(layers/ops.py:5-18); here the build is a plain nvcc run at the first call.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+ATTN_TILE_Q = 16          # queries per block of the chunk-attention kernels (csrc/attention_chunk.cu)
+DECODE_PARTITION = 256    # keys per partition of the decode kernel (csrc/attention_decode.cu)
+MAX_HEAD_DIM = 256
+
+_P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+_PROTOS = {
+    "me_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+    "me_add_rmsnorm": [_P, _P, _I, _P, _F, _P, _I, _P, _I, _I, _P],
+    "me_silu_mul": [_P, _P, _I, _I, _I, _P],
+    "me_gemm_simt": [_P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P],
+    "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
+    "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P],
+    "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P],
+}
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+_lib: Optional[ctypes.CDLL] = None
+launches = 0              # kernels launched through this module (counted for the benchmark)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def require_extension() -> ctypes.CDLL:
+    """The loaded kernel library; builds it at the first call; raises if that is impossible."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not torch.cuda.is_available():
+        raise KernelError("mini_engine_b200 needs a CUDA device: its kernels have no CPU path")
+    path = _build.library_path()
+    lib = ctypes.CDLL(path)
+    lib.me_last_error.restype = ctypes.c_char_p
+    for name, args in _PROTOS.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = ctypes.c_int
+    if lib.me_attn_chunk_tile_q() != ATTN_TILE_Q or lib.me_attn_decode_partition() != DECODE_PARTITION:
+        raise KernelError("the kernel library and ops/__init__.py disagree on tile sizes")
+    _lib = lib
+    return lib
+
+
+def library_file() -> str:
+    require_extension()
+    return _lib._name
+
+
+def _call(name: str, *args) -> None:
+    global launches
+    lib = _lib or require_extension()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise KernelError(lib.me_last_error().decode())
+    launches += 1
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported by the kernels (float32 and bfloat16 are)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def check_attention_sizes(head_dim: int, num_heads: int, num_kv_heads: int) -> None:
+    """What the attention kernels take; anything else is refused here, before any launch."""
+    if head_dim % 16 or not 16 <= head_dim <= MAX_HEAD_DIM:
+        raise ValueError(f"head_dim {head_dim} is not supported: the attention kernels take multiples "
+                         f"of 16 from 16 to {MAX_HEAD_DIM}")
+    if num_heads < 1 or num_kv_heads < 1 or num_heads % num_kv_heads:
+        raise ValueError(f"{num_heads} heads with {num_kv_heads} key/value heads is not supported")
+
+
+# ---- element-wise and normalisation ----------------------------------------------------
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
+    _need(ids.dtype == torch.int32 and ids.is_contiguous(), "embed: token ids must be contiguous int32")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous(), "embed: bad tensors")
+    T, (V, H) = ids.shape[0], table.shape
+    _need(tuple(out.shape) == (T, H), "embed: output shape")
+    _call("me_embed", ids.data_ptr(), table.data_ptr(), _dt(table), out.data_ptr(), T, H, V, err.data_ptr(), _stream())
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """``residual += delta`` (float32, in place), ``out = rmsnorm(residual) * weight``; with ``rows``
+    only those rows are read and ``residual`` is not written."""
+    H = residual.shape[1]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_rmsnorm: residual must be float32")
+    _need(weight.dtype == torch.float32 and weight.shape == (H,), "add_rmsnorm: weight must be float32 [H]")
+    n = residual.shape[0] if rows is None else rows.shape[0]
+    _need(out.is_contiguous() and tuple(out.shape) == (n, H), "add_rmsnorm: output shape")
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.shape == residual.shape, "add_rmsnorm: delta shape")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.is_contiguous(), "add_rmsnorm: rows must be int32")
+    _call("me_add_rmsnorm", residual.data_ptr(), _ptr(delta), _dt(delta) if delta is not None else 0,
+          weight.data_ptr(), float(eps), out.data_ptr(), _dt(out), _ptr(rows), n, H, _stream())
+
+
+def silu_mul(x: torch.Tensor, out: torch.Tensor) -> None:
+    T, I2 = x.shape
+    _need(I2 % 2 == 0 and tuple(out.shape) == (T, I2 // 2) and x.dtype == out.dtype, "silu_mul: shapes")
+    _need(x.is_contiguous() and out.is_contiguous(), "silu_mul: contiguous tensors")
+    _call("me_silu_mul", x.data_ptr(), out.data_ptr(), _dt(x), T, I2 // 2, _stream())
+
+
+# ---- matrix products ----------------------------------------------------------------------
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "none") -> None:
+    """``out = x @ weight.T`` with float32 accumulation; ``epilogue="silu_mul"`` takes a weight of
+    rows gate | up and writes ``silu(x Wg^T) * (x Wu^T)``."""
+    M, K = x.shape
+    _need(weight.dim() == 2 and weight.shape[1] == K and weight.is_contiguous(), "linear: weight shape")
+    _need(x.stride(1) == 1 and out.stride(1) == 1, "linear: rows must be contiguous")
+    epi = {"none": 0, "silu_mul": 1}[epilogue]
+    N = weight.shape[0] // 2 if epi else weight.shape[0]
+    _need(tuple(out.shape) == (M, N), f"linear: output is {tuple(out.shape)}, expected {(M, N)}")
+    _call("me_gemm_simt", x.data_ptr(), _dt(x), x.stride(0), weight.data_ptr(), _dt(weight),
+          out.data_ptr(), _dt(out), out.stride(0), M, N, K, epi, _stream())
+
+
+# ---- attention ------------------------------------------------------------------------------
+def qk_norm_rope_kv_write(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                          q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                          cos_sin: Optional[torch.Tensor], positions: torch.Tensor,
+                          slot_mapping: Optional[torch.Tensor], pool: torch.Tensor, page_size: int) -> None:
+    """In place on the packed rows q|k|v: RMSNorm of every q and k head, rotary embedding, and the
+    write of k and v to ``pool`` [pages, 2, kv_heads, page_size, head_dim] at ``slot_mapping``."""
+    T = qkv.shape[0]
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, "qk_norm_rope: qkv shape")
+    _need(pool.dtype == qkv.dtype and pool.is_contiguous()
+          and tuple(pool.shape[1:]) == (2, num_kv_heads, page_size, head_dim), "qk_norm_rope: pool shape")
+    for w in (q_weight, k_weight):
+        if w is not None:
+            _need(w.dtype == torch.float32 and w.shape == (head_dim,), "qk_norm_rope: norm weights are float32 [head_dim]")
+    if cos_sin is not None:
+        _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == head_dim,
+              "qk_norm_rope: the rotary table must be float32 [positions, head_dim]")
+    _need(positions.dtype == torch.int32 and positions.shape[0] == T, "qk_norm_rope: positions")
+    if slot_mapping is not None:
+        _need(slot_mapping.dtype == torch.int32 and slot_mapping.shape[0] == T, "qk_norm_rope: slot mapping")
+    _call("me_qk_norm_rope_kv_write", qkv.data_ptr(), _dt(qkv), qkv.stride(0), T, num_heads, num_kv_heads,
+          head_dim, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos_sin), positions.data_ptr(),
+          _ptr(slot_mapping), pool.data_ptr(), page_size, _stream())
+
+
+def attention_chunks(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
+                     scale, window, tiles=None, num_tiles=None) -> None:
+    """The chunk kernel over the query tiles of ``meta`` (requests that bring several tokens)."""
+    tiles = meta.tiles if tiles is None else tiles
+    n = meta.num_tiles if num_tiles is None else num_tiles
+    _call("me_attn_chunk", qkv.data_ptr(), _dt(qkv), qkv.stride(0), out.data_ptr(), out.stride(0),
+          pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
+          meta.context_lens.data_ptr(), tiles.data_ptr(), n, num_heads, num_kv_heads, head_dim,
+          page_size, float(scale), int(window or 0), _stream())
+
+
+def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
+                     scale, window) -> None:
+    """The split-K decode kernel and its merge over requests [0, meta.num_decodes)."""
+    D = meta.num_decodes
+    parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
+    tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * parts * head_dim,), torch.float32)
+    tmp_ml = meta.workspace("decode_tmp_ml", (2, D * num_heads * parts), torch.float32)
+    _call("me_attn_decode", qkv.data_ptr(), _dt(qkv), qkv.stride(0), out.data_ptr(), out.stride(0),
+          pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
+          meta.context_lens.data_ptr(), D, num_heads, num_kv_heads, head_dim, page_size, float(scale),
+          int(window or 0), tmp_out.data_ptr(), tmp_ml[0].data_ptr(), tmp_ml[1].data_ptr(), parts, _stream())
+    global launches
+    launches += 1          # partition kernel + merge kernel
+
+
+def paged_attention(qkv: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                    pool: torch.Tensor, page_size: int, block_tables: torch.Tensor, meta, scale: float,
+                    window: Optional[int]) -> None:
+    """Attention of one step over the paged cache: requests that bring one token go to the decode
+    kernel, portions of prompts to the chunk kernel; both write their rows of ``out``
+    (the split of layers/attention.py:64-76)."""
+    check_attention_sizes(head_dim, num_heads, num_kv_heads)
+    _need(qkv.stride(1) == 1 and out.stride(1) == 1 and out.shape[1] == num_heads * head_dim, "paged_attention: shapes")
+    _need(pool.dtype == qkv.dtype == out.dtype and pool.is_contiguous(), "paged_attention: dtypes")
+    _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "paged_attention: block tables")
+    if meta.num_decodes > 0:
+        attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window)
+    if meta.num_tiles > 0:
+        attention_chunks(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window)
+
+
+# ---- sampling -------------------------------------------------------------------------------
+def sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor, positions: torch.Tensor,
+           out: torch.Tensor) -> None:
+    S, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: logits must be float32 rows")
+    _need(temperatures.dtype == torch.float32 and seeds.dtype == torch.int32 and positions.dtype == torch.int32
+          and out.dtype == torch.int32, "sample: dtypes")
+    _need(temperatures.shape[0] == S and seeds.shape[0] == S and positions.shape[0] == S and out.shape[0] == S, "sample: sizes")
+    _call("me_sample", logits.data_ptr(), logits.stride(0), temperatures.data_ptr(), seeds.data_ptr(),
+          positions.data_ptr(), out.data_ptr(), S, V, _stream())

@@ -1,0 +1,12 @@
+from .base import (DiskSource, FeedForward, KVCacheNeed, Mixer, Norm, ParamDecl, Part,
+                   PositionEncoding, StateNeed)
+from .registry import (PartSpec, build_part, register_feed_forward, register_mixer, register_norm,
+                       register_position_encoding, registered)
+from .norm import RMSNorm
+from .rope import RotaryEmbedding
+from .linear import Linear
+from .attention import GQAAttention
+from .mlp import SwiGLU
+from .embed import LMHead, TokenEmbedding
+from .block import BlockSpec, PreNormBlock, SharedRef
+from .model import DecoderModel, LayerCall, ModelPlan

@@ -1,0 +1,108 @@
+"""Interfaces that every part of a layer implements.
+
+A *part* (norm, position encoding, mixer, feed-forward, embedding, head) knows its own
+sizes and constants, which it gets as constructor parameters, and nothing about the
+model it sits in.  It declares
+
+* its parameters (``param_decls``): shapes, how they are initialised at random and from
+  which tensors on disk each one is filled (several disk tensors may be packed into one
+  parameter, as the reference packs q/k/v and gate/up: layers/linear.py:4-45,
+  models/qwen3.py:96-102);
+* what it needs of the cache (``cache_needs``): pages of keys and values, all of them or
+  a window, and/or a slot of fixed size per request.
+
+and runs on the tokens of one step through ``forward``; everything a step knows (token
+positions, which request a token belongs to, block tables, state slots, the cache
+storage, work buffers) arrives in the ``StepContext``, never through a module global as
+in the reference (utils/context.py:3-27).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class DiskSource:
+    """Rows ``[row_start, row_start+rows)`` of a parameter come from one tensor on disk."""
+    disk_name: str
+    row_start: int
+    rows: int
+
+
+@dataclass
+class ParamDecl:
+    name: str                              # local name; the owner's prefix is put in front
+    shape: tuple[int, ...]
+    init: str = "normal"                   # "normal": N(0, 0.02); "norm": 1 + N(0, 0.1)
+    sources: list[DiskSource] = field(default_factory=list)   # empty: one tensor, same name
+    role: str = "matrix"                   # "matrix" | "vector" (vectors are held in float32)
+    tied_to: Optional[str] = None          # full name of the parameter whose storage is shared
+
+
+@dataclass(frozen=True)
+class KVCacheNeed:
+    """Paged keys and values: ``window=None`` keeps every key, else the last ``window``."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A slot of fixed size per request (float32 elements)."""
+    shape: tuple[int, ...]
+
+
+class Part:
+    """Base of all parts.  ``params`` is filled by the weight loader."""
+
+    def __init__(self):
+        self.params: dict[str, torch.Tensor] = {}
+
+    def param_decls(self) -> list[ParamDecl]:
+        return []
+
+    def cache_needs(self) -> list[Any]:
+        return []
+
+    def sub_parts(self) -> list[tuple[str, "Part"]]:
+        """(relative prefix, part) pairs of the parts this one is put together from."""
+        return []
+
+    def finalize(self, dtype: torch.dtype, device: torch.device) -> None:
+        """Called once after the parameters are in place (build tables, check dtypes)."""
+
+    def p(self, name: str) -> torch.Tensor:
+        try:
+            return self.params[name]
+        except KeyError:
+            raise RuntimeError(f"{type(self).__name__}: parameter {name!r} was never loaded") from None
+
+
+class Mixer(Part):
+    """Mixes information between the tokens of a request (attention, or a mixer with state)."""
+
+    def forward(self, x: torch.Tensor, ctx: "Any", call: "Any") -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: "Any") -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: "Any",
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``residual += delta`` (if given), then the normalised rows in the working dtype.
+
+        With ``rows`` only those rows are normalised and ``residual`` is left unchanged.
+        """
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Position information applied to queries and keys before the cache write."""

@@ -1,0 +1,33 @@
+"""SwiGLU feed-forward: ``down( silu(gate(x)) * up(x) )``.
+
+Reference: models/qwen3.py:42-51, layers/activation.py:4-7; gate and up are packed into
+one weight (rows gate | up) so that one product reads x once, and SiLU-and-multiply runs in
+that product's epilogue.
+"""
+from __future__ import annotations
+
+from .base import FeedForward
+from .linear import Linear
+from .registry import register_feed_forward
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.gate_up_proj = Linear(hidden_size, [("gate_proj.weight", intermediate_size),
+                                                 ("up_proj.weight", intermediate_size)],
+                                   name="gate_up_proj.weight")
+        self.down_proj = Linear(intermediate_size, [("down_proj.weight", hidden_size)],
+                                name="down_proj.weight")
+
+    def sub_parts(self):
+        return [("", self.gate_up_proj), ("", self.down_proj)]
+
+    def forward(self, x, ctx):
+        act = self.gate_up_proj.forward(x, ctx, "ffn_act", epilogue="silu_mul")
+        return self.down_proj.forward(act, ctx, "ffn_out")
+
+
+register_feed_forward("swiglu", SwiGLU)

@@ -1,0 +1,36 @@
+"""RMSNorm with the residual sum folded in.
+
+Reference formula (layers/layernorm.py:11-23): ``y = x * rsqrt(mean(x^2) + eps)`` in
+float32, cast to the working dtype, times the weight; with a residual the sum
+``x + residual`` is normalised and also returned.  Here the residual stream itself is
+kept in float32 in both precisions, so the sum, the statistics and the weight multiply
+all happen in float32 and the result is rounded once.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from .base import Norm, ParamDecl
+from .registry import register_norm
+
+
+class RMSNorm(Norm):
+    def __init__(self, size: int, eps: float):
+        super().__init__()
+        self.size = size
+        self.eps = float(eps)
+
+    def param_decls(self):
+        return [ParamDecl("weight", (self.size,), init="norm", role="vector")]
+
+    def forward(self, residual, delta, ctx, rows: Optional[torch.Tensor] = None):
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer("norm_out", (n, self.size), ctx.act_dtype)
+        ops.add_rmsnorm(residual, delta, self.p("weight"), self.eps, out, rows=rows)
+        return out
+
+
+register_norm("rmsnorm", RMSNorm)

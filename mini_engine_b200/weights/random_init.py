@@ -1,0 +1,60 @@
+"""Random-weights mode: write a model folder from a configuration and a seed.
+
+The reference has no such mode (its parameters are ``torch.empty`` until loaded,
+layers/linear.py:10,34).  The folder holds ``config.json`` and ``model.safetensors`` with
+the architecture's own disk names (unpacked q/k/v and gate/up), so that the engine loads
+it like any other model and the by-name loader is exercised.  Matrices are N(0, 0.02),
+norm weights 1 + N(0, 0.1), drawn tensor by tensor in the model's declaration order from
+one seeded CPU generator.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Any
+
+import torch
+from safetensors.torch import save_file
+
+from ..config.model_config import architecture_name
+from ..config.registry import get_architecture
+from ..parts.model import DecoderModel
+from .loader import expected_disk_tensors, iter_param_decls
+
+
+def build_model_from_config_dict(raw: dict[str, Any]) -> tuple[Any, DecoderModel]:
+    arch = get_architecture(architecture_name(raw))
+    cfg = arch.config_from_dict(raw)
+    return cfg, DecoderModel(arch.plan(cfg))
+
+
+def random_state_dict(model: DecoderModel, seed: int, dtype: torch.dtype = torch.bfloat16,
+                      matrix_std: float = 0.02, norm_std: float = 0.1) -> dict[str, torch.Tensor]:
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(int(seed))
+    init_of = {}
+    for prefix, _, decl in iter_param_decls(model):
+        if decl.tied_to is not None:
+            continue
+        names = [prefix + s.disk_name for s in decl.sources] or [prefix + decl.name]
+        for n in names:
+            init_of[n] = decl.init
+    out: dict[str, torch.Tensor] = {}
+    for name, e in expected_disk_tensors(model).items():
+        x = torch.randn(e.shape, generator=gen, dtype=torch.float32)
+        x = 1.0 + norm_std * x if init_of[name] == "norm" else matrix_std * x
+        out[name] = x.to(dtype).contiguous()
+    return out
+
+
+def write_random_model(folder: str, config: dict[str, Any], seed: int,
+                       dtype: torch.dtype = torch.bfloat16) -> str:
+    """Write ``config.json`` and ``model.safetensors`` into ``folder``; returns the folder."""
+    folder = os.path.expanduser(folder)
+    os.makedirs(folder, exist_ok=True)
+    _, model = build_model_from_config_dict(config)
+    tensors = random_state_dict(model, seed, dtype)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(config, f, indent=1)
+    save_file(tensors, os.path.join(folder, "model.safetensors"))
+    return folder
