@@ -10,11 +10,58 @@ import argparse
 import json
 import os
 import sys
+from typing import Optional
 
 import numpy as np
 
 from ..cache.manager import CacheHolder
 from ..config.registry import load_model_config
+
+
+class TraceReplayer:
+    """Feeds steps ``{"step", "entries": [{"id", "tokens", "want"}], "end"}`` to a model runner."""
+
+    def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, **runner_args):
+        from .model_runner import ModelRunner
+        unit = max(64, page_size)
+        held = (max_tokens + unit - 1) // unit * unit
+        num_pages = max(1, (held + page_size - 1) // page_size)
+        cfg = load_model_config(model_dir)
+        args = dict(max_num_seqs=8, max_num_batched_tokens=4096, max_model_len=cfg.max_position_embeddings)
+        args.update(runner_args)
+        self.runner = ModelRunner(model_dir, dtype=dtype, page_size=page_size, num_pages=num_pages,
+                                  model_config=cfg, **args)
+        self.cache = self.runner.make_cache_manager(enable_prefix_caching=False)
+        self.live: dict[str, CacheHolder] = {}
+
+    def run_step(self, rec: dict) -> Optional[np.ndarray]:
+        """Runs one step; returns the logits at the wanted places ([wanted, vocab] float32) or None."""
+        from .model_runner import StepItem
+        items, n_want = [], 0
+        for e in rec.get("entries", []):
+            rid, toks = str(e["id"]), [int(t) for t in e["tokens"]]
+            if not toks:
+                continue
+            h = self.live.get(rid)
+            if h is None:
+                h = self.live[rid] = CacheHolder()
+            if not self.cache.allocate(h, len(toks)):
+                raise RuntimeError(f"step {rec.get('step')}: no pages left for request {rid!r} (free pages per "
+                                   f"group: {self.cache.num_free_pages}); raise --max-tokens")
+            want = [int(w) for w in e.get("want", [])]
+            n_want += len(want)
+            items.append(StepItem(h, toks, h.num_computed_tokens, want))
+        logits = self.runner.step(items) if items else None
+        out = logits.cpu().numpy().astype("<f4", copy=True) if n_want else None
+        for it in items:
+            it.holder.num_computed_tokens += len(it.tokens)
+            self.cache.release_behind_window(it.holder)
+        self.runner.check_device_errors()
+        for rid in rec.get("end", []):
+            h = self.live.pop(str(rid), None)
+            if h is not None:
+                self.cache.free(h)
+        return out
 
 
 def main(argv=None) -> int:
@@ -27,51 +74,16 @@ def main(argv=None) -> int:
     ap.add_argument("--page-size", type=int, default=16)
     args = ap.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)
-
-    from .model_runner import ModelRunner, StepItem
-    page = args.page_size
-    unit = max(64, page)
-    num_pages = max(1, ((args.max_tokens + unit - 1) // unit * unit + page - 1) // page)
-    cfg = load_model_config(args.model)
-    runner = ModelRunner(args.model, dtype=args.dtype, page_size=page, num_pages=num_pages,
-                         max_num_seqs=8, max_num_batched_tokens=4096,
-                         max_model_len=cfg.max_position_embeddings, model_config=cfg)
-    cache = runner.make_cache_manager(enable_prefix_caching=False)
-    live: dict[str, CacheHolder] = {}
-
+    replayer = TraceReplayer(args.model, args.dtype, args.max_tokens, args.page_size)
     for line in sys.stdin:
         line = line.strip()
         if not line:
             continue
         rec = json.loads(line)
-        step = rec["step"]
-        items, n_want = [], 0
-        for e in rec.get("entries", []):
-            rid, toks = str(e["id"]), [int(t) for t in e["tokens"]]
-            if not toks:
-                continue
-            h = live.get(rid)
-            if h is None:
-                h = live[rid] = CacheHolder()
-            if not cache.allocate(h, len(toks)):
-                raise RuntimeError(f"step {step}: no pages left for request {rid!r} "
-                                   f"(free pages per group: {cache.num_free_pages}); raise --max-tokens")
-            want = [int(w) for w in e.get("want", [])]
-            n_want += len(want)
-            items.append(StepItem(h, toks, h.num_computed_tokens, want))
-        logits = runner.step(items) if items else None
-        if n_want:
-            arr = logits.cpu().numpy().astype("<f4", copy=False)
-            arr.tofile(os.path.join(args.out, f"{step}.f32"))
-        for it in items:
-            it.holder.num_computed_tokens += len(it.tokens)
-            cache.release_behind_window(it.holder)
-        runner.check_device_errors()
-        for rid in rec.get("end", []):
-            h = live.pop(str(rid), None)
-            if h is not None:
-                cache.free(h)
-        print(f"done {step}", flush=True)
+        logits = replayer.run_step(rec)
+        if logits is not None:
+            logits.tofile(os.path.join(args.out, f"{rec['step']}.f32"))
+        print(f"done {rec['step']}", flush=True)
     return 0
 
 

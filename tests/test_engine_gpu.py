@@ -1,0 +1,115 @@
+"""Generation through the Python entry point against the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_model
+import plain_ops
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+
+
+def _llm(name, dtype, **kw):
+    from mini_engine_b200 import LLM
+    args = dict(dtype=dtype, kvcache_block_size=ALL[name][2], num_kvcache_blocks=64, max_num_seqs=8,
+                max_num_batched_tokens=64, max_model_len=256)
+    args.update(kw)
+    return LLM(helpers.model_folder(name), **args)
+
+
+def _check_greedy(name, dtype, prompt, tokens):
+    """Every generated token is the plain implementation's argmax, or within the tolerance of it."""
+    ref = helpers.plain_logits(name, list(prompt) + list(tokens))
+    for k, t in enumerate(tokens):
+        row = ref[len(prompt) + k - 1]
+        assert row[t] >= row.max() - 2 * helpers.TOL[dtype], f"token {k}: {t} is not the plain argmax {row.argmax()}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation(name, dtype):
+    from mini_engine_b200 import SamplingParams
+    llm = _llm(name, dtype)
+    lengths = (5, 17, 33, 9) if name == "A" else (3, 40, 21, 12)
+    prompts = helpers.random_requests(ALL[name][0]["vocab_size"], lengths, seed=2)
+    out = llm.generate(prompts, SamplingParams(temperature=0, max_tokens=8), use_tqdm=False)
+    assert [len(o["token_ids"]) for o in out] == [8] * len(prompts)
+    for p, o in zip(prompts, out):
+        _check_greedy(name, dtype, p, o["token_ids"])
+    if dtype == "float32":
+        cfg, w = helpers.plain_weights(name)
+        assert out[1]["token_ids"] == plain_model.greedy_generate(cfg, w, prompts[1], 8)
+    llm.cache.check([])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_sampling_with_shared_prefix_and_small_budget(dtype):
+    """Six prompts of 3 to 40 tokens, two sharing a 16-token prefix, portions under a budget of 24,
+    temperature 0.7 with fixed seeds: every drawn token wins the race on the plain logits."""
+    from mini_engine_b200 import SamplingParams
+    name = "B"
+    llm = _llm(name, dtype, max_num_batched_tokens=24)
+    prompts = helpers.random_requests(ALL[name][0]["vocab_size"], (3, 40, 17, 29, 9, 33), seed=3)
+    prompts[4] = prompts[1][:16] + prompts[4]
+    sps = [SamplingParams(temperature=0.7, max_tokens=6, seed=100 + i, ignore_eos=True) for i in range(6)]
+    out = llm.generate(prompts, sps, use_tqdm=False)
+    margin = 2 * helpers.TOL[dtype] / 0.7
+    for i, (p, o) in enumerate(zip(prompts, out)):
+        ref = helpers.plain_logits(name, list(p) + o["token_ids"])
+        for k, t in enumerate(o["token_ids"]):
+            pos = len(p) + k
+            keys = plain_ops.sample_keys(torch.from_numpy(ref[pos - 1]), 0.7, 100 + i, pos)
+            assert keys[t] >= keys.max() - margin, f"request {i} token {k}"
+    # the same seeds give the same tokens whatever the batching
+    llm2 = _llm(name, dtype, max_num_batched_tokens=64, max_num_seqs=2)
+    out2 = llm2.generate(prompts, sps, use_tqdm=False)
+    if dtype == "float32":
+        assert [o["token_ids"] for o in out2] == [o["token_ids"] for o in out]
+
+
+def test_running_out_of_pages_preempts_and_gives_the_same_tokens():
+    from mini_engine_b200 import SamplingParams
+    name = "A"
+    prompts = helpers.random_requests(ALL[name][0]["vocab_size"], (40, 40, 25), seed=4)
+    sp = SamplingParams(temperature=0, max_tokens=30, ignore_eos=True)
+    roomy = _llm(name, "float32", num_kvcache_blocks=64).generate(prompts, sp, use_tqdm=False)
+    tight = _llm(name, "float32", num_kvcache_blocks=7, max_num_batched_tokens=128)
+    out = tight.generate(prompts, sp, use_tqdm=False)
+    assert tight.scheduler.num_preemptions > 0
+    assert [o["token_ids"] for o in out] == [o["token_ids"] for o in roomy]
+    tight.cache.check([])
+    assert tight.cache.num_free_pages == [7]
+
+
+def test_request_too_large_is_refused():
+    from mini_engine_b200 import SamplingParams
+    llm = _llm("A", "float32", num_kvcache_blocks=4)
+    with pytest.raises(ValueError):
+        llm.generate([list(range(100))], SamplingParams(max_tokens=10), use_tqdm=False)
+    with pytest.raises(ValueError, match="max_model_len"):
+        llm.generate([list(range(250))], SamplingParams(max_tokens=10), use_tqdm=False)
+
+
+def test_token_outside_the_vocabulary_is_reported():
+    from mini_engine_b200 import SamplingParams
+    llm = _llm("A", "float32")
+    with pytest.raises(RuntimeError, match="vocabulary"):
+        llm.generate([[1, 2, 100000]], SamplingParams(temperature=0, max_tokens=2), use_tqdm=False)
+
+
+def test_add_request_and_step_surface():
+    from mini_engine_b200 import SamplingParams
+    llm = _llm("A", "float32")
+    a = llm.add_request([1, 2, 3, 4, 5], SamplingParams(temperature=0, max_tokens=2))
+    b = llm.add_request([9, 8, 7], SamplingParams(temperature=0, max_tokens=3), priority=1)
+    finished, n_prefill, n_decode, emitted = llm.step()
+    assert (n_prefill, n_decode, finished, sorted(emitted)) == (8, 0, [], [a, b])
+    finished, n_prefill, n_decode, emitted = llm.step()
+    assert n_decode == 2 and [f[0] for f in finished] == [a] and len(finished[0][1]) == 2
+    while not llm.is_finished():
+        finished, *_ = llm.step()
+    assert finished[0][0] == b and len(finished[0][1]) == 3
+    with pytest.raises(ValueError, match="tokenizer"):
+        llm.add_request("some text", SamplingParams())

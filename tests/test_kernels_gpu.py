@@ -1,0 +1,318 @@
+"""Each CUDA kernel alone against its plain twin (tests/plain_ops.py), at many sizes."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mini_engine_b200 import ops as o
+    o.require_extension()
+    return o
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(a, b, dtype, scale=1.0):
+    tol = {torch.float32: 2e-5, torch.bfloat16: 1.6e-2}[dtype] * scale
+    d = (a.float() - b.float()).abs().max().item()
+    assert d <= tol, f"max abs diff {d:.3e} > {tol:.3e}"
+
+
+# ---- embedding ------------------------------------------------------------------------------
+@pytest.mark.parametrize("wd", ["float32", "bfloat16"])
+def test_embed(ops, wd):
+    V, H, T = 333, 96, 37
+    table = rnd(V, H, dtype=DT[wd])
+    ids = torch.randint(0, V, (T,), dtype=torch.int32, device=DEV)
+    out = torch.full((T, H), float("nan"), device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.embed(ids, table, out, err)
+    assert torch.equal(out, table[ids.long()].float()) and err.tolist() == [0, 0, 0, 0]
+    ids[5] = V
+    ops.embed(ids, table, out, err)
+    assert err[0].item() == 1 and torch.all(out[5] == 0)
+
+
+# ---- residual add + RMSNorm --------------------------------------------------------------------
+@pytest.mark.parametrize("H", [64, 96, 1000, 4104])
+@pytest.mark.parametrize("od", ["float32", "bfloat16"])
+def test_add_rmsnorm(ops, H, od):
+    T = 19
+    for delta_dt in (None, od, "float32"):
+        res = rnd(T, H, seed=1)
+        delta = None if delta_dt is None else rnd(T, H, dtype=DT[delta_dt], seed=2)
+        w = 1 + 0.1 * rnd(H, seed=3)
+        out, ref_out = torch.empty(T, H, dtype=DT[od], device=DEV), torch.empty(T, H, dtype=DT[od], device=DEV)
+        ref_res = res.clone()
+        plain_ops.add_rmsnorm(ref_res, delta, w, 1e-5, ref_out)
+        ops.add_rmsnorm(res, delta, w, 1e-5, out)
+        assert torch.allclose(res, ref_res, atol=1e-6)
+        close(out, ref_out, DT[od], scale=4)
+    # gathered rows: the residual is read, not written
+    res, delta = rnd(T, H, seed=4), rnd(T, H, dtype=DT[od], seed=5)
+    rows = torch.tensor([3, 0, 18, 3], dtype=torch.int32, device=DEV)
+    keep = res.clone()
+    out, ref_out = torch.empty(4, H, dtype=DT[od], device=DEV), torch.empty(4, H, dtype=DT[od], device=DEV)
+    ops.add_rmsnorm(res, delta, w, 1e-6, out, rows=rows)
+    plain_ops.add_rmsnorm(keep.clone(), delta, w, 1e-6, ref_out, rows=rows)
+    assert torch.equal(res, keep)
+    close(out, ref_out, DT[od], scale=4)
+
+
+def test_silu_mul(ops):
+    for dt in (torch.float32, torch.bfloat16):
+        x = rnd(23, 2 * 200, dtype=dt, scale=2.0)
+        out, ref = torch.empty(23, 200, dtype=dt, device=DEV), torch.empty(23, 200, dtype=dt, device=DEV)
+        ops.silu_mul(x, out)
+        plain_ops.silu_mul(x, ref)
+        close(out, ref, dt, scale=4)
+
+
+# ---- matrix products ------------------------------------------------------------------------
+@pytest.mark.parametrize("M, N, K", [(1, 96, 64), (37, 224, 96), (130, 333, 72), (5, 1000, 513), (64, 64, 16), (8, 4096, 1024)])
+@pytest.mark.parametrize("kinds", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
+                                   ("bfloat16", "bfloat16", "float32"), ("bfloat16", "float32", "bfloat16")])
+def test_linear(ops, M, N, K, kinds):
+    xd, wd, od = (DT[k] for k in kinds)
+    x, w = rnd(M, K, dtype=xd, seed=1), rnd(N, K, dtype=wd, seed=2, scale=K ** -0.5)
+    out, ref = torch.empty(M, N, dtype=od, device=DEV), torch.empty(M, N, dtype=od, device=DEV)
+    ops.linear(x, w, out)
+    plain_ops.linear(x, w, ref)
+    close(out, ref, od, scale=4)
+
+
+@pytest.mark.parametrize("M, I, K", [(1, 128, 64), (37, 224, 96), (70, 200, 72), (8, 3072, 1024)])
+@pytest.mark.parametrize("dt", ["float32", "bfloat16"])
+def test_linear_silu_mul(ops, M, I, K, dt):
+    x, w = rnd(M, K, dtype=DT[dt], seed=1), rnd(2 * I, K, dtype=DT[dt], seed=2, scale=K ** -0.5)
+    out, ref = torch.empty(M, I, dtype=DT[dt], device=DEV), torch.empty(M, I, dtype=DT[dt], device=DEV)
+    ops.linear(x, w, out, epilogue="silu_mul")
+    plain_ops.linear(x, w, ref, epilogue="silu_mul")
+    close(out, ref, DT[dt], scale=4)
+
+
+def test_linear_rows_do_not_depend_on_the_batch(ops):
+    x, w = rnd(70, 96, seed=1), rnd(224, 96, seed=2)
+    full, one = torch.empty(70, 224, device=DEV), torch.empty(1, 224, device=DEV)
+    ops.linear(x, w, full)
+    ops.linear(x[41:42], w, one)
+    assert torch.equal(full[41:42], one)
+
+
+# ---- q/k norm + rotary + cache write --------------------------------------------------------------
+@pytest.mark.parametrize("nh, nkv, hd", [(4, 2, 16), (8, 2, 32), (6, 3, 48), (16, 8, 128), (5, 5, 80), (2, 1, 256)])
+@pytest.mark.parametrize("dt", ["float32", "bfloat16"])
+@pytest.mark.parametrize("norm, rope", [(True, True), (False, True), (True, False)])
+def test_qk_norm_rope_kv_write(ops, nh, nkv, hd, dt, norm, rope):
+    T, page, pages = 29, 8, 9
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=DT[dt], seed=1)
+    qw = (1 + 0.1 * rnd(hd, seed=2)) if norm else None
+    kw = (1 + 0.1 * rnd(hd, seed=3)) if norm else None
+    pos = torch.randint(0, 200, (T,), dtype=torch.int32, device=DEV)
+    inv = 1.0 / (5000.0 ** (torch.arange(0, hd, 2).float() / hd))
+    fr = torch.outer(torch.arange(200).float(), inv)
+    cs = torch.cat((fr.cos(), fr.sin()), -1).to(DEV) if rope else None
+    slots = torch.randperm(pages * page)[:T].to(torch.int32).to(DEV)
+    slots[7] = -1
+    pool = torch.full((pages, 2, nkv, page, hd), float("nan"), dtype=DT[dt], device=DEV)
+    ref_qkv, ref_pool = qkv.clone(), pool.clone()
+    ops.qk_norm_rope_kv_write(qkv, nh, nkv, hd, qw, kw, 1e-5, cs, pos, slots, pool, page)
+    plain_ops.qk_norm_rope_kv_write(ref_qkv, nh, nkv, hd, qw, kw, 1e-5, cs, pos, slots, ref_pool, page)
+    close(qkv, ref_qkv, DT[dt], scale=4)
+    assert torch.equal(pool.isnan(), ref_pool.isnan())                  # exactly the given slots were written
+    close(pool.nan_to_num(0), ref_pool.nan_to_num(0), DT[dt], scale=4)
+    # v is copied bit for bit (csrc/kv_cache.cu in the reference is bit-exact too)
+    s = int(slots[0])
+    assert torch.equal(pool[s // page, 1, :, s % page].reshape(-1), qkv[0, (nh + nkv) * hd:])
+    # without a slot mapping nothing is written
+    pool2 = torch.zeros_like(pool)
+    ops.qk_norm_rope_kv_write(ref_qkv.clone(), nh, nkv, hd, qw, kw, 1e-5, cs, pos, None, pool2, page)
+    assert not pool2.any()
+
+
+def test_head_dim_is_checked(ops):
+    with pytest.raises(ValueError, match="head_dim"):
+        ops.check_attention_sizes(40, 4, 2)
+    with pytest.raises(ValueError, match="head_dim"):
+        ops.check_attention_sizes(272, 4, 2)
+    with pytest.raises(ValueError):
+        ops.check_attention_sizes(64, 6, 4)
+
+
+# ---- attention ------------------------------------------------------------------------------
+class Batch:
+    """Requests with cached context and new tokens, laid out in a scattered, NaN-filled pool."""
+
+    def __init__(self, ctx_lens, q_lens, nh, nkv, hd, page, dtype, seed=0, standout=None, window=None):
+        from mini_engine_b200.engine.step_context import AttnMeta
+        g = torch.Generator().manual_seed(seed)
+        B, T = len(ctx_lens), sum(q_lens)
+        order = sorted(range(B), key=lambda b: q_lens[b] != 1)            # single tokens first
+        ctx_lens, q_lens = [ctx_lens[b] for b in order], [q_lens[b] for b in order]
+        self.nh, self.nkv, self.hd, self.page = nh, nkv, hd, page
+        n_pages = sum((L + page - 1) // page for L in ctx_lens) + 3
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        self.pool = torch.full((n_pages, 2, nkv, page, hd), float("nan"), dtype=dtype)
+        width = max((L + page - 1) // page for L in ctx_lens) + 1
+        bt = torch.full((B, width), -1, dtype=torch.int32)
+        self.qkv = (torch.randn(T, (nh + 2 * nkv) * hd, generator=g)).to(dtype)
+        cu = [0]
+        for b, (L, n) in enumerate(zip(ctx_lens, q_lens)):
+            k = torch.randn(L, nkv, hd, generator=g) * 0.5
+            v = torch.randn(L, nkv, hd, generator=g)
+            if standout is not None:                                      # one key whose score stands out
+                jb, tb = standout(b, L, n)
+                if jb is not None:
+                    q = self.qkv[cu[-1] + tb].float().view(nh + 2 * nkv, hd)[:nh]
+                    for kh in range(nkv):
+                        qd = q[kh * (nh // nkv)]
+                        k[jb, kh] = 12.0 * qd / qd.norm() ** 2 * math.sqrt(hd)
+            for i in range((L + page - 1) // page):
+                p = perm.pop()
+                bt[b, i] = p
+                n_in = min(page, L - i * page)
+                if window is not None and (i + 1) * page <= L - n - window + 1:
+                    bt[b, i] = -1                                        # behind every window: given back
+                    continue
+                self.pool[p, 0, :, :n_in] = k[i * page:i * page + n_in].transpose(0, 1).to(dtype)
+                self.pool[p, 1, :, :n_in] = v[i * page:i * page + n_in].transpose(0, 1).to(dtype)
+            cu.append(cu[-1] + n)
+        D = sum(1 for n in q_lens if n == 1)
+        from mini_engine_b200 import ops as o
+        tiles = [(b, q0) for b in range(D, B) for q0 in range(0, q_lens[b], o.ATTN_TILE_Q)]
+        self.pool, self.qkv, self.bt = self.pool.to(DEV), self.qkv.to(DEV), bt.to(DEV)
+        self._ws = {}
+
+        def workspace(name, shape, dt):
+            key = (name, tuple(shape), dt)
+            if key not in self._ws:
+                self._ws[key] = torch.full(tuple(shape), float("nan"), dtype=dt, device=DEV)
+            return self._ws[key]
+        self.meta = AttnMeta(num_reqs=B, num_tokens=T, num_decodes=D,
+                             cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                             context_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
+                             tiles=torch.tensor(tiles or [(0, 0)], dtype=torch.int32, device=DEV), num_tiles=len(tiles),
+                             max_context_len=max(ctx_lens), workspace=workspace)
+        self.all_tiles = torch.tensor([(b, q0) for b in range(B) for q0 in range(0, q_lens[b], o.ATTN_TILE_Q)],
+                                      dtype=torch.int32, device=DEV)
+        self.q_lens, self.ctx_lens = q_lens, ctx_lens
+
+
+def run_attention(ops, bt: Batch, dtype, window, which="split"):
+    T = bt.qkv.shape[0]
+    out = torch.full((T, bt.nh * bt.hd), float("nan"), dtype=dtype, device=DEV)
+    ref = torch.empty_like(out)
+    scale = bt.hd ** -0.5
+    args = (bt.nh, bt.nkv, bt.hd, bt.pool, bt.page, bt.bt, bt.meta, scale, window)
+    if which == "split":
+        ops.paged_attention(bt.qkv, out, *args)
+    else:                                                                  # everything through the chunk kernel
+        ops.attention_chunks(bt.qkv, out, *args, tiles=bt.all_tiles, num_tiles=bt.all_tiles.shape[0])
+    plain_ops.paged_attention(bt.qkv, ref, *args)
+    assert not out.isnan().any(), "the kernel read a slot that no request owns (NaN-filled pool)"
+    return out, ref
+
+
+SHAPES = [(4, 2, 16, 16), (8, 2, 32, 8), (6, 3, 48, 16), (16, 8, 128, 16), (8, 1, 64, 32), (5, 5, 80, 4), (4, 2, 256, 16)]
+
+
+@pytest.mark.parametrize("nh, nkv, hd, page", SHAPES)
+@pytest.mark.parametrize("dt", ["float32", "bfloat16"])
+def test_attention_mixed_batch(ops, nh, nkv, hd, page, dt):
+    # portions of prompts (with and without earlier context), single tokens, lengths at tile and page edges
+    ctx = [1, 300, 257, 31, 33, 64, 150, 16, 512, 17]
+    ql = [1, 1, 1, 31, 17, 64, 2, 16, 1, 1]
+    b = Batch(ctx, ql, nh, nkv, hd, page, DT[dt], seed=hd)
+    for which in ("split", "chunks"):
+        out, ref = run_attention(ops, b, DT[dt], None, which)
+        close(out, ref, DT[dt])
+
+
+@pytest.mark.parametrize("dt", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["split", "chunks"])
+def test_attention_finds_one_far_key_among_hundreds(ops, dt, which):
+    # one key far back gets a score that stands out: the output must be (nearly) its value
+    ctx, ql = [700, 1000, 520, 300], [1, 1, 40, 16]
+    far = {0: 3, 1: 511, 2: 256, 3: 15}                                  # page edges, partition edges, the start
+    b = Batch(ctx, ql, 8, 2, 64, 16, DT[dt], seed=1, standout=lambda r, L, n: (far[r], n - 1))
+    out, ref = run_attention(ops, b, DT[dt], None, which)
+    close(out, ref, DT[dt])
+    cu = b.meta.cu_seqlens.tolist()
+    for r in range(4):                                                     # and it really dominates
+        row = cu[r + 1] - 1
+        j = far[r]
+        v = b.pool[b.bt[r, j // 16].long(), 1, 0, j % 16].float()
+        assert (ref[row, :64].float() - v).abs().max() < 0.05
+
+
+@pytest.mark.parametrize("dt", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["split", "chunks"])
+@pytest.mark.parametrize("edge", [0, 1])
+def test_attention_window_edge(ops, dt, which, edge):
+    # the standout key sits exactly at the window's edge (edge=0: last key still seen, edge=1: first not seen)
+    w = 40
+    ctx, ql = [300, 130, 97], [1, 30, 1]
+
+    def stand(r, L, n):
+        p = L - 1                                                          # position of the request's last query
+        return (p - w + 1 - edge, n - 1)
+    b = Batch(ctx, ql, 4, 2, 32, 8, DT[dt], seed=2, standout=stand, window=w)
+    out, ref = run_attention(ops, b, DT[dt], w, which)
+    close(out, ref, DT[dt])
+    cu = b.meta.cu_seqlens.tolist()
+    for r in range(3):
+        row = cu[r + 1] - 1
+        j = b.ctx_lens[r] - 1 - w + 1 - edge
+        page = b.bt[r, j // 8].long()
+        if edge == 0:
+            assert (ref[row, :32].float() - b.pool[page, 1, 0, j % 8].float()).abs().max() < 0.05
+        # edge == 1: the key is outside; its page may even be given back (NaN there would show)
+
+
+@pytest.mark.parametrize("dt", ["float32", "bfloat16"])
+def test_attention_does_not_depend_on_the_batch(ops, dt):
+    # the same request alone and among others: bit-identical rows
+    ctx, ql = [300, 77, 150, 90], [1, 20, 1, 90]
+    many = Batch(ctx, ql, 8, 2, 64, 16, DT[dt], seed=3)
+    out_many, _ = run_attention(ops, many, DT[dt], None)
+    alone = Batch(ctx[:1], ql[:1], 8, 2, 64, 16, DT[dt], seed=3)
+    out_alone, _ = run_attention(ops, alone, DT[dt], None)
+    assert torch.equal(many.qkv[0], alone.qkv[0])
+    assert torch.equal(out_many[0], out_alone[0])
+
+
+# ---- sampling -------------------------------------------------------------------------------
+def test_sample(ops):
+    S, V = 6, 5003
+    logits = rnd(S, V, seed=9, scale=2.0)
+    temps = torch.tensor([0.0, 0.7, 1.0, 0.0, 1.5, 0.3], device=DEV)
+    seeds = torch.tensor([1, 2, 3, 4, 5, 6], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([10, 11, 12, 13, 14, 2 ** 20], dtype=torch.int32, device=DEV)
+    out = torch.empty(S, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temps, seeds, pos, out)
+    got = out.tolist()
+    for r in range(S):
+        keys = plain_ops.sample_keys(logits[r], float(temps[r]), int(seeds[r]), int(pos[r]))
+        assert keys[got[r]] >= keys.max() - 1e-4, f"row {r}"
+        if float(temps[r]) == 0:
+            assert got[r] == int(np.argmax(keys))
+    # the draw does not depend on the row's place in the batch
+    out2 = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops.sample(logits[4:5], temps[4:5], seeds[4:5], pos[4:5], out2)
+    assert out2.item() == got[4]
+    # ties go to the lower index
+    flat = torch.zeros(2, 100, device=DEV)
+    ops.sample(flat, torch.zeros(2, device=DEV), seeds[:2], pos[:2], out[:2])
+    assert out[:2].tolist() == [0, 0]
