@@ -12,12 +12,10 @@ from dataclasses import fields
 from time import perf_counter
 from typing import Optional, Sequence as Seq
 
-import numpy as np
 import torch
 
 from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler
 from .model_runner import ModelRunner, StepItem
 from .scheduler import Scheduler
 from .sequence import Sequence
@@ -47,9 +45,6 @@ class LLMEngine:
             config.eos = self.tokenizer.eos_token_id        # engine/llm_engine.py:19
         self.cache = self.model_runner.make_cache_manager(config.enable_prefix_caching)
         self.scheduler = Scheduler(config, self.cache)
-        self.sampler = Sampler()
-        self._pin = torch.empty(3 * config.max_num_seqs, dtype=torch.int32, pin_memory=True)
-        self._dev = torch.empty(3 * config.max_num_seqs, dtype=torch.int32, device=self.model_runner.device)
         self._tokens_dev = torch.empty(config.max_num_seqs + 4, dtype=torch.int32, device=self.model_runner.device)
         self._tokens_pin = torch.empty(config.max_num_seqs + 4, dtype=torch.int32, pin_memory=True)
         self.h2d_bytes = 0
@@ -80,25 +75,20 @@ class LLMEngine:
         for s in seqs:
             a, n = s.num_computed_tokens, s.num_scheduled_tokens
             wants = s.samples_this_step
-            items.append(StepItem(s, s.token_ids[a:a + n], a, [n - 1] if wants else []))
+            items.append(StepItem(s, s.token_ids[a:a + n], a, [n - 1] if wants else [],
+                                  (s.sampling_params.temperature, self._seed_of(s)) if wants else None))
             if wants:
                 samplers.append(s)
-        logits = self.model_runner.step(items)
+        # One copy to the device (the step's metadata, sampling options included), the step with the
+        # draw on the device, one copy back (the drawn ids and the kernels' error flags).
+        result = self.model_runner.step(items, sample=True)
         self.h2d_bytes += self.model_runner.last_h2d_bytes
         sampled = {}
         if samplers:
             S = len(samplers)
-            host = self._pin.numpy()
-            host[0:S] = np.asarray([s.sampling_params.temperature for s in samplers], dtype=np.float32).view(np.int32)
-            host[S:2 * S] = [self._seed_of(s) for s in samplers]
-            host[2 * S:3 * S] = [s.num_tokens for s in samplers]     # position of the token being drawn
-            self._dev[:3 * S].copy_(self._pin[:3 * S], non_blocking=True)
-            tokens = self._tokens_dev[:S]
-            self.sampler(logits, self._dev[0:S].view(torch.float32), self._dev[S:2 * S], self._dev[2 * S:3 * S], tokens)
-            # One device-to-host copy per step: the sampled ids and the kernels' error flags.
+            self._tokens_dev[:S].copy_(result.tokens)
             self._tokens_dev[S:S + 4].copy_(self.model_runner.error_flag)
             self._tokens_pin[:S + 4].copy_(self._tokens_dev[:S + 4])
-            self.h2d_bytes += 3 * S * 4
             self.d2h_bytes += (S + 4) * 4
             got = self._tokens_pin[:S + 4].tolist()
             if any(got[S:]):

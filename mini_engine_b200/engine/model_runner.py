@@ -35,6 +35,26 @@ class StepItem:
     tokens: Sequence[int]          # the request's next tokens
     start: int                     # position of tokens[0] in the request
     want: Sequence[int] = ()       # places among ``tokens`` whose logits are wanted
+    sampling: Optional[tuple[float, int]] = None   # (temperature, seed) when tokens are to be drawn
+
+
+@dataclass
+class StepResult:
+    logits: Optional[torch.Tensor]     # [wanted, vocab] float32, in the order of the items and their ``want``
+    tokens: Optional[torch.Tensor]     # [wanted] int32, drawn on the device when the step was asked to sample
+
+
+class _DecodeGraph:
+    """A captured decode step for a fixed number of requests: its own context, metadata and buffers."""
+
+    def __init__(self, runner, bucket: int):
+        self.bucket = bucket
+        self.ctx = StepContext(runner)
+        self.meta_dev: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.tokens: Optional[torch.Tensor] = None
+        self.launches = 0
 
 
 def plan_cache_groups(model: DecoderModel) -> tuple[list[GroupSpec], dict[int, tuple[int, int]], dict[int, StateNeed]]:
@@ -87,10 +107,17 @@ class ModelRunner:
                                                 device=self.device)
                               for slot, need in self.state_needs.items()}
         self.ctx = StepContext(self)
-        self._staging: Optional[torch.Tensor] = None     # pinned host int32
+        self._pins: list[Optional[torch.Tensor]] = [None, None]     # pinned host int32, used in turn
+        self._pin_events: list[Any] = [None, None]
+        self._pin_turn = 0
         self._staging_dev: Optional[torch.Tensor] = None
-        self.use_cuda_graphs = use_cuda_graphs
-        self._graphs: dict[int, Any] = {}
+        # A decode step is replayed from a graph only if every part of the model allows it.
+        self.use_cuda_graphs = (use_cuda_graphs and self.device.type == "cuda"
+                                and all(part.capturable for _, part in self.model.walk()))
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256) if b <= max_num_seqs]
+        self.sample_tokens = torch.empty(max(max_num_seqs, 1), dtype=torch.int32, device=self.device)
+        self.graph_launches = 0          # kernels replayed from graphs (they bypass ops.launches)
         self.last_h2d_bytes = 0
 
     # ---- sizes -----------------------------------------------------------------------
@@ -134,15 +161,21 @@ class ModelRunner:
                             has_state=bool(self.state_needs))
 
     # ---- the step --------------------------------------------------------------------
-    def _stage(self, n_ints: int) -> tuple[np.ndarray, torch.Tensor]:
-        if self._staging is None or self._staging.numel() < n_ints:
-            cap = max(n_ints * 2, 1 << 16)
-            self._staging = torch.empty(cap, dtype=torch.int32, pin_memory=True)
-            self._staging_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
-        return self._staging.numpy(), self._staging_dev
+    def _stage(self, n_ints: int, dev: Optional[torch.Tensor]) -> tuple[torch.Tensor, torch.Tensor]:
+        """A pinned host buffer whose last copy has finished, and the device buffer it goes to."""
+        k = self._pin_turn = 1 - self._pin_turn
+        if self._pin_events[k] is not None:
+            self._pin_events[k].synchronize()
+        if self._pins[k] is None or self._pins[k].numel() < n_ints:
+            self._pins[k] = torch.empty(max(n_ints * 2, 1 << 16), dtype=torch.int32, pin_memory=True)
+        if dev is None:
+            if self._staging_dev is None or self._staging_dev.numel() < n_ints:
+                self._staging_dev = torch.empty(max(n_ints * 2, 1 << 16), dtype=torch.int32, device=self.device)
+            dev = self._staging_dev
+        return self._pins[k], dev
 
     def build_batch(self, items: Sequence[StepItem], ctx: StepContext, *, pad_reqs: int = 0,
-                    table_width: int = 0) -> tuple[torch.Tensor, list[int]]:
+                    table_width: int = 0, dev: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, list[int]]:
         """Lay the step's metadata out in pinned memory, copy it once, fill ``ctx``.
 
         Requests that bring one token come first (as in engine/model_runner.py:88-89).
@@ -181,6 +214,9 @@ class ModelRunner:
                 if not 0 <= w < len(it.tokens):
                     raise ValueError(f"wanted place {w} is outside the item's {len(it.tokens)} tokens")
                 want_rows.append(offsets[i] + w)
+        S_real = len(want_rows)
+        if pad_reqs:                                  # fixed shape: as many rows as requests
+            want_rows += [0] * (B - S_real)
         S = len(want_rows)
         BQ = ops.ATTN_TILE_Q
         tiles = [(b, q0) for b in range(D, B_real) for q0 in range(0, lens[b], BQ)]
@@ -189,9 +225,13 @@ class ModelRunner:
         def al(n):                       # keep every array 16-byte aligned on the device
             return (n + 3) & ~3
         sizes = dict(tok=al(T), pos=al(T), req=al(T), cu=al(B + 1), ctxlen=al(B), slot=al(B),
-                     rows=al(max(S, 1)), tiles=al(max(2 * n_tiles, 1)))
+                     rows=al(max(S, 1)), temp=al(max(S, 1)), seed=al(max(S, 1)), spos=al(max(S, 1)),
+                     tiles=al(max(2 * n_tiles, 1)))
         total = sum(sizes.values()) + sum(al(T) + al(B * widths[g]) for g in range(G))
-        host, dev = self._stage(total)
+        pin, dev = self._stage(total, dev)
+        if dev.numel() < total:
+            raise RuntimeError("a captured step's metadata outgrew its buffer")
+        host = pin.numpy()
         cur = 0
 
         def take(n):
@@ -200,7 +240,8 @@ class ModelRunner:
             return a
         o_tok, o_pos, o_req = take(sizes["tok"]), take(sizes["pos"]), take(sizes["req"])
         o_cu, o_ctx, o_slot = take(sizes["cu"]), take(sizes["ctxlen"]), take(sizes["slot"])
-        o_rows, o_tiles = take(sizes["rows"]), take(sizes["tiles"])
+        o_rows, o_temp, o_seed, o_spos = (take(sizes[k]) for k in ("rows", "temp", "seed", "spos"))
+        o_tiles = take(sizes["tiles"])
         o_sm = [take(al(T)) for _ in range(G)]
         o_bt = [take(al(B * widths[g])) for g in range(G)]
 
@@ -223,6 +264,17 @@ class ModelRunner:
         host[o_slot:o_slot + B] = [items[i].holder.state_slot for i in order] + [-1] * pad
         if S:
             host[o_rows:o_rows + S] = want_rows
+            temps, seeds, spos = [], [], []
+            for i, it in enumerate(items):
+                t_, s_ = it.sampling if it.sampling is not None else (0.0, 0)
+                for w in it.want:
+                    temps.append(t_)
+                    seeds.append(int(s_) & 0x7FFFFFFF)
+                    spos.append(it.start + w + 1)      # position of the token that is drawn
+            padn = S - S_real
+            host[o_temp:o_temp + S] = np.asarray(temps + [0.0] * padn, dtype=np.float32).view(np.int32)
+            host[o_seed:o_seed + S] = seeds + [0] * padn
+            host[o_spos:o_spos + S] = spos + [0] * padn
         if n_tiles:
             host[o_tiles:o_tiles + 2 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
         for g in range(G):
@@ -244,13 +296,22 @@ class ModelRunner:
                     raise ValueError("a new token would be written to a page that was given back")
                 sm[t:t + lens[k]] = pages * ps + pos % ps
                 t += lens[k]
-        dev[:total].copy_(self._staging[:total], non_blocking=True)
+        dev[:total].copy_(pin[:total], non_blocking=True)
+        ev = self._pin_events[self._pin_turn]
+        if ev is None and self.device.type == "cuda":
+            ev = self._pin_events[self._pin_turn] = torch.cuda.Event()
+        if ev is not None:
+            ev.record()
         self.last_h2d_bytes = total * 4
+        self.last_num_wanted = S_real
 
         ctx.positions = dev[o_pos:o_pos + T]
         ctx.token_req = dev[o_req:o_req + T]
         ctx.state_slots = dev[o_slot:o_slot + B]
         ctx.logits_rows = dev[o_rows:o_rows + S]
+        ctx.sample_temps = dev[o_temp:o_temp + S].view(torch.float32)
+        ctx.sample_seeds = dev[o_seed:o_seed + S]
+        ctx.sample_positions = dev[o_spos:o_spos + S]
         ctx._bt = [dev[o_bt[g]:o_bt[g] + B * widths[g]].view(B, widths[g]) for g in range(G)]
         ctx._sm = [dev[o_sm[g]:o_sm[g] + T] for g in range(G)]
         ctx.attn_meta = AttnMeta(
@@ -264,23 +325,64 @@ class ModelRunner:
                             holders=[items[i].holder for i in order])
         return dev[o_tok:o_tok + T], order
 
-    @torch.inference_mode()
-    def step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
-        """Run exactly the tokens of ``items`` as one batch against the cache.
-
-        Returns float32 logits ``[wanted, vocab]`` in the order of the items and of each item's
-        ``want`` (None when nothing is wanted).  The tensor is a work buffer: it is overwritten
-        by the next step."""
-        if not items:
-            return None
-        if len(items) > self.max_num_seqs:
-            raise ValueError(f"{len(items)} requests in one step, max_num_seqs is {self.max_num_seqs}")
-        ctx = self.ctx
-        token_ids, _ = self.build_batch(items, ctx)
+    def _forward(self, token_ids: torch.Tensor, ctx: StepContext, sample: bool):
         hidden = self.model.forward(token_ids, ctx)
         if ctx.logits_rows.numel() == 0:
-            return None
-        return self.model.compute_logits(hidden, ctx)
+            return None, None
+        logits = self.model.compute_logits(hidden, ctx)
+        tokens = None
+        if sample:
+            tokens = ctx.buffer("sampled_tokens", (logits.shape[0],), torch.int32)
+            ops.sample(logits, ctx.sample_temps, ctx.sample_seeds, ctx.sample_positions, tokens)
+        return logits, tokens
+
+    @torch.inference_mode()
+    def step(self, items: Sequence[StepItem], sample: bool = False) -> StepResult:
+        """Run exactly the tokens of ``items`` as one batch against the cache.
+
+        Returns the float32 logits ``[wanted, vocab]`` in the order of the items and of each item's
+        ``want`` and, with ``sample``, the tokens drawn from them on the device.  Both are work
+        buffers that the next step overwrites."""
+        if not items:
+            return StepResult(None, None)
+        if len(items) > self.max_num_seqs:
+            raise ValueError(f"{len(items)} requests in one step, max_num_seqs is {self.max_num_seqs}")
+        if self.use_cuda_graphs and all(len(it.tokens) == 1 for it in items):
+            bucket = next((b for b in self.graph_buckets if b >= len(items)), None)
+            if bucket is not None:
+                return self._step_graph(items, bucket, sample)
+        token_ids, _ = self.build_batch(items, self.ctx)
+        logits, tokens = self._forward(token_ids, self.ctx, sample)
+        return StepResult(logits, tokens)
+
+    def _step_graph(self, items: Sequence[StepItem], bucket: int, sample: bool) -> StepResult:
+        """Decode-only steps replay a graph captured for the bucket: metadata goes to fixed device
+        addresses, padding requests have no keys, write nowhere and their rows are ignored."""
+        g = self._graphs.get(bucket)
+        width = (self.max_model_len + self.page_size - 1) // self.page_size
+        if g is None:
+            g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+            n = 16 * bucket + 64 + sum(4 * bucket + bucket * width + 8 for _ in self.groups)
+            g.meta_dev = torch.zeros(n + 64, dtype=torch.int32, device=self.device)
+        token_ids, _ = self.build_batch(items, g.ctx, pad_reqs=bucket, table_width=width, dev=g.meta_dev)
+        if g.graph is None:
+            # Once eagerly (allocates the work buffers), then captured; both runs do the step's real work.
+            g.ctx.frozen = False
+            self._forward(token_ids, g.ctx, True)
+            torch.cuda.current_stream().synchronize()
+            g.ctx.frozen = True
+            before = ops.launches
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g.logits, g.tokens = self._forward(token_ids, g.ctx, True)
+            g.launches = ops.launches - before
+            g.graph = graph
+        g.graph.replay()
+        self.graph_launches += g.launches
+        n = self.last_num_wanted
+        if n == 0:
+            return StepResult(None, None)
+        return StepResult(g.logits[:n], g.tokens[:n] if sample else None)
 
     def check_device_errors(self) -> None:
         """Raise if a kernel flagged bad input (a token id outside the vocabulary)."""

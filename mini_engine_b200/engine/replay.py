@@ -51,7 +51,7 @@ class TraceReplayer:
             want = [int(w) for w in e.get("want", [])]
             n_want += len(want)
             items.append(StepItem(h, toks, h.num_computed_tokens, want))
-        logits = self.runner.step(items) if items else None
+        logits = self.runner.step(items).logits if items else None
         out = logits.cpu().numpy().astype("<f4", copy=True) if n_want else None
         for it in items:
             it.holder.num_computed_tokens += len(it.tokens)

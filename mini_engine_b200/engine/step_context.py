@@ -60,6 +60,9 @@ class StepContext:
         self.token_req: torch.Tensor = None
         self.state_slots: torch.Tensor = None
         self.logits_rows: torch.Tensor = None
+        self.sample_temps: torch.Tensor = None
+        self.sample_seeds: torch.Tensor = None
+        self.sample_positions: torch.Tensor = None
         self.attn_meta: AttnMeta = None
         self.host: HostMeta = None
         self._bt: list[torch.Tensor] = []

@@ -136,15 +136,42 @@ def silu_mul(x: torch.Tensor, out: torch.Tensor) -> None:
 
 
 # ---- matrix products ----------------------------------------------------------------------
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "none") -> None:
+library_calls = 0         # cuBLAS products issued through torch (not counted as this package's kernels)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "none",
+           workspace=None) -> None:
     """``out = x @ weight.T`` with float32 accumulation; ``epilogue="silu_mul"`` takes a weight of
-    rows gate | up and writes ``silu(x Wg^T) * (x Wu^T)``."""
+    rows gate | up and writes ``silu(x Wg^T) * (x Wu^T)``.
+
+    float32 operands (and any mix of dtypes) run the CUDA-core kernel of csrc/gemm_simt.cu: plain
+    FMA, no reduced-precision matrix mode.  bfloat16 x bfloat16 products go to cuBLAS, as the
+    reference's do through ``F.linear`` (layers/linear.py:26,45), with SiLU-and-multiply as a
+    kernel of ours behind it."""
+    global library_calls
     M, K = x.shape
     _need(weight.dim() == 2 and weight.shape[1] == K and weight.is_contiguous(), "linear: weight shape")
     _need(x.stride(1) == 1 and out.stride(1) == 1, "linear: rows must be contiguous")
     epi = {"none": 0, "silu_mul": 1}[epilogue]
     N = weight.shape[0] // 2 if epi else weight.shape[0]
     _need(tuple(out.shape) == (M, N), f"linear: output is {tuple(out.shape)}, expected {(M, N)}")
+    if M == 0:
+        return
+    if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.is_cuda:
+        if epi == 0 and out.dtype == torch.bfloat16:
+            torch.mm(x, weight.t(), out=out)
+            library_calls += 1
+            return
+        if epi == 0 and out.dtype == torch.float32:
+            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+            library_calls += 1
+            return
+        if epi == 1 and out.dtype == torch.bfloat16 and workspace is not None:
+            tmp = workspace("linear_gate_up", (M, 2 * N), torch.bfloat16)
+            torch.mm(x, weight.t(), out=tmp)
+            library_calls += 1
+            silu_mul(tmp, out)
+            return
     _call("me_gemm_simt", x.data_ptr(), _dt(x), x.stride(0), weight.data_ptr(), _dt(weight),
           out.data_ptr(), _dt(out), out.stride(0), M, N, K, epi, _stream())
 

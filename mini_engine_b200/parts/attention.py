@@ -23,6 +23,8 @@ from .registry import PartSpec, build_part, register_mixer
 
 
 class GQAAttention(Mixer):
+    capturable = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm_eps: Optional[float], position_encoding: Optional[PartSpec | object],
                  window: Optional[int] = None, scale: Optional[float] = None):

@@ -57,7 +57,14 @@ class StateNeed:
 
 
 class Part:
-    """Base of all parts.  ``params`` is filled by the weight loader."""
+    """Base of all parts.  ``params`` is filled by the weight loader.
+
+    ``capturable`` says that ``forward`` only launches kernels that read the step's shape from
+    device memory, so a decode step may be recorded once in a CUDA graph and replayed.  A part
+    that decides in Python on the step's host-side numbers leaves it False (the default), and a
+    model with such a part runs every step eagerly."""
+
+    capturable = False
 
     def __init__(self):
         self.params: dict[str, torch.Tensor] = {}

@@ -26,6 +26,8 @@ class BlockSpec:
 
 
 class PreNormBlock(Part):
+    capturable = True
+
     def __init__(self, spec: BlockSpec, shared: Optional[dict] = None):
         super().__init__()
         self.spec = spec

@@ -13,6 +13,8 @@ from .base import ParamDecl, Part
 
 
 class TokenEmbedding(Part):
+    capturable = True
+
     def __init__(self, vocab_size: int, hidden_size: int):
         super().__init__()
         self.vocab_size = vocab_size
@@ -28,6 +30,8 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    capturable = True
+
     def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None):
         super().__init__()
         self.vocab_size = vocab_size
@@ -39,5 +43,5 @@ class LMHead(Part):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         out = ctx.buffer("logits", (x.shape[0], self.vocab_size), torch.float32)
-        ops.linear(x, self.p("weight"), out)
+        ops.linear(x, self.p("weight"), out, workspace=ctx.buffer)
         return out

@@ -15,6 +15,9 @@ from .base import DiskSource, ParamDecl, Part
 class Linear(Part):
     """``pieces``: (disk name relative to the owner, rows) for every packed piece."""
 
+    capturable = True
+
+
     def __init__(self, in_features: int, pieces: Sequence[tuple[str, int]], name: str = "weight"):
         super().__init__()
         self.in_features = in_features
@@ -37,5 +40,5 @@ class Linear(Part):
                 epilogue: str = "none") -> torch.Tensor:
         n_out = self.out_features // 2 if epilogue == "silu_mul" else self.out_features
         out = ctx.buffer(out_name, (x.shape[0], n_out), out_dtype or ctx.act_dtype)
-        ops.linear(x, self.weight, out, epilogue=epilogue)
+        ops.linear(x, self.weight, out, epilogue=epilogue, workspace=ctx.buffer)
         return out

@@ -12,6 +12,8 @@ from .registry import register_feed_forward
 
 
 class SwiGLU(FeedForward):
+    capturable = True
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         super().__init__()
         self.hidden_size = hidden_size

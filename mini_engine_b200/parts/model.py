@@ -45,6 +45,8 @@ class ModelPlan:
 
 
 class DecoderModel(Part):
+    capturable = True
+
     def __init__(self, plan: ModelPlan):
         super().__init__()
         self.plan = plan

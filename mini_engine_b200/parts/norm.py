@@ -18,6 +18,8 @@ from .registry import register_norm
 
 
 class RMSNorm(Norm):
+    capturable = True
+
     def __init__(self, size: int, eps: float):
         super().__init__()
         self.size = size

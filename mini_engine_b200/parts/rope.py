@@ -16,6 +16,8 @@ from .registry import register_position_encoding
 
 
 class RotaryEmbedding(PositionEncoding):
+    capturable = True
+
     def __init__(self, rotary_dim: int, max_position: int, theta: float):
         super().__init__()
         if rotary_dim % 2:

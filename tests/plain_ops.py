@@ -48,7 +48,7 @@ def silu_mul(x, out):
     out.copy_((torch.nn.functional.silu(g) * u).to(out.dtype))
 
 
-def linear(x, weight, out, epilogue="none"):
+def linear(x, weight, out, epilogue="none", workspace=None):
     # layers/linear.py:26,45 (F.linear), float32 accumulate
     y = x.float() @ weight.float().T
     if epilogue == "silu_mul":

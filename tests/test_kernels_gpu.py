@@ -283,14 +283,24 @@ def test_attention_window_edge(ops, dt, which, edge):
 
 @pytest.mark.parametrize("dt", ["float32", "bfloat16"])
 def test_attention_does_not_depend_on_the_batch(ops, dt):
-    # the same request alone and among others: bit-identical rows
+    # the same requests alone and among others (same pages, same tokens): bit-identical rows
+    from mini_engine_b200.engine.step_context import AttnMeta
     ctx, ql = [300, 77, 150, 90], [1, 20, 1, 90]
-    many = Batch(ctx, ql, 8, 2, 64, 16, DT[dt], seed=3)
+    many = Batch(ctx, ql, 8, 2, 64, 16, DT[dt], seed=3)                   # batch order: 300/1, 150/1, 77/20, 90/90
     out_many, _ = run_attention(ops, many, DT[dt], None)
-    alone = Batch(ctx[:1], ql[:1], 8, 2, 64, 16, DT[dt], seed=3)
-    out_alone, _ = run_attention(ops, alone, DT[dt], None)
-    assert torch.equal(many.qkv[0], alone.qkv[0])
-    assert torch.equal(out_many[0], out_alone[0])
+    cu = many.meta.cu_seqlens.tolist()
+    for b in (0, 2, 3):
+        n, L = many.q_lens[b], many.ctx_lens[b]
+        tiles = [(0, q0) for q0 in range(0, n, ops.ATTN_TILE_Q)] if n > 1 else []
+        meta = AttnMeta(num_reqs=1, num_tokens=n, num_decodes=1 if n == 1 else 0,
+                        cu_seqlens=torch.tensor([0, n], dtype=torch.int32, device=DEV),
+                        context_lens=torch.tensor([L], dtype=torch.int32, device=DEV),
+                        tiles=torch.tensor(tiles or [(0, 0)], dtype=torch.int32, device=DEV), num_tiles=len(tiles),
+                        max_context_len=L, workspace=many.meta.workspace)
+        qkv = many.qkv[cu[b]:cu[b + 1]].clone()
+        out = torch.full((n, 8 * 64), float("nan"), dtype=DT[dt], device=DEV)
+        ops.paged_attention(qkv, out, 8, 2, 64, many.pool, 16, many.bt[b:b + 1].clone(), meta, 64 ** -0.5, None)
+        assert torch.equal(out, out_many[cu[b]:cu[b + 1]]), f"request {b}"
 
 
 # ---- sampling -------------------------------------------------------------------------------
