@@ -55,6 +55,9 @@ def parse_args():
     p.add_argument("--context", type=int, default=4096)
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
     p.add_argument("--dtype", default="bfloat16")
+    p.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                   help="run one part only (small runs for profilers); the JSON line then holds that part")
+    p.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
     p.add_argument("--seed", type=int, default=0)
     # the reference's own options (its bench.py:8-19), used by --mode offline
     p.add_argument("--model", default="", help="model folder; empty: random weights of the 0.6B shape")
@@ -275,20 +278,32 @@ def run_step_mode(args) -> int:
     itemsize = 2 if args.dtype in ("bfloat16", "bf16") else 4
     pages = (max(64, args.batch) * (args.prompt_len + args.steps + args.warmup + 64) + 4096) // 16 + 64
     llm = LLM(folder, dtype=args.dtype, kvcache_block_size=16, num_kvcache_blocks=pages, max_num_seqs=max(64, args.batch),
-              max_num_batched_tokens=2048, max_model_len=args.context, enable_prefix_caching=False, seed=args.seed)
+              max_num_batched_tokens=2048, max_model_len=args.context, enable_prefix_caching=False, seed=args.seed,
+              use_cuda_graphs=not args.no_graphs)
     runner, cache = llm.model_runner, llm.cache
     vocab = cfg["vocab_size"]
     prompts = random_prompts(max(64, args.batch), args.prompt_len, vocab, args.seed + 1)
 
+    T = 2048
+    if args.only == "prefill":
+        ms_prefill = prefill_on_device(runner, cache, random_prompts(1, T, vocab, args.seed + 2)[0], reps=args.steps, warmup=args.warmup)
+        print(json.dumps({"only": "prefill", "tokens": T, "ms": round(ms_prefill, 4), "value": round(T * 1000.0 / ms_prefill, 1),
+                          "frac": round(prefill_flops(cfg, layers, T) / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}))
+        return 0
     with ClockSampler() as clocks:
         ms_step, launches, mean_ctx = decode_on_device(runner, cache, prompts[:args.batch], args.steps, args.warmup)
+    if args.only == "decode":
+        b = weight_bytes_per_step(cfg, layers, itemsize) + args.batch * mean_ctx * kv_bytes_per_token(cfg, layers, itemsize)
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms_step, 4),
+                          "value": round(args.batch * 1000.0 / ms_step, 1), "gpu_launches": int(launches),
+                          "hbm_frac": round(b / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}))
+        return 0
     value = args.batch * 1000.0 / ms_step
     points = {}
     for b, k in ((1, max(20, args.steps // 2)), (64, max(20, args.steps // 4))):
         ms_b, _, _ = decode_on_device(runner, cache, prompts[:b], k, max(3, args.warmup))
         points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
     e2e_value, h2d, d2h = decode_e2e(llm, prompts[:args.batch], args.steps, max(3, args.warmup))
-    T = 2048
     ms_prefill = prefill_on_device(runner, cache, random_prompts(1, T, vocab, args.seed + 2)[0], reps=5, warmup=3)
     flops = prefill_flops(cfg, layers, T)
     bytes_step = weight_bytes_per_step(cfg, layers, itemsize) + args.batch * mean_ctx * kv_bytes_per_token(cfg, layers, itemsize)

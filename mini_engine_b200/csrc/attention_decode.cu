@@ -1,6 +1,6 @@
 // Paged attention for requests that bring one token: split over the keys, then merged.
 //
-// Reference (csrc/paged_decode.cu:247-334): the context is cut into partitions of 256 keys at
+// Reference (csrc/paged_decode.cu:247-334): the context is cut into partitions of 256 keys (128 here) at
 // fixed absolute positions; a block handles one request, one key/value head and one
 // partition, all query heads of the group sharing every K/V load; it writes an un-normalised
 // output with its maximum and exponential sum, and a second kernel merges the partitions
@@ -12,8 +12,9 @@
 // only on the request's own keys.  Any head size that is a multiple of 8 up to 256, any
 // group size, any page size, optional window (keys j > position - window).
 #include "common.cuh"
+#include "mma_prims.cuh"
 
-constexpr int DEC_PART = 256, DEC_THREADS = 128, DEC_LANES = 8, DEC_GROUPS = DEC_THREADS / DEC_LANES;
+constexpr int DEC_PART = 128, DEC_THREADS = 128, DEC_LANES = 8, DEC_GROUPS = DEC_THREADS / DEC_LANES;
 
 template <typename T> struct Vec8;
 template <> struct Vec8<bf16> {
@@ -169,6 +170,417 @@ decode_partition_kernel(const T* __restrict__ qkv, int64_t q_row_stride, const T
   }
 }
 
+// ---- the same partition step with the keys and values brought in by bulk copies ----------------
+// A page of one key/value head is one contiguous piece of memory ([page][k|v][kv_head][offset][head_dim]),
+// so one thread issues a cp.async.bulk per page for K and for V into shared memory, all of the
+// partition's copies at once (two stages of 64 keys, an mbarrier each), and the block computes from
+// shared memory as the stages land.  bfloat16, head_dim <= 128, page sizes 8, 16, 32, 64.
+constexpr int DEC_STAGE = 64, DEC_STAGES = DEC_PART / DEC_STAGE;
+constexpr unsigned DEC_WAIT_LIMIT = 1u << 22;      // polls of an mbarrier before the kernel gives up
+
+__device__ __forceinline__ uint32_t dec_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t phase) {
+  for (unsigned i = 0; i < DEC_WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(bar), "r"(phase) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+template <int GT, int CH>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_partition_tma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, const bf16* __restrict__ pool,
+                            const int* __restrict__ block_tables, int bt_stride,
+                            const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
+                            int nh, int nkv, int hd, int page_size, float scale, int window,
+                            float* __restrict__ tmp_out, float* __restrict__ tmp_m,
+                            float* __restrict__ tmp_l, int max_parts, int* __restrict__ err) {
+  extern __shared__ __align__(128) unsigned char dec_smem[];
+  __shared__ __align__(8) unsigned long long bars[DEC_STAGES];
+  const int G = nh / nkv, head_tiles = (G + GT - 1) / GT;
+  const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * GT;
+  const int z = blockIdx.z;
+  const int L = context_lens[b];
+  const int tid = threadIdx.x, kg = tid / DEC_LANES, lg = tid % DEC_LANES;
+  const int n_g = min(GT, G - g0);
+  const int lo_w = window > 0 ? max(0, L - window) : 0;
+  const int part_lo = z * DEC_PART, part_hi = min(L, part_lo + DEC_PART);
+  const int64_t slot0 = ((int64_t)b * nh + kvh * G + g0) * max_parts + z;
+  if (part_hi <= part_lo || part_hi <= lo_w) {
+    if (part_lo < L || z == 0)
+      for (int g = tid; g < n_g; g += DEC_THREADS) {
+        tmp_m[slot0 + (int64_t)g * max_parts] = -INFINITY;
+        tmp_l[slot0 + (int64_t)g * max_parts] = 0.f;
+      }
+    return;
+  }
+  bf16* k_s = reinterpret_cast<bf16*>(dec_smem);                  // [DEC_PART][hd]
+  bf16* v_s = k_s + DEC_PART * hd;                                // [DEC_PART][hd]
+  float* q_s = reinterpret_cast<float*>(v_s + DEC_PART * hd);     // [GT][hd], scaled
+  float* s_m = q_s + GT * hd;
+  float* s_l = s_m + DEC_GROUPS * GT;
+  float* s_acc = s_l + DEC_GROUPS * GT;                           // [DEC_GROUPS][GT][hd]
+  const int* bt = block_tables + (int64_t)b * bt_stride;
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(dec_smem_u32(&bars[s])));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    const unsigned page_bytes = (unsigned)(page_size * hd * sizeof(bf16));
+    const int64_t v_off = (int64_t)nkv * page_size * hd;
+    const int pages_per_stage = DEC_STAGE / page_size;
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES; ++s) {
+      const uint32_t bar = dec_smem_u32(&bars[s]);
+      const int key0 = part_lo + s * DEC_STAGE;
+      unsigned bytes = 0;
+      int pages[DEC_STAGE / 8];
+      for (int i = 0; i < pages_per_stage; ++i) {
+        const int j0 = key0 + i * page_size;                       // first key of the page
+        int page = -1;
+        if (j0 < part_hi && j0 + page_size > lo_w) page = bt[j0 / page_size];
+        pages[i] = page;
+        if (page >= 0) bytes += 2 * page_bytes;
+      }
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+      for (int i = 0; i < pages_per_stage; ++i) {
+        if (pages[i] < 0) continue;
+        const bf16* src = pool + (((int64_t)pages[i] * 2) * nkv + kvh) * page_size * hd;
+        const int row = s * DEC_STAGE + i * page_size;
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                     ::"r"(dec_smem_u32(k_s + row * hd)), "l"(src), "r"(page_bytes), "r"(bar) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                     ::"r"(dec_smem_u32(v_s + row * hd)), "l"(src + v_off), "r"(page_bytes), "r"(bar) : "memory");
+      }
+    }
+  }
+  const int64_t tok = cu_seqlens[b];
+  for (int idx = tid; idx < GT * hd; idx += DEC_THREADS) {
+    const int g = idx / hd, d = idx - g * hd;
+    q_s[idx] = g < n_g ? to_f<bf16>(qkv[tok * q_row_stride + (int64_t)(kvh * G + g0 + g) * hd + d]) * scale : 0.f;
+  }
+  __syncthreads();                                                 // barriers initialised, q in place
+
+  float m[GT], l[GT], acc[GT][CH][8];
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int u = 0; u < CH; ++u)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][u][e] = 0.f;
+  }
+  const unsigned gmask = 0xFFu << ((tid & 31) & ~7);
+  bool gave_up = false;
+#pragma unroll 1
+  for (int s = 0; s < DEC_STAGES; ++s) {
+    if (part_lo + s * DEC_STAGE >= part_hi) break;
+    if (!mbar_wait(dec_smem_u32(&bars[s]), 0)) {
+      gave_up = true;
+      break;
+    }
+#pragma unroll 2
+    for (int jj = s * DEC_STAGE + kg; jj < (s + 1) * DEC_STAGE; jj += DEC_GROUPS) {
+      const int j = part_lo + jj;
+      if (j >= part_hi || j < lo_w) continue;
+      if (bt[j / page_size] < 0) continue;
+      float kx[CH][8], vx[CH][8];
+#pragma unroll
+      for (int u = 0; u < CH; ++u) {
+        const int d0 = (lg + DEC_LANES * u) * 8;
+        if (d0 < hd) {
+          Vec8<bf16>::load(k_s + jj * hd + d0, kx[u]);
+          Vec8<bf16>::load(v_s + jj * hd + d0, vx[u]);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        float dot = 0.f;
+#pragma unroll
+        for (int u = 0; u < CH; ++u) {
+          const int d0 = (lg + DEC_LANES * u) * 8;
+          if (d0 < hd) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dot = fmaf(q_s[g * hd + d0 + e], kx[u][e], dot);
+          }
+        }
+#pragma unroll
+        for (int o = 1; o < DEC_LANES; o <<= 1) dot += __shfl_xor_sync(gmask, dot, o);
+        const float m_new = fmaxf(m[g], dot);
+        const float alpha = expf(m[g] - m_new), p = expf(dot - m_new);
+        l[g] = l[g] * alpha + p;
+        m[g] = m_new;
+#pragma unroll
+        for (int u = 0; u < CH; ++u) {
+          const int d0 = (lg + DEC_LANES * u) * 8;
+          if (d0 < hd) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][u][e] = fmaf(p, vx[u][e], acc[g][u][e] * alpha);
+          }
+        }
+      }
+    }
+  }
+  if (gave_up) {
+    // A copy did not land within the limit: report it, wait (bounded) for what is still in flight so that
+    // no copy writes into memory the next block owns, and leave this partition empty.
+    if (tid == 0) atomicOr(err + 1, 1);
+    for (int s = 0; s < DEC_STAGES; ++s)
+      if (part_lo + s * DEC_STAGE < part_hi) mbar_wait(dec_smem_u32(&bars[s]), 0);
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+      m[g] = -INFINITY;
+      l[g] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    if (lg == 0) {
+      s_m[kg * GT + g] = m[g];
+      s_l[kg * GT + g] = l[g];
+    }
+#pragma unroll
+    for (int u = 0; u < CH; ++u) {
+      const int d0 = (lg + DEC_LANES * u) * 8;
+      if (d0 < hd) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s_acc[((int64_t)kg * GT + g) * hd + d0 + e] = acc[g][u][e];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < n_g * hd; idx += DEC_THREADS) {
+    const int g = idx / hd, d = idx - g * hd;
+    float M = -INFINITY;
+    for (int k = 0; k < DEC_GROUPS; ++k) M = fmaxf(M, s_m[k * GT + g]);
+    float lt = 0.f, o = 0.f;
+    if (M > -INFINITY) {
+      for (int k = 0; k < DEC_GROUPS; ++k) {
+        const float mk = s_m[k * GT + g];
+        const float f = mk == -INFINITY ? 0.f : expf(mk - M);
+        lt += f * s_l[k * GT + g];
+        o += f * s_acc[((int64_t)k * GT + g) * hd + d];
+      }
+    }
+    const int64_t slot = slot0 + (int64_t)g * max_parts;
+    tmp_out[slot * hd + d] = o;
+    if (d == 0) {
+      tmp_m[slot] = M;
+      tmp_l[slot] = lt;
+    }
+  }
+}
+
+template <int GT, int CH>
+static int launch_partition_tma(dim3 grid, cudaStream_t stream, const void* qkv, int64_t q_row_stride, const void* pool,
+                                const int* bt, int bt_stride, const int* cu, const int* cl, int nh, int nkv, int hd,
+                                int page_size, float scale, int window, float* to, float* tm, float* tl, int max_parts,
+                                int* err) {
+  const size_t smem = (size_t)2 * DEC_PART * hd * sizeof(bf16) +
+                      sizeof(float) * ((size_t)GT * hd + 2 * DEC_GROUPS * GT + (size_t)DEC_GROUPS * GT * hd);
+  static size_t attr = 0;
+  if (smem > attr) {
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_kernel<GT, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
+    attr = smem;
+  }
+  decode_partition_tma_kernel<GT, CH><<<grid, DEC_THREADS, smem, stream>>>(
+      (const bf16*)qkv, q_row_stride, (const bf16*)pool, bt, bt_stride, cu, cl, nh, nkv, hd, page_size, scale, window,
+      to, tm, tl, max_parts, err);
+  return 0;
+}
+
+// ---- the partition step on the tensor cores -----------------------------------------------------
+// The query heads of one key/value head (up to 16) form the rows of an m16 strip; each of the four
+// warps takes 32 keys of the 128-key partition: S = Q K^T and O = P V with mma.sync m16n8k16, softmax
+// in float32 on the accumulator fragments, then the four warps' (m, l, O) are merged in index order.
+// K and V arrive by cp.async (zero fill outside the request's keys) in two groups, so the scores are
+// computed while V is still on its way.  bfloat16, head_dim 64 or 128, any page size.
+template <int HD>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_partition_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, const bf16* __restrict__ pool,
+                            const int* __restrict__ block_tables, int bt_stride,
+                            const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
+                            int nh, int nkv, int page_size, float scale, int window,
+                            float* __restrict__ tmp_out, float* __restrict__ tmp_m,
+                            float* __restrict__ tmp_l, int max_parts) {
+  using namespace mma_prims;
+  extern __shared__ __align__(128) unsigned char dec_smem[];
+  __shared__ float w_m[4][16], w_l[4][16];
+  constexpr int PIECES = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8;
+  const int G = nh / nkv, head_tiles = (G + 15) / 16;
+  const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * 16;
+  const int z = blockIdx.z;
+  const int L = context_lens[b];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  const int n_g = min(16, G - g0);
+  const int lo_w = window > 0 ? max(0, L - window) : 0;
+  const int part_lo = z * DEC_PART, part_hi = min(L, part_lo + DEC_PART);
+  const int64_t slot0 = ((int64_t)b * nh + kvh * G + g0) * max_parts + z;
+  if (part_hi <= part_lo || part_hi <= lo_w) {
+    if (part_lo < L || z == 0)
+      for (int r = tid; r < n_g; r += DEC_THREADS) {
+        tmp_m[slot0 + (int64_t)r * max_parts] = -INFINITY;
+        tmp_l[slot0 + (int64_t)r * max_parts] = 0.f;
+      }
+    return;
+  }
+  bf16* qs = reinterpret_cast<bf16*>(dec_smem);     // [16][HD]
+  bf16* ks = qs + 16 * HD;                           // [128][HD]; later the warps' partial outputs
+  bf16* vs = ks + DEC_PART * HD;                     // [128][HD]
+  const int* bt = block_tables + (int64_t)b * bt_stride;
+  const int64_t tok = cu_seqlens[b];
+  for (int c = tid; c < 16 * PIECES; c += DEC_THREADS) {
+    const int row = c / PIECES, piece = c % PIECES;
+    const bool ok = row < n_g;
+    cp_async16(tile_ptr<HD>(qs, row, piece),
+               ok ? qkv + tok * q_row_stride + (int64_t)(kvh * G + g0 + row) * HD + piece * 8 : qkv, ok);
+  }
+  const int64_t v_off = (int64_t)nkv * page_size * HD;
+#pragma unroll 1
+  for (int which = 0; which < 2; ++which) {          // K first, then V, each its own group
+    bf16* dst = which ? vs : ks;
+    for (int c = tid; c < DEC_PART * PIECES; c += DEC_THREADS) {
+      const int row = c / PIECES, piece = c % PIECES;
+      const int j = part_lo + row;
+      bool ok = j < part_hi && j >= lo_w;
+      const bf16* src = pool;
+      if (ok) {
+        const int page = bt[j / page_size];
+        ok = page >= 0;
+        if (ok) src = pool + (((int64_t)page * 2) * nkv + kvh) * page_size * HD + (int64_t)(j % page_size) * HD + piece * 8 +
+                      (which ? v_off : 0);
+      }
+      cp_async16(tile_ptr<HD>(dst, row, piece), src, ok);
+    }
+    cp_async_commit();
+  }
+  cp_async_wait<1>();
+  __syncthreads();
+  const float sl2 = scale * 1.4426950408889634f;
+  const int mi = lane >> 3;
+  float s[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+    uint32_t qf[4];
+    ldmatrix_x4(qf, tile_ptr<HD>(qs, (mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
+#pragma unroll
+    for (int np = 0; np < 2; ++np) {
+      uint32_t bfr[4];
+      ldmatrix_x4(bfr, tile_ptr<HD>(ks, warp * 32 + np * 16 + (mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)));
+      mma_bf16(s[2 * np], qf, bfr[0], bfr[1]);
+      mma_bf16(s[2 * np + 1], qf, bfr[2], bfr[3]);
+    }
+  }
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int j = part_lo + warp * 32 + i * 8 + 2 * t4 + e;
+      if (j >= part_hi || j < lo_w) s[i][e] = s[i][e + 2] = -INFINITY;
+    }
+    mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mu0 = mx0 == -INFINITY ? 0.f : mx0, mu1 = mx1 == -INFINITY ? 0.f : mx1;
+  float l0 = 0.f, l1 = 0.f;
+  uint32_t pf[2][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float p0 = exp2f((s[i][0] - mu0) * sl2), p1 = exp2f((s[i][1] - mu0) * sl2);
+    const float p2 = exp2f((s[i][2] - mu1) * sl2), p3 = exp2f((s[i][3] - mu1) * sl2);
+    l0 += p0 + p1;
+    l1 += p2 + p3;
+    pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+    pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  cp_async_wait<0>();
+  __syncthreads();                                   // V has landed; every warp is done reading K
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+    for (int np = 0; np < NT_O / 2; ++np) {
+      uint32_t bfr[4];
+      ldmatrix_x4_trans(bfr, tile_ptr<HD>(vs, warp * 32 + kk * 16 + (mi & 1) * 8 + (lane & 7), np * 2 + (mi >> 1)));
+      mma_bf16(o[2 * np], pf[kk], bfr[0], bfr[1]);
+      mma_bf16(o[2 * np + 1], pf[kk], bfr[2], bfr[3]);
+    }
+  }
+  // Each warp's (m, l, O) for the rows that are real heads, then the merge in warp order.
+  float* po = reinterpret_cast<float*>(ks);          // [4][16][HD] float32, over the K tile
+  if (t4 == 0) {
+    w_m[warp][g] = mx0;
+    w_l[warp][g] = l0;
+    w_m[warp][g + 8] = mx1;
+    w_l[warp][g + 8] = l1;
+  }
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) {
+    if (g < n_g) *reinterpret_cast<float2*>(po + ((warp * 16 + g) * HD + i * 8 + 2 * t4)) = make_float2(o[i][0], o[i][1]);
+    if (g + 8 < n_g) *reinterpret_cast<float2*>(po + ((warp * 16 + g + 8) * HD + i * 8 + 2 * t4)) = make_float2(o[i][2], o[i][3]);
+  }
+  __syncthreads();
+  for (int idx = tid; idx < n_g * HD; idx += DEC_THREADS) {
+    const int r = idx / HD, d = idx - r * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, w_m[w][r]);
+    float lt = 0.f, acc = 0.f;
+    if (M > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = w_m[w][r];
+        const float f = mw == -INFINITY ? 0.f : exp2f((mw - M) * sl2);
+        lt += f * w_l[w][r];
+        acc += f * po[(w * 16 + r) * HD + d];
+      }
+    }
+    const int64_t slot = slot0 + (int64_t)r * max_parts;
+    tmp_out[slot * HD + d] = acc;
+    if (d == 0) {
+      tmp_m[slot] = M == -INFINITY ? -INFINITY : M * scale;     // natural-log units, as the merge kernel expects
+      tmp_l[slot] = lt;
+    }
+  }
+}
+
+template <int HD>
+static int launch_partition_mma(int num_reqs, int max_parts, cudaStream_t stream, const void* qkv, int64_t q_row_stride,
+                                const void* pool, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
+                                int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl) {
+  const size_t smem = (size_t)(16 + 2 * DEC_PART) * HD * sizeof(bf16);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const int G = nh / nkv;
+  dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
+  decode_partition_mma_kernel<HD><<<grid, DEC_THREADS, smem, stream>>>(
+      (const bf16*)qkv, q_row_stride, (const bf16*)pool, bt, bt_stride, cu, cl, nh, nkv, page_size, scale, window, to, tm, tl,
+      max_parts);
+  return 0;
+}
+
 template <typename T>
 __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
                                     const int* __restrict__ cu_seqlens,
@@ -216,7 +628,7 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
                           int bt_stride, const int* cu_seqlens, const int* context_lens,
                           int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
                           int window, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts,
-                          cudaStream_t stream) {
+                          int* err, int kind, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   ME_REQUIRE(hd % 8 == 0 && hd >= 8 && hd <= 256, "me_attn_decode: head_dim %d is not a multiple of 8 up to 256", hd);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "me_attn_decode: %d heads, %d kv heads", nh, nkv);
@@ -231,8 +643,35 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   ME_REQUIRE((int64_t)nkv * head_tiles <= 65535, "me_attn_decode: too many heads");
   dim3 grid(num_reqs, nkv * head_tiles, max_parts);
   const size_t smem = sizeof(float) * ((size_t)GT * hd + 2 * DEC_GROUPS * GT + (size_t)DEC_GROUPS * GT * hd);
+  // kind: 0 = the fastest kernel that takes the shape, 1 = CUDA cores, 2 = CUDA cores fed by bulk copies,
+  // 3 = tensor cores.
+  const bool mma_ok = dtype == ME_BF16 && (hd == 64 || hd == 128);
+  const bool tma_ok = dtype == ME_BF16 && hd <= 128 && err != nullptr &&
+                      (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
+  ME_REQUIRE(kind >= 0 && kind <= 3 && (kind != 3 || mma_ok) && (kind != 2 || tma_ok),
+             "me_attn_decode: kernel kind %d does not take this shape", kind);
+  const bool mma = kind == 3 || (kind == 0 && mma_ok);
+  const bool tma = kind == 2;
+  if (mma) {
+    ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode: too many heads");
+    int rc = hd == 64 ? launch_partition_mma<64>(num_reqs, max_parts, stream, qkv, q_row_stride, pool, block_tables, bt_stride,
+                                                 cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l)
+                      : launch_partition_mma<128>(num_reqs, max_parts, stream, qkv, q_row_stride, pool, block_tables, bt_stride,
+                                                  cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l);
+    if (rc) return rc;
+  }
+#define ME_DEC_TMA_CASE(GT_, CH_)                                                                   \
+  if (tma && !mma && GT == GT_ && CH == CH_) {                                                              \
+    int rc = launch_partition_tma<GT_, CH_>(grid, stream, qkv, q_row_stride, pool, block_tables,    \
+        bt_stride, cu_seqlens, context_lens, nh, nkv, hd, page_size, scale, window, tmp_out, tmp_m, \
+        tmp_l, max_parts, err);                                                                     \
+    if (rc) return rc;                                                                              \
+  }
+  ME_DEC_TMA_CASE(1, 1) ME_DEC_TMA_CASE(2, 1) ME_DEC_TMA_CASE(4, 1)
+  ME_DEC_TMA_CASE(1, 2) ME_DEC_TMA_CASE(2, 2) ME_DEC_TMA_CASE(4, 2)
+#undef ME_DEC_TMA_CASE
 #define ME_DEC_CASE(GT_, CH_)                                                                       \
-  if (GT == GT_ && CH == CH_) {                                                                     \
+  if (!tma && !mma && GT == GT_ && CH == CH_) {                                                             \
     ME_DISPATCH_DTYPE(dtype, T, (launch_partition<T, GT_, CH_>(grid, smem, stream, qkv, q_row_stride, \
         pool, block_tables, bt_stride, cu_seqlens, context_lens, nh, nkv, hd, page_size, scale,     \
         window, tmp_out, tmp_m, tmp_l, max_parts)));                                                \

@@ -16,37 +16,20 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   return x;
 }
 
-constexpr int SAMPLE_THREADS = 1024;
+constexpr int SAMPLE_THREADS = 256;
+constexpr int SAMPLE_CHUNK = 4096;        // vocabulary entries per block of the first pass
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(const float* __restrict__ logits, int64_t row_stride, const float* __restrict__ temperature,
-              const int* __restrict__ seeds, const int* __restrict__ positions, int* __restrict__ out, int V) {
+__device__ __forceinline__ bool better(float k, int i, float bk, int bi) { return k > bk || (k == bk && i < bi); }
+
+// Reduce (key, index) over the block; the result is valid in thread 0.
+__device__ __forceinline__ void block_best(float& best, int& best_i) {
   __shared__ float s_key[32];
   __shared__ int s_idx[32];
-  const int row = blockIdx.x;
-  const float* x = logits + (int64_t)row * row_stride;
-  const float T = temperature[row];
-  const uint32_t s = mix32((uint32_t)seeds[row] + 0x9E3779B9u);
-  const uint32_t p = mix32((s ^ (uint32_t)positions[row]) + 0x85EBCA6Bu);
-  float best = -INFINITY;
-  int best_i = 0x7fffffff;
-  for (int v = threadIdx.x; v < V; v += SAMPLE_THREADS) {
-    float key = x[v];
-    if (T > 0.f) {
-      const uint32_t h = mix32((p ^ (uint32_t)v) + 0xC2B2AE35u);
-      const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
-      key = key / T - logf(-logf(u));
-    }
-    if (key > best || (key == best && v < best_i)) {
-      best = key;
-      best_i = v;
-    }
-  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ok = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-    if (ok > best || (ok == best && oi < best_i)) {
+    if (better(ok, oi, best, best_i)) {
       best = ok;
       best_i = oi;
     }
@@ -57,21 +40,78 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, const float*
     s_idx[warp] = best_i;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int w = 1; w < SAMPLE_THREADS / 32; ++w)
-      if (s_key[w] > best || (s_key[w] == best && s_idx[w] < best_i)) {
+  if (threadIdx.x == 0)
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (better(s_key[w], s_idx[w], best, best_i)) {
         best = s_key[w];
         best_i = s_idx[w];
       }
-    out[row] = best_i == 0x7fffffff ? 0 : best_i;
+}
+
+// Pass 1: block (row, chunk) finds the best entry of its piece of the vocabulary.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_partial_kernel(const float* __restrict__ logits, int64_t row_stride, const float* __restrict__ temperature,
+                      const int* __restrict__ seeds, const int* __restrict__ positions,
+                      float* __restrict__ part_key, int* __restrict__ part_idx, int V, int chunks) {
+  const int row = blockIdx.x, chunk = blockIdx.y;
+  const float* x = logits + (int64_t)row * row_stride;
+  const float T = temperature[row];
+  const uint32_t s = mix32((uint32_t)seeds[row] + 0x9E3779B9u);
+  const uint32_t p = mix32((s ^ (uint32_t)positions[row]) + 0x85EBCA6Bu);
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  const int v_end = min(V, (chunk + 1) * SAMPLE_CHUNK);
+  for (int v = chunk * SAMPLE_CHUNK + threadIdx.x; v < v_end; v += SAMPLE_THREADS) {
+    float key = x[v];
+    if (T > 0.f) {
+      const uint32_t h = mix32((p ^ (uint32_t)v) + 0xC2B2AE35u);
+      const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+      key = key / T - logf(-logf(u));
+    }
+    if (better(key, v, best, best_i)) {
+      best = key;
+      best_i = v;
+    }
+  }
+  block_best(best, best_i);
+  if (threadIdx.x == 0) {
+    part_key[(int64_t)row * chunks + chunk] = best;
+    part_idx[(int64_t)row * chunks + chunk] = best_i;
   }
 }
 
+// Pass 2: one block per row picks the best of the chunks.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_final_kernel(const float* __restrict__ part_key, const int* __restrict__ part_idx, int* __restrict__ out, int chunks) {
+  const int row = blockIdx.x;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int c = threadIdx.x; c < chunks; c += SAMPLE_THREADS) {
+    const float k = part_key[(int64_t)row * chunks + c];
+    const int i = part_idx[(int64_t)row * chunks + c];
+    if (better(k, i, best, best_i)) {
+      best = k;
+      best_i = i;
+    }
+  }
+  block_best(best, best_i);
+  if (threadIdx.x == 0) out[row] = best_i == 0x7fffffff ? 0 : best_i;
+}
+
+ME_API int me_sample_chunks(int V) { return (V + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK; }
+
+// Scratch (caller-provided): part_key and part_idx of S * me_sample_chunks(V) entries each.
 ME_API int me_sample(const float* logits, int64_t row_stride, const float* temperature, const int* seeds,
-                     const int* positions, int* out, int S, int V, cudaStream_t stream) {
+                     const int* positions, int* out, int S, int V, float* part_key, int* part_idx,
+                     cudaStream_t stream) {
   if (S == 0) return 0;
   ME_REQUIRE(S > 0 && V > 0, "me_sample: bad sizes S=%d V=%d", S, V);
-  sample_kernel<<<S, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, temperature, seeds, positions, out, V);
-  ME_LAUNCH_CHECK("me_sample");
+  const int chunks = me_sample_chunks(V);
+  ME_REQUIRE(chunks <= 65535, "me_sample: vocabulary %d is too large", V);
+  sample_partial_kernel<<<dim3(S, chunks), SAMPLE_THREADS, 0, stream>>>(logits, row_stride, temperature, seeds, positions,
+                                                                       part_key, part_idx, V, chunks);
+  ME_LAUNCH_CHECK("me_sample (pass 1)");
+  sample_final_kernel<<<S, SAMPLE_THREADS, 0, stream>>>(part_key, part_idx, out, chunks);
+  ME_LAUNCH_CHECK("me_sample (pass 2)");
   return 0;
 }

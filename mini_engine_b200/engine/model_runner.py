@@ -218,15 +218,18 @@ class ModelRunner:
         if pad_reqs:                                  # fixed shape: as many rows as requests
             want_rows += [0] * (B - S_real)
         S = len(want_rows)
-        BQ = ops.ATTN_TILE_Q
-        tiles = [(b, q0) for b in range(D, B_real) for q0 in range(0, lens[b], BQ)]
-        n_tiles = len(tiles)
+        tile_np = {}
+        for tq in ops.ATTN_TILE_SIZES:
+            per_req = [np.stack((np.full((lens[b] + tq - 1) // tq, b, dtype=np.int32),
+                                 np.arange(0, lens[b], tq, dtype=np.int32)), axis=1) for b in range(D, B_real)]
+            tile_np[tq] = np.concatenate(per_req).reshape(-1) if per_req else np.zeros(0, dtype=np.int32)
+        n_tiles = sum(len(a) // 2 for a in tile_np.values())
 
         def al(n):                       # keep every array 16-byte aligned on the device
             return (n + 3) & ~3
         sizes = dict(tok=al(T), pos=al(T), req=al(T), cu=al(B + 1), ctxlen=al(B), slot=al(B),
                      rows=al(max(S, 1)), temp=al(max(S, 1)), seed=al(max(S, 1)), spos=al(max(S, 1)),
-                     tiles=al(max(2 * n_tiles, 1)))
+                     tiles=sum(al(max(len(a), 1)) for a in tile_np.values()))
         total = sum(sizes.values()) + sum(al(T) + al(B * widths[g]) for g in range(G))
         pin, dev = self._stage(total, dev)
         if dev.numel() < total:
@@ -275,8 +278,11 @@ class ModelRunner:
             host[o_temp:o_temp + S] = np.asarray(temps + [0.0] * padn, dtype=np.float32).view(np.int32)
             host[o_seed:o_seed + S] = seeds + [0] * padn
             host[o_spos:o_spos + S] = spos + [0] * padn
-        if n_tiles:
-            host[o_tiles:o_tiles + 2 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+        tile_off, cur_t = {}, o_tiles
+        for tq, a in tile_np.items():
+            tile_off[tq] = cur_t
+            host[cur_t:cur_t + len(a)] = a
+            cur_t += al(max(len(a), 1))
         for g in range(G):
             w = widths[g]
             bt = host[o_bt[g]:o_bt[g] + B * w].reshape(B, w)
@@ -317,9 +323,11 @@ class ModelRunner:
         ctx.attn_meta = AttnMeta(
             num_reqs=B, num_tokens=T, num_decodes=D + pad if pad_reqs else D,
             cu_seqlens=dev[o_cu:o_cu + B + 1], context_lens=dev[o_ctx:o_ctx + B],
-            tiles=dev[o_tiles:o_tiles + 2 * max(n_tiles, 1)].view(-1, 2), num_tiles=n_tiles,
+            tile_lists={tq: (dev[tile_off[tq]:tile_off[tq] + max(len(a), 2)].view(-1, 2), len(a) // 2)
+                        for tq, a in tile_np.items()},
+            num_tiles=n_tiles,
             max_context_len=max(ends + [1]) if not table_width else table_width * ps,
-            workspace=ctx.buffer)
+            workspace=ctx.buffer, error_flag=self.error_flag)
         ctx.host = HostMeta(starts=starts, lengths=lens,
                             state_slots=[items[i].holder.state_slot for i in order],
                             holders=[items[i].holder for i in order])
@@ -333,7 +341,7 @@ class ModelRunner:
         tokens = None
         if sample:
             tokens = ctx.buffer("sampled_tokens", (logits.shape[0],), torch.int32)
-            ops.sample(logits, ctx.sample_temps, ctx.sample_seeds, ctx.sample_positions, tokens)
+            ops.sample(logits, ctx.sample_temps, ctx.sample_seeds, ctx.sample_positions, tokens, workspace=ctx.buffer)
         return logits, tokens
 
     @torch.inference_mode()
@@ -390,4 +398,4 @@ class ModelRunner:
         if any(flags):
             self.error_flag.zero_()
             raise RuntimeError(f"a kernel reported bad input: flags {flags} "
-                               "(flag 0: token id outside the vocabulary)")
+                               "(flag 0: token id outside the vocabulary; flag 1: a bulk copy did not land in time)")

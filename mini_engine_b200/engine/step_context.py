@@ -32,10 +32,11 @@ class AttnMeta:
     num_decodes: int
     cu_seqlens: torch.Tensor           # [B+1] int32
     context_lens: torch.Tensor         # [B] int32: keys of the request after this step
-    tiles: torch.Tensor                # [num_tiles, 2] int32: (request, first local query) per query tile
-    num_tiles: int
+    tile_lists: dict                   # tile size -> ([n, 2] int32 (request, first local query), n), requests >= num_decodes
+    num_tiles: int                     # > 0 if any request brings several tokens
     max_context_len: int               # host upper bound of context_lens (sizes split-K scratch)
     workspace: Any                     # callable (name, shape, dtype) -> tensor
+    error_flag: Any = None             # int32[4] on the device: kernels report bad input or a timed-out wait here
 
 
 @dataclass

@@ -14,8 +14,9 @@ import torch
 
 from . import build as _build
 
-ATTN_TILE_Q = 16          # queries per block of the chunk-attention kernels (csrc/attention_chunk.cu)
-DECODE_PARTITION = 256    # keys per partition of the decode kernel (csrc/attention_decode.cu)
+ATTN_TILE_Q = 16          # query tokens per block of the CUDA-core chunk kernel (csrc/attention_chunk.cu)
+ATTN_TILE_SIZES = (8, 16, 32, 64)   # query tokens per block that some attention kernel may ask for
+DECODE_PARTITION = 128    # keys per partition of the decode kernel (csrc/attention_decode.cu)
 MAX_HEAD_DIM = 256
 
 _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
@@ -26,8 +27,9 @@ _PROTOS = {
     "me_gemm_simt": [_P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P],
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
-    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P],
-    "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P],
+    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P],
+    "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
 }
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -55,6 +57,8 @@ def require_extension() -> ctypes.CDLL:
         fn.restype = ctypes.c_int
     if lib.me_attn_chunk_tile_q() != ATTN_TILE_Q or lib.me_attn_decode_partition() != DECODE_PARTITION:
         raise KernelError("the kernel library and ops/__init__.py disagree on tile sizes")
+    lib.me_attn_prefill_heads_per_block.argtypes = [_I, _I, _I]
+    lib.me_sample_chunks.argtypes = [_I]
     _lib = lib
     return lib
 
@@ -203,18 +207,42 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, 
 
 def attention_chunks(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
                      scale, window, tiles=None, num_tiles=None) -> None:
-    """The chunk kernel over the query tiles of ``meta`` (requests that bring several tokens)."""
-    tiles = meta.tiles if tiles is None else tiles
-    n = meta.num_tiles if num_tiles is None else num_tiles
+    """The CUDA-core chunk kernel over query tiles of 16 tokens (requests that bring several tokens)."""
+    if tiles is None:
+        tiles, num_tiles = meta.tile_lists[ATTN_TILE_Q]
     _call("me_attn_chunk", qkv.data_ptr(), _dt(qkv), qkv.stride(0), out.data_ptr(), out.stride(0),
           pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
-          meta.context_lens.data_ptr(), tiles.data_ptr(), n, num_heads, num_kv_heads, head_dim,
+          meta.context_lens.data_ptr(), tiles.data_ptr(), num_tiles, num_heads, num_kv_heads, head_dim,
           page_size, float(scale), int(window or 0), _stream())
 
 
+def prefill_heads_per_block(num_heads: int, num_kv_heads: int, head_dim: int) -> int:
+    """How many heads of a group share a block of the tensor-core prefill kernel; 0 if it refuses the shape."""
+    return (_lib or require_extension()).me_attn_prefill_heads_per_block(num_heads, num_kv_heads, head_dim)
+
+
+def attention_prefill(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
+                      scale, window, tiles=None, num_tiles=None) -> None:
+    """The tensor-core prefill kernel (bfloat16, head_dim 64 or 128) over tiles of 64 / heads-per-block tokens."""
+    gp = prefill_heads_per_block(num_heads, num_kv_heads, head_dim)
+    _need(gp > 0 and qkv.dtype == torch.bfloat16, "attention_prefill: shape or dtype not taken by the tensor-core kernel")
+    if tiles is None:
+        tiles, num_tiles = meta.tile_lists[64 // gp]
+    _call("me_attn_prefill", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), pool.data_ptr(),
+          block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(),
+          tiles.data_ptr(), num_tiles, num_heads, num_kv_heads, head_dim, page_size, float(scale),
+          int(window or 0), _stream())
+
+
+DECODE_KINDS = {"auto": 0, "cuda_cores": 1, "bulk_copy": 2, "tensor_cores": 3}
+
+
 def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
-                     scale, window) -> None:
-    """The split-K decode kernel and its merge over requests [0, meta.num_decodes)."""
+                     scale, window, kind: str = "auto") -> None:
+    """The split-K decode kernel and its merge over requests [0, meta.num_decodes).
+
+    ``kind`` picks the partition kernel: "auto" (tensor cores for bfloat16 with head_dim 64 or 128, else
+    CUDA cores), or one of them by name (tests run each)."""
     D = meta.num_decodes
     parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
     tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * parts * head_dim,), torch.float32)
@@ -222,7 +250,8 @@ def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_siz
     _call("me_attn_decode", qkv.data_ptr(), _dt(qkv), qkv.stride(0), out.data_ptr(), out.stride(0),
           pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
           meta.context_lens.data_ptr(), D, num_heads, num_kv_heads, head_dim, page_size, float(scale),
-          int(window or 0), tmp_out.data_ptr(), tmp_ml[0].data_ptr(), tmp_ml[1].data_ptr(), parts, _stream())
+          int(window or 0), tmp_out.data_ptr(), tmp_ml[0].data_ptr(), tmp_ml[1].data_ptr(), parts,
+          _ptr(meta.error_flag), DECODE_KINDS[kind], _stream())
     global launches
     launches += 1          # partition kernel + merge kernel
 
@@ -240,16 +269,26 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv
     if meta.num_decodes > 0:
         attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window)
     if meta.num_tiles > 0:
-        attention_chunks(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window)
+        fn = attention_prefill if (qkv.dtype == torch.bfloat16
+                                   and prefill_heads_per_block(num_heads, num_kv_heads, head_dim) > 0) else attention_chunks
+        fn(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window)
 
 
 # ---- sampling -------------------------------------------------------------------------------
 def sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor, positions: torch.Tensor,
-           out: torch.Tensor) -> None:
+           out: torch.Tensor, workspace=None) -> None:
+    """Greedy (temperature 0) or exponential-race draw per row; two passes over pieces of the vocabulary."""
+    global launches
     S, V = logits.shape
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: logits must be float32 rows")
     _need(temperatures.dtype == torch.float32 and seeds.dtype == torch.int32 and positions.dtype == torch.int32
           and out.dtype == torch.int32, "sample: dtypes")
     _need(temperatures.shape[0] == S and seeds.shape[0] == S and positions.shape[0] == S and out.shape[0] == S, "sample: sizes")
+    chunks = (_lib or require_extension()).me_sample_chunks(V)
+    if workspace is None:
+        part = torch.empty(2, S * chunks, dtype=torch.float32, device=logits.device)
+    else:
+        part = workspace("sample_partials", (2, S * chunks), torch.float32)
     _call("me_sample", logits.data_ptr(), logits.stride(0), temperatures.data_ptr(), seeds.data_ptr(),
-          positions.data_ptr(), out.data_ptr(), S, V, _stream())
+          positions.data_ptr(), out.data_ptr(), S, V, part[0].data_ptr(), part[1].data_ptr(), _stream())
+    launches += 1

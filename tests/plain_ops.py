@@ -12,7 +12,8 @@ import numpy as np
 import torch
 
 ATTN_TILE_Q = 16
-DECODE_PARTITION = 256
+ATTN_TILE_SIZES = (8, 16, 32, 64)
+DECODE_PARTITION = 128
 
 
 def check_attention_sizes(head_dim, num_heads, num_kv_heads):
@@ -148,7 +149,7 @@ def sample_keys(logits_row, temperature, seed, position):
     return x / temperature - np.log(-np.log(u))
 
 
-def sample(logits, temperatures, seeds, positions, out):
+def sample(logits, temperatures, seeds, positions, out, workspace=None):
     for r in range(logits.shape[0]):
         keys = sample_keys(logits[r], float(temperatures[r]), int(seeds[r]), int(positions[r]))
         out[r] = int(np.argmax(keys))

@@ -28,7 +28,7 @@ def _check_greedy(name, dtype, prompt, tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_greedy_generation(name, dtype):
     from mini_engine_b200 import SamplingParams
     llm = _llm(name, dtype)

@@ -191,7 +191,10 @@ class Batch:
             cu.append(cu[-1] + n)
         D = sum(1 for n in q_lens if n == 1)
         from mini_engine_b200 import ops as o
-        tiles = [(b, q0) for b in range(D, B) for q0 in range(0, q_lens[b], o.ATTN_TILE_Q)]
+
+        def tile_list(first, tq):
+            t = [(b, q0) for b in range(first, B) for q0 in range(0, q_lens[b], tq)]
+            return torch.tensor(t or [(0, 0)], dtype=torch.int32, device=DEV), len(t)
         self.pool, self.qkv, self.bt = self.pool.to(DEV), self.qkv.to(DEV), bt.to(DEV)
         self._ws = {}
 
@@ -203,10 +206,10 @@ class Batch:
         self.meta = AttnMeta(num_reqs=B, num_tokens=T, num_decodes=D,
                              cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV),
                              context_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
-                             tiles=torch.tensor(tiles or [(0, 0)], dtype=torch.int32, device=DEV), num_tiles=len(tiles),
-                             max_context_len=max(ctx_lens), workspace=workspace)
-        self.all_tiles = torch.tensor([(b, q0) for b in range(B) for q0 in range(0, q_lens[b], o.ATTN_TILE_Q)],
-                                      dtype=torch.int32, device=DEV)
+                             tile_lists={tq: tile_list(D, tq) for tq in o.ATTN_TILE_SIZES}, num_tiles=B - D,
+                             max_context_len=max(ctx_lens), workspace=workspace,
+                             error_flag=torch.zeros(4, dtype=torch.int32, device=DEV))
+        self.all_tiles = {tq: tile_list(0, tq) for tq in o.ATTN_TILE_SIZES}     # single tokens as tiles too
         self.q_lens, self.ctx_lens = q_lens, ctx_lens
 
 
@@ -216,12 +219,17 @@ def run_attention(ops, bt: Batch, dtype, window, which="split"):
     ref = torch.empty_like(out)
     scale = bt.hd ** -0.5
     args = (bt.nh, bt.nkv, bt.hd, bt.pool, bt.page, bt.bt, bt.meta, scale, window)
-    if which == "split":
+    if which == "split":                                                   # decode kernel + the dtype's prefill kernel
         ops.paged_attention(bt.qkv, out, *args)
-    else:                                                                  # everything through the chunk kernel
-        ops.attention_chunks(bt.qkv, out, *args, tiles=bt.all_tiles, num_tiles=bt.all_tiles.shape[0])
+    elif which == "chunks":                                                # everything through the CUDA-core chunk kernel
+        tiles, n = bt.all_tiles[ops.ATTN_TILE_Q]
+        ops.attention_chunks(bt.qkv, out, *args, tiles=tiles, num_tiles=n)
+    else:                                                                  # everything through the tensor-core kernel
+        tiles, n = bt.all_tiles[64 // ops.prefill_heads_per_block(bt.nh, bt.nkv, bt.hd)]
+        ops.attention_prefill(bt.qkv, out, *args, tiles=tiles, num_tiles=n)
     plain_ops.paged_attention(bt.qkv, ref, *args)
     assert not out.isnan().any(), "the kernel read a slot that no request owns (NaN-filled pool)"
+    assert bt.meta.error_flag.tolist() == [0, 0, 0, 0]
     return out, ref
 
 
@@ -240,9 +248,47 @@ def test_attention_mixed_batch(ops, nh, nkv, hd, page, dt):
         close(out, ref, DT[dt])
 
 
+@pytest.mark.parametrize("nh, nkv, hd, page", [(16, 8, 128, 16), (8, 1, 64, 32), (4, 4, 64, 8), (12, 4, 128, 16),
+                                                  (6, 1, 64, 16), (8, 2, 128, 64), (32, 2, 64, 16)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_tensor_core_prefill(ops, nh, nkv, hd, page, window):
+    # groups of 1, 2, 3 (not packed), 4, 6, 8 and 16 heads; tile, page and window edges; single tokens as tiles
+    assert ops.prefill_heads_per_block(nh, nkv, hd) in (1, 2, 4, 8)
+    ctx = [1, 300, 257, 31, 33, 64, 150, 16, 512, 129, 65]
+    ql = [1, 1, 1, 31, 17, 64, 2, 16, 130, 129, 64]
+    b = Batch(ctx, ql, nh, nkv, hd, page, torch.bfloat16, seed=hd + nh, window=window)
+    for which in ("split", "tensor"):
+        out, ref = run_attention(ops, b, torch.bfloat16, window, which)
+        close(out, ref, torch.bfloat16)
+    assert ops.prefill_heads_per_block(8, 2, 32) == 0 and ops.prefill_heads_per_block(8, 2, 96) == 0
+
+
+@pytest.mark.parametrize("kind", ["cuda_cores", "bulk_copy", "tensor_cores"])
+@pytest.mark.parametrize("nh, nkv, hd, page", [(16, 8, 128, 16), (8, 1, 64, 32), (4, 4, 64, 8), (12, 4, 128, 16),
+                                                  (40, 2, 64, 16), (6, 3, 48, 16), (8, 2, 32, 8)])
+@pytest.mark.parametrize("window", [None, 200])
+def test_attention_decode_kernels_by_name(ops, kind, nh, nkv, hd, page, window):
+    # every decode kernel on single tokens: contexts at partition (128) and page edges, groups of 1 to 20 heads
+    if kind == "tensor_cores" and hd not in (64, 128):
+        pytest.skip("the tensor-core decode kernel takes head_dim 64 and 128")
+    ctx = [1, 127, 128, 129, 300, 1000, 16, 255, 256, 257, 513]
+    b = Batch(ctx, [1] * len(ctx), nh, nkv, hd, page, torch.bfloat16, seed=nh + hd, window=window,
+              standout=lambda r, L, n: (L // 2, 0))
+    T = b.qkv.shape[0]
+    out = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ref = torch.empty_like(out)
+    args = (nh, nkv, hd, b.pool, page, b.bt, b.meta, hd ** -0.5, window)
+    ops.attention_decode(b.qkv, out, *args, kind=kind)
+    plain_ops.paged_attention(b.qkv, ref, *args)
+    assert not out.isnan().any() and b.meta.error_flag.tolist() == [0, 0, 0, 0]
+    close(out, ref, torch.bfloat16)
+
+
 @pytest.mark.parametrize("dt", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["split", "chunks"])
+@pytest.mark.parametrize("which", ["split", "chunks", "tensor"])
 def test_attention_finds_one_far_key_among_hundreds(ops, dt, which):
+    if which == "tensor" and dt != "bfloat16":
+        pytest.skip("the tensor-core kernel is bfloat16 only")
     # one key far back gets a score that stands out: the output must be (nearly) its value
     ctx, ql = [700, 1000, 520, 300], [1, 1, 40, 16]
     far = {0: 3, 1: 511, 2: 256, 3: 15}                                  # page edges, partition edges, the start
@@ -258,9 +304,11 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dt, which):
 
 
 @pytest.mark.parametrize("dt", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["split", "chunks"])
+@pytest.mark.parametrize("which", ["split", "chunks", "tensor"])
 @pytest.mark.parametrize("edge", [0, 1])
 def test_attention_window_edge(ops, dt, which, edge):
+    if which == "tensor" and dt != "bfloat16":
+        pytest.skip("the tensor-core kernel is bfloat16 only")
     # the standout key sits exactly at the window's edge (edge=0: last key still seen, edge=1: first not seen)
     w = 40
     ctx, ql = [300, 130, 97], [1, 30, 1]
@@ -268,7 +316,7 @@ def test_attention_window_edge(ops, dt, which, edge):
     def stand(r, L, n):
         p = L - 1                                                          # position of the request's last query
         return (p - w + 1 - edge, n - 1)
-    b = Batch(ctx, ql, 4, 2, 32, 8, DT[dt], seed=2, standout=stand, window=w)
+    b = Batch(ctx, ql, 4, 2, 64, 8, DT[dt], seed=2, standout=stand, window=w)
     out, ref = run_attention(ops, b, DT[dt], w, which)
     close(out, ref, DT[dt])
     cu = b.meta.cu_seqlens.tolist()
@@ -277,7 +325,7 @@ def test_attention_window_edge(ops, dt, which, edge):
         j = b.ctx_lens[r] - 1 - w + 1 - edge
         page = b.bt[r, j // 8].long()
         if edge == 0:
-            assert (ref[row, :32].float() - b.pool[page, 1, 0, j % 8].float()).abs().max() < 0.05
+            assert (ref[row, :64].float() - b.pool[page, 1, 0, j % 8].float()).abs().max() < 0.05
         # edge == 1: the key is outside; its page may even be given back (NaN there would show)
 
 
@@ -291,12 +339,14 @@ def test_attention_does_not_depend_on_the_batch(ops, dt):
     cu = many.meta.cu_seqlens.tolist()
     for b in (0, 2, 3):
         n, L = many.q_lens[b], many.ctx_lens[b]
-        tiles = [(0, q0) for q0 in range(0, n, ops.ATTN_TILE_Q)] if n > 1 else []
+        def tl(tq):
+            t = [(0, q0) for q0 in range(0, n, tq)] if n > 1 else []
+            return torch.tensor(t or [(0, 0)], dtype=torch.int32, device=DEV), len(t)
         meta = AttnMeta(num_reqs=1, num_tokens=n, num_decodes=1 if n == 1 else 0,
                         cu_seqlens=torch.tensor([0, n], dtype=torch.int32, device=DEV),
                         context_lens=torch.tensor([L], dtype=torch.int32, device=DEV),
-                        tiles=torch.tensor(tiles or [(0, 0)], dtype=torch.int32, device=DEV), num_tiles=len(tiles),
-                        max_context_len=L, workspace=many.meta.workspace)
+                        tile_lists={tq: tl(tq) for tq in ops.ATTN_TILE_SIZES}, num_tiles=1 if n > 1 else 0,
+                        max_context_len=L, workspace=many.meta.workspace, error_flag=many.meta.error_flag)
         qkv = many.qkv[cu[b]:cu[b + 1]].clone()
         out = torch.full((n, 8 * 64), float("nan"), dtype=DT[dt], device=DEV)
         ops.paged_attention(qkv, out, 8, 2, 64, many.pool, 16, many.bt[b:b + 1].clone(), meta, 64 ** -0.5, None)

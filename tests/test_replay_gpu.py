@@ -12,7 +12,8 @@ from tiny_configs import ALL
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LENGTHS = {"A": (70, 45, 100, 33, 64, 129), "B": (37, 88, 50, 112, 41, 65), "C": (90, 47, 130, 36, 80, 52)}
+LENGTHS = {"A": (70, 45, 100, 33, 64, 129), "B": (37, 88, 50, 112, 41, 65), "C": (90, 47, 130, 36, 80, 52),
+           "D": (150, 33, 97, 64, 200, 41)}
 
 
 def _requests(name):
@@ -43,7 +44,7 @@ def _check(name, dtype, reqs, got, tag):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_each_request_alone_and_whole(name, dtype):
     reqs = _requests(name)
     got, _ = _replay(name, dtype, helpers.trace_whole(reqs))
@@ -51,7 +52,7 @@ def test_each_request_alone_and_whole(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_last_32_tokens_one_by_one(name, dtype):
     reqs = _requests(name)
     got, _ = _replay(name, dtype, helpers.trace_decode_tail(reqs))
@@ -59,7 +60,7 @@ def test_last_32_tokens_one_by_one(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_changing_size(name, dtype):
     reqs = _requests(name)
     got, _ = _replay(name, dtype, helpers.trace_portions(reqs))
@@ -67,7 +68,7 @@ def test_portions_of_changing_size(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_batches_with_pages_used_again(name, dtype):
     reqs = _requests(name) + _requests(name)[:3]
     steps = helpers.trace_mixed(reqs, max_live=4, seed=3)

@@ -24,4 +24,11 @@ TINY_C = _cfg(hidden_size=72, num_hidden_layers=4, num_attention_heads=6, num_ke
               tie_word_embeddings=False, use_sliding_window=True, sliding_window=24,
               layer_types=["full_attention", "sliding_attention", "full_attention", "sliding_attention"])
 
-ALL = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}   # config, seed, page size
+# 2 layers, 6/2 heads (groups of 3), head_dim 64: the head size the bfloat16 tensor-core attention takes; a window
+# of 40 keys on layer 1; pages of 32
+TINY_D = _cfg(hidden_size=80, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2,
+              head_dim=64, intermediate_size=176, vocab_size=300, rope_theta=20000.0, rms_norm_eps=2e-6,
+              tie_word_embeddings=True, use_sliding_window=True, sliding_window=40,
+              layer_types=["full_attention", "sliding_attention"])
+
+ALL = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16), "D": (TINY_D, 3, 32)}   # config, seed, page size
