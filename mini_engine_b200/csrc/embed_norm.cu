@@ -28,11 +28,14 @@ ME_API int me_embed(const int* ids, const void* table, int table_dtype, float* o
   return 0;
 }
 
-// One block per output row.  Both passes read res (+ delta); the second writes.
+// One block per output row.  Both passes read res (+ delta); the second writes.  ``delta`` may
+// come as ``splits`` partial results (a split-K product), each ``split_stride`` elements apart;
+// they are added in order.
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ res, const TD* __restrict__ delta,
                                    const float* __restrict__ w, float eps, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int H, int write_res) {
+                                   const int* __restrict__ rows, int H, int write_res, int splits,
+                                   int64_t split_stride) {
   __shared__ float red[32];
   const int r_out = blockIdx.x;
   const int64_t r = rows ? rows[r_out] : r_out;
@@ -41,7 +44,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const TD* __restrict
   float ss = 0.f;
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     float v = rr[h];
-    if (dd) v += to_f<TD>(dd[h]);
+    if (dd) {
+      float d = to_f<TD>(dd[h]);
+      for (int s = 1; s < splits; ++s) d += to_f<TD>(dd[h + s * split_stride]);
+      v += d;
+    }
     ss += v * v;
   }
   ss = block_sum(ss, red);
@@ -49,22 +56,26 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const TD* __restrict
   TO* oo = out + (int64_t)r_out * H;
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     float v = rr[h];
-    if (dd) v += to_f<TD>(dd[h]);
+    if (dd) {
+      float d = to_f<TD>(dd[h]);
+      for (int s = 1; s < splits; ++s) d += to_f<TD>(dd[h + s * split_stride]);
+      v += d;
+    }
     if (write_res) rr[h] = v;
     oo[h] = from_f<TO>((v * inv) * w[h]);
   }
 }
 
 ME_API int me_add_rmsnorm(float* res, const void* delta, int delta_dtype, const float* w, float eps,
-                          void* out, int out_dtype, const int* rows, int n_rows, int H,
-                          cudaStream_t stream) {
+                          void* out, int out_dtype, const int* rows, int n_rows, int H, int splits,
+                          int64_t split_stride, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  ME_REQUIRE(n_rows > 0 && H > 0, "me_add_rmsnorm: bad sizes rows=%d H=%d", n_rows, H);
+  ME_REQUIRE(n_rows > 0 && H > 0 && splits >= 1, "me_add_rmsnorm: bad sizes rows=%d H=%d splits=%d", n_rows, H, splits);
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : (H >= 128 ? 128 : 64));
   const int write_res = rows == nullptr;     // gathered rows leave the residual as it is
   ME_DISPATCH_DTYPE(delta_dtype, TD, ME_DISPATCH_DTYPE(out_dtype, TO,
       (add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(
-          res, (const TD*)delta, w, eps, (TO*)out, rows, H, write_res))));
+          res, (const TD*)delta, w, eps, (TO*)out, rows, H, write_res, splits, split_stride))));
   ME_LAUNCH_CHECK("me_add_rmsnorm");
   return 0;
 }

@@ -114,7 +114,7 @@ class ModelRunner:
         # A decode step is replayed from a graph only if every part of the model allows it.
         self.use_cuda_graphs = (use_cuda_graphs and self.device.type == "cuda"
                                 and all(part.capturable for _, part in self.model.walk()))
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256) if b <= max_num_seqs]
         self.sample_tokens = torch.empty(max(max_num_seqs, 1), dtype=torch.int32, device=self.device)
         self.graph_launches = 0          # kernels replayed from graphs (they bypass ops.launches)
@@ -366,10 +366,20 @@ class ModelRunner:
     def _step_graph(self, items: Sequence[StepItem], bucket: int, sample: bool) -> StepResult:
         """Decode-only steps replay a graph captured for the bucket: metadata goes to fixed device
         addresses, padding requests have no keys, write nowhere and their rows are ignored."""
-        g = self._graphs.get(bucket)
-        width = (self.max_model_len + self.page_size - 1) // self.page_size
+        # The graph's shape also fixes how many key partitions the attention kernel is launched for, so
+        # graphs are kept per context bucket (powers of two) as well: a short context does not pay for
+        # the longest one.
+        longest = max(it.start for it in items) + 1
+        ctx_bucket = 256
+        while ctx_bucket < longest:
+            ctx_bucket *= 2
+        ctx_bucket = min(ctx_bucket, (self.max_model_len + self.page_size - 1) // self.page_size * self.page_size)
+        if longest > ctx_bucket:
+            raise ValueError(f"a request is at position {longest - 1}, beyond max_model_len {self.max_model_len}")
+        width = (ctx_bucket + self.page_size - 1) // self.page_size
+        g = self._graphs.get((bucket, ctx_bucket))
         if g is None:
-            g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+            g = self._graphs[(bucket, ctx_bucket)] = _DecodeGraph(self, bucket)
             n = 16 * bucket + 64 + sum(4 * bucket + bucket * width + 8 for _ in self.groups)
             g.meta_dev = torch.zeros(n + 64, dtype=torch.int32, device=self.device)
         token_ids, _ = self.build_batch(items, g.ctx, pad_reqs=bucket, table_width=width, dev=g.meta_dev)

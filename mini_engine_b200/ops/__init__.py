@@ -22,7 +22,8 @@ MAX_HEAD_DIM = 256
 _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 _PROTOS = {
     "me_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
-    "me_add_rmsnorm": [_P, _P, _I, _P, _F, _P, _I, _P, _I, _I, _P],
+    "me_add_rmsnorm": [_P, _P, _I, _P, _F, _P, _I, _P, _I, _I, _I, _L, _P],
+    "me_gemm_skinny": [_P, _L, _P, _P, _I, _L, _P, _I, _I, _I, _I, _P],
     "me_silu_mul": [_P, _P, _I, _I, _I, _P],
     "me_gemm_simt": [_P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P],
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
@@ -59,6 +60,7 @@ def require_extension() -> ctypes.CDLL:
         raise KernelError("the kernel library and ops/__init__.py disagree on tile sizes")
     lib.me_attn_prefill_heads_per_block.argtypes = [_I, _I, _I]
     lib.me_sample_chunks.argtypes = [_I]
+    lib.me_gemm_skinny_splits.argtypes = [_I]
     _lib = lib
     return lib
 
@@ -118,18 +120,24 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
     """``residual += delta`` (float32, in place), ``out = rmsnorm(residual) * weight``; with ``rows``
-    only those rows are read and ``residual`` is not written."""
+    only those rows are read and ``residual`` is not written.  A 3-D ``delta`` [splits, T, H] holds the
+    partial results of a split-K product; they are added in order."""
     H = residual.shape[1]
     _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_rmsnorm: residual must be float32")
     _need(weight.dtype == torch.float32 and weight.shape == (H,), "add_rmsnorm: weight must be float32 [H]")
     n = residual.shape[0] if rows is None else rows.shape[0]
     _need(out.is_contiguous() and tuple(out.shape) == (n, H), "add_rmsnorm: output shape")
+    splits, stride = 1, 0
     if delta is not None:
-        _need(delta.is_contiguous() and delta.shape == residual.shape, "add_rmsnorm: delta shape")
+        if delta.dim() == 3:                      # partial results of a split-K product: [splits, T, H]
+            splits, stride = delta.shape[0], delta.stride(0)
+            _need(delta.is_contiguous() and tuple(delta.shape[1:]) == tuple(residual.shape), "add_rmsnorm: delta shape")
+        else:
+            _need(delta.is_contiguous() and delta.shape == residual.shape, "add_rmsnorm: delta shape")
     if rows is not None:
         _need(rows.dtype == torch.int32 and rows.is_contiguous(), "add_rmsnorm: rows must be int32")
     _call("me_add_rmsnorm", residual.data_ptr(), _ptr(delta), _dt(delta) if delta is not None else 0,
-          weight.data_ptr(), float(eps), out.data_ptr(), _dt(out), _ptr(rows), n, H, _stream())
+          weight.data_ptr(), float(eps), out.data_ptr(), _dt(out), _ptr(rows), n, H, splits, stride, _stream())
 
 
 def silu_mul(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -141,6 +149,31 @@ def silu_mul(x: torch.Tensor, out: torch.Tensor) -> None:
 
 # ---- matrix products ----------------------------------------------------------------------
 library_calls = 0         # cuBLAS products issued through torch (not counted as this package's kernels)
+
+
+SKINNY_MAX_ROWS = 16      # rows up to which bfloat16 products run csrc/gemm_skinny.cu
+
+
+def skinny_splits(M: int, K: int, x: torch.Tensor, weight: torch.Tensor) -> int:
+    """How many float32 partial results the small-batch kernel would leave for this product
+    (0: the kernel does not take it; 1: it writes the result itself)."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS
+            and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+        return 0
+    return (_lib or require_extension()).me_gemm_skinny_splits(K)
+
+
+def linear_partials(x: torch.Tensor, weight: torch.Tensor, workspace, name: str) -> Optional[torch.Tensor]:
+    """``x @ weight.T`` as float32 partial results [splits, M, N] of a split-K product, for a consumer that
+    adds them (``add_rmsnorm``); None when the product is not one the small-batch kernel splits."""
+    M, K = x.shape
+    splits = skinny_splits(M, K, x, weight)
+    if splits < 2:
+        return None
+    N = weight.shape[0]
+    part = workspace(name, (splits, M, N), torch.float32)
+    _call("me_gemm_skinny", x.data_ptr(), x.stride(0), weight.data_ptr(), 0, 0, 0, part.data_ptr(), M, N, K, 0, _stream())
+    return part
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "none",
@@ -160,6 +193,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
     N = weight.shape[0] // 2 if epi else weight.shape[0]
     _need(tuple(out.shape) == (M, N), f"linear: output is {tuple(out.shape)}, expected {(M, N)}")
     if M == 0:
+        return
+    if skinny_splits(M, K, x, weight) == 1 and (epi == 0 or out.dtype == torch.bfloat16):
+        _call("me_gemm_skinny", x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), _dt(out), out.stride(0),
+              0, M, N, K, epi, _stream())
         return
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.is_cuda:
         if epi == 0 and out.dtype == torch.bfloat16:

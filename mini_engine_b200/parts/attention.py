@@ -81,7 +81,7 @@ class GQAAttention(Mixer):
         ops.paged_attention(qkv, out, self.num_heads, self.num_kv_heads, self.head_dim,
                             kv.pool, kv.page_size, kv.block_tables, ctx.attn_meta,
                             self.scale, self.window)
-        return self.o_proj.forward(out, ctx, "mixer_out")
+        return self.o_proj.forward(out, ctx, "mixer_out", may_split=True)
 
 
 register_mixer("gqa_attention", GQAAttention)

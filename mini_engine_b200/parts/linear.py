@@ -37,7 +37,13 @@ class Linear(Part):
         return self.p(self.name)
 
     def forward(self, x: torch.Tensor, ctx, out_name: str, *, out_dtype: Optional[torch.dtype] = None,
-                epilogue: str = "none") -> torch.Tensor:
+                epilogue: str = "none", may_split: bool = False) -> torch.Tensor:
+        """``x W^T``.  With ``may_split`` the result may come as float32 partial results [splits, T, N] of a
+        split-K product; only a consumer that adds them (the next norm) may ask for that."""
+        if may_split and epilogue == "none":
+            part = ops.linear_partials(x, self.weight, ctx.buffer, out_name + "_partials")
+            if part is not None:
+                return part
         n_out = self.out_features // 2 if epilogue == "silu_mul" else self.out_features
         out = ctx.buffer(out_name, (x.shape[0], n_out), out_dtype or ctx.act_dtype)
         ops.linear(x, self.weight, out, epilogue=epilogue, workspace=ctx.buffer)

@@ -29,7 +29,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, ctx):
         act = self.gate_up_proj.forward(x, ctx, "ffn_act", epilogue="silu_mul")
-        return self.down_proj.forward(act, ctx, "ffn_out")
+        return self.down_proj.forward(act, ctx, "ffn_out", may_split=True)
 
 
 register_feed_forward("swiglu", SwiGLU)

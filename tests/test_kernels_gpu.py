@@ -103,6 +103,49 @@ def test_linear_silu_mul(ops, M, I, K, dt):
     close(out, ref, DT[dt], scale=4)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 16])
+@pytest.mark.parametrize("N, K", [(96, 64), (1000, 200), (4096, 1024), (1024, 2048), (1030, 3072), (200, 4096 + 72)])
+def test_small_batch_products(ops, M, N, K):
+    # the decode kernel: bfloat16 and float32 results, split-K partial results, SiLU-and-multiply
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5)
+    splits = ops.skinny_splits(M, K, x, w)
+    assert splits == (K + 1023) // 1024
+    ref = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    plain_ops.linear(x, w, ref)
+    ws = {}
+
+    def workspace(name, shape, dt):
+        return ws.setdefault(name, torch.full(tuple(shape), float("nan"), dtype=dt, device=DEV))
+    part = ops.linear_partials(x, w, workspace, "p")
+    if splits == 1:
+        assert part is None
+        for od in (torch.bfloat16, torch.float32):
+            before = ops.library_calls
+            out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
+            ops.linear(x, w, out)
+            assert ops.library_calls == before                     # our kernel, not the library
+            close(out, ref, od, scale=4)
+    else:
+        assert part.shape == (splits, M, N) and part.dtype == torch.float32
+        close(part.sum(0), ref, torch.float32, scale=50)            # bfloat16 inputs, float32 sums
+        res = rnd(M, N, seed=5)
+        wn = 1 + 0.1 * rnd(N, seed=6)
+        out, ref_out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV), torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        res2 = res.clone()
+        ops.add_rmsnorm(res, part, wn, 1e-6, out)
+        plain_ops.add_rmsnorm(res2, part, wn, 1e-6, ref_out)
+        assert torch.allclose(res, res2, atol=1e-5)
+        close(out, ref_out, torch.bfloat16, scale=4)
+    if K <= 1024 and N % 2 == 0:
+        I = N // 2
+        out, ref2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV), torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+        before = ops.library_calls
+        ops.linear(x, w, out, epilogue="silu_mul", workspace=workspace)
+        assert ops.library_calls == before
+        plain_ops.linear(x, w, ref2, epilogue="silu_mul")
+        close(out, ref2, torch.bfloat16, scale=4)
+
+
 def test_linear_rows_do_not_depend_on_the_batch(ops):
     x, w = rnd(70, 96, seed=1), rnd(224, 96, seed=2)
     full, one = torch.empty(70, 224, device=DEV), torch.empty(1, 224, device=DEV)
