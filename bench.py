@@ -58,6 +58,7 @@ def parse_args():
     p.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                    help="run one part only (small runs for profilers); the JSON line then holds that part")
     p.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
+    p.add_argument("--no-pdl", action="store_true", help="launch kernels without programmatic dependent launch")
     p.add_argument("--seed", type=int, default=0)
     # the reference's own options (its bench.py:8-19), used by --mode offline
     p.add_argument("--model", default="", help="model folder; empty: random weights of the 0.6B shape")
@@ -267,7 +268,9 @@ def prefill_on_device(runner, cache, prompt, reps: int, warmup: int):
 
 def run_step_mode(args) -> int:
     import torch
-    from mini_engine_b200 import LLM
+    from mini_engine_b200 import LLM, ops
+    if args.no_pdl:
+        ops.set_programmatic_launch(False)
     cfg = dict(QWEN3_0_6B)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:

@@ -26,6 +26,8 @@ attn_chunk_kernel(const T* __restrict__ qkv, int64_t q_row_stride, T* __restrict
                   const int* __restrict__ tiles, int nh, int nkv, int hd, int page_size,
                   float scale, int window) {
   extern __shared__ float smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   const int ldh = hd + 1;
   float* Qs = smem;                          // [ATT_BQ][ldh]
   float* Ks = Qs + ATT_BQ * ldh;             // [ATT_BK][ldh]
@@ -146,7 +148,7 @@ ME_API int me_attn_chunk(const void* qkv, int dtype, int64_t q_row_stride, void*
       ME_REQUIRE(e == cudaSuccess, "me_attn_chunk: cannot raise shared memory: %s", cudaGetErrorString(e));
       attr_set = true;
     }
-    attn_chunk_kernel<T><<<grid, ATT_THREADS, smem, stream>>>(
+    me_launch(attn_chunk_kernel<T>, grid, dim3(ATT_THREADS), smem, stream,
         (const T*)qkv, q_row_stride, (T*)out, out_row_stride, (const T*)pool, block_tables, bt_stride,
         cu_seqlens, context_lens, tiles, nh, nkv, hd, page_size, scale, window);
   });

@@ -13,6 +13,7 @@
 // group size, any page size, optional window (keys j > position - window).
 #include "common.cuh"
 #include "mma_prims.cuh"
+#include "tma.cuh"
 
 constexpr int DEC_PART = 128, DEC_THREADS = 128, DEC_LANES = 8, DEC_GROUPS = DEC_THREADS / DEC_LANES;
 
@@ -47,6 +48,8 @@ decode_partition_kernel(const T* __restrict__ qkv, int64_t q_row_stride, const T
                         float* __restrict__ tmp_out, float* __restrict__ tmp_m,
                         float* __restrict__ tmp_l, int max_parts) {
   extern __shared__ float smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   const int G = nh / nkv, head_tiles = (G + GT - 1) / GT;
   const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * GT;
   const int z = blockIdx.z;
@@ -200,6 +203,8 @@ decode_partition_tma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, 
                             float* __restrict__ tmp_l, int max_parts, int* __restrict__ err) {
   extern __shared__ __align__(128) unsigned char dec_smem[];
   __shared__ __align__(8) unsigned long long bars[DEC_STAGES];
+  pdl_wait();
+  pdl_launch_dependents();
   const int G = nh / nkv, head_tiles = (G + GT - 1) / GT;
   const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * GT;
   const int z = blockIdx.z;
@@ -388,7 +393,7 @@ static int launch_partition_tma(dim3 grid, cudaStream_t stream, const void* qkv,
     ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr = smem;
   }
-  decode_partition_tma_kernel<GT, CH><<<grid, DEC_THREADS, smem, stream>>>(
+  me_launch(decode_partition_tma_kernel<GT, CH>, grid, dim3(DEC_THREADS), smem, stream,
       (const bf16*)qkv, q_row_stride, (const bf16*)pool, bt, bt_stride, cu, cl, nh, nkv, hd, page_size, scale, window,
       to, tm, tl, max_parts, err);
   return 0;
@@ -422,6 +427,8 @@ decode_partition_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, 
   const int part_lo = z * DEC_PART, part_hi = min(L, part_lo + DEC_PART);
   const int64_t slot0 = ((int64_t)b * nh + kvh * G + g0) * max_parts + z;
   if (part_hi <= part_lo || part_hi <= lo_w) {
+    pdl_wait();
+    pdl_launch_dependents();
     if (part_lo < L || z == 0)
       for (int r = tid; r < n_g; r += DEC_THREADS) {
         tmp_m[slot0 + (int64_t)r * max_parts] = -INFINITY;
@@ -434,32 +441,46 @@ decode_partition_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, 
   bf16* vs = ks + DEC_PART * HD;                     // [128][HD]
   const int* bt = block_tables + (int64_t)b * bt_stride;
   const int64_t tok = cu_seqlens[b];
-  for (int c = tid; c < 16 * PIECES; c += DEC_THREADS) {
+  // Only the partition that holds the request's newest key depends on the kernel before this one (which
+  // wrote that key); the others fetch their keys and values while that kernel is still running.
+  const bool has_new = part_hi == L;
+  // Thread t copies piece (t % PIECES) of rows (t / PIECES) + k * (128 / PIECES); the rows' places in the
+  // pool are looked up once and serve both K (first group) and V (second group).
+  const int64_t v_off = (int64_t)nkv * page_size * HD;
+  const PageMap pm{bt, page_size, log2_if_pow2(page_size), 2 * v_off, (int64_t)kvh * page_size * HD, HD};
+  constexpr int ROWS_PER_PASS = DEC_THREADS / PIECES, PASSES = DEC_PART / ROWS_PER_PASS;
+  const int piece = tid % PIECES, r0 = tid / PIECES;
+  int64_t base[PASSES];
+#pragma unroll
+  for (int k = 0; k < PASSES; ++k) {
+    const int j = part_lo + r0 + k * ROWS_PER_PASS;
+    base[k] = (j < part_hi && j >= lo_w) ? pm.row(j) : -1;
+  }
+  if (has_new) {
+    pdl_wait();
+    pdl_launch_dependents();
+  }
+#pragma unroll
+  for (int k = 0; k < PASSES; ++k)
+    cp_async16(tile_ptr<HD>(ks, r0 + k * ROWS_PER_PASS, piece), base[k] >= 0 ? pool + base[k] + piece * 8 : pool, base[k] >= 0);
+  cp_async_commit();
+#pragma unroll
+  for (int k = 0; k < PASSES; ++k)
+    cp_async16(tile_ptr<HD>(vs, r0 + k * ROWS_PER_PASS, piece), base[k] >= 0 ? pool + base[k] + v_off + piece * 8 : pool,
+               base[k] >= 0);
+  cp_async_commit();
+  if (!has_new) {
+    pdl_wait();
+    pdl_launch_dependents();
+  }
+  for (int c = tid; c < 16 * PIECES; c += DEC_THREADS) {       // q is written by the kernel before this one
     const int row = c / PIECES, piece = c % PIECES;
     const bool ok = row < n_g;
     cp_async16(tile_ptr<HD>(qs, row, piece),
                ok ? qkv + tok * q_row_stride + (int64_t)(kvh * G + g0 + row) * HD + piece * 8 : qkv, ok);
   }
-  const int64_t v_off = (int64_t)nkv * page_size * HD;
-#pragma unroll 1
-  for (int which = 0; which < 2; ++which) {          // K first, then V, each its own group
-    bf16* dst = which ? vs : ks;
-    for (int c = tid; c < DEC_PART * PIECES; c += DEC_THREADS) {
-      const int row = c / PIECES, piece = c % PIECES;
-      const int j = part_lo + row;
-      bool ok = j < part_hi && j >= lo_w;
-      const bf16* src = pool;
-      if (ok) {
-        const int page = bt[j / page_size];
-        ok = page >= 0;
-        if (ok) src = pool + (((int64_t)page * 2) * nkv + kvh) * page_size * HD + (int64_t)(j % page_size) * HD + piece * 8 +
-                      (which ? v_off : 0);
-      }
-      cp_async16(tile_ptr<HD>(dst, row, piece), src, ok);
-    }
-    cp_async_commit();
-  }
-  cp_async_wait<1>();
+  cp_async_commit();
+  cp_async_wait<0>();
   __syncthreads();
   const float sl2 = scale * 1.4426950408889634f;
   const int mi = lane >> 3;
@@ -509,8 +530,7 @@ decode_partition_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, 
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  cp_async_wait<0>();
-  __syncthreads();                                   // V has landed; every warp is done reading K
+  __syncthreads();                                   // every warp is done reading K
   float o[NT_O][4];
 #pragma unroll
   for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -575,9 +595,231 @@ static int launch_partition_mma(int num_reqs, int max_parts, cudaStream_t stream
   }
   const int G = nh / nkv;
   dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
-  decode_partition_mma_kernel<HD><<<grid, DEC_THREADS, smem, stream>>>(
+  me_launch(decode_partition_mma_kernel<HD>, grid, dim3(DEC_THREADS), smem, stream,
       (const bf16*)qkv, q_row_stride, (const bf16*)pool, bt, bt_stride, cu, cl, nh, nkv, page_size, scale, window, to, tm, tl,
       max_parts);
+  return 0;
+}
+
+// ---- the tensor-core partition step fed by tensor-map loads ------------------------------------------
+// As above, but K and V come by TMA: the pool of one cache slot is a 2-D tensor [pages * 2 * kv_heads *
+// page_size][head_dim]; a box is one page of one head, 64 columns wide, written with the 128-byte swizzle
+// that ldmatrix wants.  One thread issues every box of the partition (K on one mbarrier, V on another),
+// so the block has its 64 KB in flight as a few dozen requests instead of four thousand 16-byte copies.
+// Rows of V that are not keys of the request (a page's tail, keys behind the window) are zeroed before
+// P V, because 0 * (whatever the page holds there) must be 0.  Page sizes that divide 128.
+template <int HD>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ qkv,
+                                int64_t q_row_stride, const int* __restrict__ block_tables, int bt_stride,
+                                const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
+                                int nh, int nkv, int page_size, float scale, int window,
+                                float* __restrict__ tmp_out, float* __restrict__ tmp_m,
+                                float* __restrict__ tmp_l, int max_parts, int* __restrict__ err) {
+  using namespace mma_prims;
+  extern __shared__ unsigned char dec_smem_raw[];
+  __shared__ float w_m[4][16], w_l[4][16];
+  __shared__ __align__(8) unsigned long long bar_k, bar_v;
+  constexpr int PIECES = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, HALVES = HD / 64;
+  const int G = nh / nkv, head_tiles = (G + 15) / 16;
+  const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * 16;
+  const int z = blockIdx.z;
+  const int L = context_lens[b];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  const int n_g = min(16, G - g0);
+  const int lo_w = window > 0 ? max(0, L - window) : 0;
+  const int part_lo = z * DEC_PART, part_hi = min(L, part_lo + DEC_PART);
+  const int64_t slot0 = ((int64_t)b * nh + kvh * G + g0) * max_parts + z;
+  if (part_hi <= part_lo || part_hi <= lo_w) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if (part_lo < L || z == 0)
+      for (int r = tid; r < n_g; r += DEC_THREADS) {
+        tmp_m[slot0 + (int64_t)r * max_parts] = -INFINITY;
+        tmp_l[slot0 + (int64_t)r * max_parts] = 0.f;
+      }
+    return;
+  }
+  // Shared memory from a 1024-byte boundary: K halves [HALVES][128][64], V halves, then Q [16][HD].
+  unsigned char* aligned = dec_smem_raw + ((1024u - (tma::smem_addr(dec_smem_raw) & 1023u)) & 1023u);
+  bf16* ks = reinterpret_cast<bf16*>(aligned);
+  bf16* vs = ks + DEC_PART * HD;
+  bf16* qs = vs + DEC_PART * HD;
+  const int* bt = block_tables + (int64_t)b * bt_stride;
+  const int64_t tok = cu_seqlens[b];
+  // Only the partition that holds the request's newest key depends on the kernel before this one (which
+  // wrote that key); the others fetch their keys and values while that kernel is still running.
+  const bool has_new = part_hi == L;
+  if (has_new) {
+    pdl_wait();
+    pdl_launch_dependents();
+  }
+  if (tid == 0) {
+    tma::mbar_init(&bar_k, 1);
+    tma::mbar_init(&bar_v, 1);
+    tma::mbar_fence_init();
+    const int n_pages = DEC_PART / page_size;
+    const unsigned box_bytes = (unsigned)page_size * 64 * sizeof(bf16);
+    int first_row[DEC_PART / 8];                       // row of the pool's 2-D view where each page's K starts
+    unsigned bytes = 0;
+    for (int i = 0; i < n_pages; ++i) {
+      const int j0 = part_lo + i * page_size;
+      int page = -1;
+      if (j0 < part_hi && j0 + page_size > lo_w) page = bt[j0 / page_size];
+      first_row[i] = page < 0 ? -1 : ((page * 2) * nkv + kvh) * page_size;
+      if (page >= 0) bytes += HALVES * box_bytes;
+    }
+    tma::mbar_expect_tx(&bar_k, bytes);
+    for (int i = 0; i < n_pages; ++i)
+      if (first_row[i] >= 0)
+        for (int h = 0; h < HALVES; ++h)
+          tma::load_2d(ks + h * DEC_PART * 64 + i * page_size * 64, &kv_map, h * 64, first_row[i], &bar_k);
+    tma::mbar_expect_tx(&bar_v, bytes);
+    const int v_rows = nkv * page_size;
+    for (int i = 0; i < n_pages; ++i)
+      if (first_row[i] >= 0)
+        for (int h = 0; h < HALVES; ++h)
+          tma::load_2d(vs + h * DEC_PART * 64 + i * page_size * 64, &kv_map, h * 64, first_row[i] + v_rows, &bar_v);
+  }
+  if (!has_new) {
+    pdl_wait();
+    pdl_launch_dependents();
+  }
+  for (int c = tid; c < 16 * PIECES; c += DEC_THREADS) {       // q is written by the kernel before this one
+    const int row = c / PIECES, piece = c % PIECES;
+    const bool ok = row < n_g;
+    cp_async16(tile_ptr<HD>(qs, row, piece),
+               ok ? qkv + tok * q_row_stride + (int64_t)(kvh * G + g0 + row) * HD + piece * 8 : qkv, ok);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();                                   // barriers initialised, Q in place
+  bool landed = tma::mbar_wait(&bar_k, 0);
+  const float sl2 = scale * 1.4426950408889634f;
+  const int mi = lane >> 3;
+  float s[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+    uint32_t qf[4];
+    ldmatrix_x4(qf, tile_ptr<HD>(qs, (mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
+#pragma unroll
+    for (int np = 0; np < 2; ++np) {
+      uint32_t bfr[4];
+      const int piece = kk * 2 + (mi & 1);
+      ldmatrix_x4(bfr, tma::swz128(ks + (piece >> 3) * DEC_PART * 64, warp * 32 + np * 16 + (mi >> 1) * 8 + (lane & 7), piece & 7));
+      mma_bf16(s[2 * np], qf, bfr[0], bfr[1]);
+      mma_bf16(s[2 * np + 1], qf, bfr[2], bfr[3]);
+    }
+  }
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int j = part_lo + warp * 32 + i * 8 + 2 * t4 + e;
+      if (j >= part_hi || j < lo_w) s[i][e] = s[i][e + 2] = -INFINITY;
+    }
+    mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mu0 = mx0 == -INFINITY ? 0.f : mx0, mu1 = mx1 == -INFINITY ? 0.f : mx1;
+  float l0 = 0.f, l1 = 0.f;
+  uint32_t pf[2][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float p0 = exp2f((s[i][0] - mu0) * sl2), p1 = exp2f((s[i][1] - mu0) * sl2);
+    const float p2 = exp2f((s[i][2] - mu1) * sl2), p3 = exp2f((s[i][3] - mu1) * sl2);
+    l0 += p0 + p1;
+    l1 += p2 + p3;
+    pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+    pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  landed = tma::mbar_wait(&bar_v, 0) && landed;
+  {                                                  // rows of V that are no keys of this request: zero
+    const int j = part_lo + tid;                     // 128 threads, 128 rows
+    if (j >= part_hi || j < lo_w)
+      for (int p = 0; p < PIECES; ++p)
+        *reinterpret_cast<uint4*>(tma::swz128(vs + (p >> 3) * DEC_PART * 64, tid, p & 7)) = make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();                                   // V complete and cleaned; every warp is done reading K
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+    for (int np = 0; np < NT_O / 2; ++np) {
+      uint32_t bfr[4];
+      const int piece = np * 2 + (mi >> 1);
+      ldmatrix_x4_trans(bfr, tma::swz128(vs + (piece >> 3) * DEC_PART * 64, warp * 32 + kk * 16 + (mi & 1) * 8 + (lane & 7), piece & 7));
+      mma_bf16(o[2 * np], pf[kk], bfr[0], bfr[1]);
+      mma_bf16(o[2 * np + 1], pf[kk], bfr[2], bfr[3]);
+    }
+  }
+  float* po = reinterpret_cast<float*>(ks);          // [4][16][HD] float32, over the K tile
+  if (t4 == 0) {
+    w_m[warp][g] = mx0;
+    w_l[warp][g] = l0;
+    w_m[warp][g + 8] = mx1;
+    w_l[warp][g + 8] = l1;
+  }
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) {
+    if (g < n_g) *reinterpret_cast<float2*>(po + ((warp * 16 + g) * HD + i * 8 + 2 * t4)) = make_float2(o[i][0], o[i][1]);
+    if (g + 8 < n_g) *reinterpret_cast<float2*>(po + ((warp * 16 + g + 8) * HD + i * 8 + 2 * t4)) = make_float2(o[i][2], o[i][3]);
+  }
+  __syncthreads();
+  if (!landed && tid == 0) atomicOr(err + 1, 1);     // a load did not land in time: the result is reported as invalid
+  for (int idx = tid; idx < n_g * HD; idx += DEC_THREADS) {
+    const int r = idx / HD, d = idx - r * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, w_m[w][r]);
+    float lt = 0.f, acc = 0.f;
+    if (M > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = w_m[w][r];
+        const float f = mw == -INFINITY ? 0.f : exp2f((mw - M) * sl2);
+        lt += f * w_l[w][r];
+        acc += f * po[(w * 16 + r) * HD + d];
+      }
+    }
+    const int64_t slot = slot0 + (int64_t)r * max_parts;
+    tmp_out[slot * HD + d] = acc;
+    if (d == 0) {
+      tmp_m[slot] = M == -INFINITY ? -INFINITY : M * scale;
+      tmp_l[slot] = lt;
+    }
+  }
+}
+
+template <int HD>
+static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_parts, cudaStream_t stream, const void* qkv,
+                                    int64_t q_row_stride, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
+                                    int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int* err) {
+  const size_t smem = (size_t)(16 + 2 * DEC_PART) * HD * sizeof(bf16) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const int G = nh / nkv;
+  dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
+  me_launch(decode_partition_tma_mma_kernel<HD>, grid, dim3(DEC_THREADS), smem, stream,
+      *reinterpret_cast<const CUtensorMap*>(kv_map), (const bf16*)qkv, q_row_stride, bt, bt_stride, cu, cl, nh, nkv, page_size,
+      scale, window, to, tm, tl, max_parts, err);
   return 0;
 }
 
@@ -587,6 +829,8 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
                                     const int* __restrict__ context_lens,
                                     const float* __restrict__ tmp_out, const float* __restrict__ tmp_m,
                                     const float* __restrict__ tmp_l, int nh, int hd, int max_parts) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y;
   const int L = context_lens[b];
   const int P = max(1, min(max_parts, (L + DEC_PART - 1) / DEC_PART));
@@ -618,7 +862,7 @@ static void launch_partition(dim3 grid, size_t smem, cudaStream_t stream, const 
                              int64_t q_row_stride, const void* pool, const int* bt, int bt_stride,
                              const int* cu, const int* cl, int nh, int nkv, int hd, int page_size,
                              float scale, int window, float* to, float* tm, float* tl, int max_parts) {
-  decode_partition_kernel<T, GT, CH><<<grid, DEC_THREADS, smem, stream>>>(
+  me_launch(decode_partition_kernel<T, GT, CH>, grid, dim3(DEC_THREADS), smem, stream,
       (const T*)qkv, q_row_stride, (const T*)pool, bt, bt_stride, cu, cl, nh, nkv, hd, page_size, scale,
       window, to, tm, tl, max_parts);
 }
@@ -628,7 +872,7 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
                           int bt_stride, const int* cu_seqlens, const int* context_lens,
                           int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
                           int window, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts,
-                          int* err, int kind, cudaStream_t stream) {
+                          int* err, int kind, const void* kv_map, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   ME_REQUIRE(hd % 8 == 0 && hd >= 8 && hd <= 256, "me_attn_decode: head_dim %d is not a multiple of 8 up to 256", hd);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "me_attn_decode: %d heads, %d kv heads", nh, nkv);
@@ -644,14 +888,24 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   dim3 grid(num_reqs, nkv * head_tiles, max_parts);
   const size_t smem = sizeof(float) * ((size_t)GT * hd + 2 * DEC_GROUPS * GT + (size_t)DEC_GROUPS * GT * hd);
   // kind: 0 = the fastest kernel that takes the shape, 1 = CUDA cores, 2 = CUDA cores fed by bulk copies,
-  // 3 = tensor cores.
+  // 3 = tensor cores fed by cp.async, 4 = tensor cores fed by tensor-map loads (needs ``kv_map``, made by
+  // me_tma_encode_2d over the cache slot: rows = pages * 2 * kv_heads * page_size, boxes page_size x 64).
   const bool mma_ok = dtype == ME_BF16 && (hd == 64 || hd == 128);
-  const bool tma_ok = dtype == ME_BF16 && hd <= 128 && err != nullptr &&
-                      (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
-  ME_REQUIRE(kind >= 0 && kind <= 3 && (kind != 3 || mma_ok) && (kind != 2 || tma_ok),
+  const bool tma_mma_ok = mma_ok && kv_map != nullptr && err != nullptr && page_size >= 8 && DEC_PART % page_size == 0;
+  const bool bulk_ok = dtype == ME_BF16 && hd <= 128 && err != nullptr &&
+                       (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
+  ME_REQUIRE(kind >= 0 && kind <= 4 && (kind != 4 || tma_mma_ok) && (kind != 3 || mma_ok) && (kind != 2 || bulk_ok),
              "me_attn_decode: kernel kind %d does not take this shape", kind);
-  const bool mma = kind == 3 || (kind == 0 && mma_ok);
+  const bool tma_mma = kind == 4 || (kind == 0 && tma_mma_ok);
+  const bool mma = !tma_mma && (kind == 3 || (kind == 0 && mma_ok));
   const bool tma = kind == 2;
+  if (tma_mma) {
+    int rc = hd == 64 ? launch_partition_tma_mma<64>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                                                     cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err)
+                      : launch_partition_tma_mma<128>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                                                      cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err);
+    if (rc) return rc;
+  }
   if (mma) {
     ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode: too many heads");
     int rc = hd == 64 ? launch_partition_mma<64>(num_reqs, max_parts, stream, qkv, q_row_stride, pool, block_tables, bt_stride,
@@ -660,8 +914,9 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
                                                   cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l);
     if (rc) return rc;
   }
+  const bool simt = !tma_mma && !mma;
 #define ME_DEC_TMA_CASE(GT_, CH_)                                                                   \
-  if (tma && !mma && GT == GT_ && CH == CH_) {                                                              \
+  if (simt && tma && GT == GT_ && CH == CH_) {                                                              \
     int rc = launch_partition_tma<GT_, CH_>(grid, stream, qkv, q_row_stride, pool, block_tables,    \
         bt_stride, cu_seqlens, context_lens, nh, nkv, hd, page_size, scale, window, tmp_out, tmp_m, \
         tmp_l, max_parts, err);                                                                     \
@@ -671,7 +926,7 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   ME_DEC_TMA_CASE(1, 2) ME_DEC_TMA_CASE(2, 2) ME_DEC_TMA_CASE(4, 2)
 #undef ME_DEC_TMA_CASE
 #define ME_DEC_CASE(GT_, CH_)                                                                       \
-  if (!tma && !mma && GT == GT_ && CH == CH_) {                                                             \
+  if (simt && !tma && GT == GT_ && CH == CH_) {                                                             \
     ME_DISPATCH_DTYPE(dtype, T, (launch_partition<T, GT_, CH_>(grid, smem, stream, qkv, q_row_stride, \
         pool, block_tables, bt_stride, cu_seqlens, context_lens, nh, nkv, hd, page_size, scale,     \
         window, tmp_out, tmp_m, tmp_l, max_parts)));                                                \
@@ -683,7 +938,7 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   ME_LAUNCH_CHECK("me_attn_decode (partitions)");
   dim3 mgrid(num_reqs, nh);
   const int mthreads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
-  ME_DISPATCH_DTYPE(dtype, T, (decode_merge_kernel<T><<<mgrid, mthreads, 0, stream>>>(
+  ME_DISPATCH_DTYPE(dtype, T, (me_launch(decode_merge_kernel<T>, mgrid, dim3(mthreads), 0, stream,
       (T*)out, out_row_stride, cu_seqlens, context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts)));
   ME_LAUNCH_CHECK("me_attn_decode (merge)");
   return 0;

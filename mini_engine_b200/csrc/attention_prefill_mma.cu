@@ -19,21 +19,19 @@ using namespace mma_prims;
 
 constexpr int PF_ROWS = 64, PF_KEYS = 64, PF_THREADS = 128;
 
+// Thread t copies piece (t % PIECES) of rows (t / PIECES) + k * (128 / PIECES): its piece and its swizzle
+// term are the same for all its rows, so the loop is one table lookup and two copies per row.
 template <int HD>
-__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const bf16* __restrict__ pool, const int* __restrict__ bt,
-                                             int kt, int hi, int kvh, int nkv, int page_size) {
-  constexpr int PIECES = HD / 8;
-  const int64_t v_off = (int64_t)nkv * page_size * HD;
-  for (int c = threadIdx.x; c < PF_KEYS * PIECES; c += PF_THREADS) {
-    const int row = c / PIECES, piece = c % PIECES;
+__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const bf16* __restrict__ pool, const PageMap& pm,
+                                             int64_t v_off, int kt, int hi) {
+  constexpr int PIECES = HD / 8, ROWS_PER_PASS = PF_THREADS / PIECES;
+  const int piece = threadIdx.x % PIECES, r0 = threadIdx.x / PIECES;
+#pragma unroll
+  for (int row = r0; row < PF_KEYS; row += ROWS_PER_PASS) {
     const int j = kt + row;
-    bool ok = j < hi;
-    const bf16* src = pool;
-    if (ok) {
-      const int page = bt[j / page_size];
-      ok = page >= 0;
-      if (ok) src = pool + (((int64_t)page * 2) * nkv + kvh) * page_size * HD + (int64_t)(j % page_size) * HD + piece * 8;
-    }
+    const int64_t base = j < hi ? pm.row(j) : -1;
+    const bool ok = base >= 0;
+    const bf16* src = ok ? pool + base + piece * 8 : pool;
     cp_async16(tile_ptr<HD>(ks, row, piece), src, ok);
     cp_async16(tile_ptr<HD>(vs, row, piece), ok ? src + v_off : pool, ok);
   }
@@ -51,6 +49,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, bf16
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);          // [64][HD]
   bf16* kv = qs + PF_ROWS * HD;                           // 2 x (K [64][HD], V [64][HD])
   constexpr int PIECES = HD / 8, KSTEPS = HD / 16, NT_S = PF_KEYS / 8, NT_O = HD / 8;
+  pdl_wait();
+  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   const int G = nh / nkv, packs = G / gp, tq = PF_ROWS / gp;
@@ -59,7 +59,9 @@ attn_prefill_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, bf16
   const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0;
   const int L = context_lens[b], start = L - q_len;
   const int n_tok = min(tq, q_len - q0);                 // query tokens of this tile
-  const int* bt = block_tables + (int64_t)b * bt_stride;
+  const int64_t v_off = (int64_t)nkv * page_size * HD;
+  const PageMap pm{block_tables + (int64_t)b * bt_stride, page_size, log2_if_pow2(page_size), 2 * v_off,
+                   (int64_t)kvh * page_size * HD, HD};
 
   // Q tile: row r = token (r / gp), head (r % gp)
   for (int c = tid; c < PF_ROWS * PIECES; c += PF_THREADS) {
@@ -74,7 +76,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, bf16
   int lo = window > 0 ? max(0, p_lo - window + 1) : 0;
   lo = (lo / PF_KEYS) * PF_KEYS;
   const int n_tiles = (hi - lo + PF_KEYS - 1) / PF_KEYS;
-  load_kv_tile<HD>(kv, kv + PF_KEYS * HD, pool, bt, lo, hi, kvh, nkv, page_size);
+  load_kv_tile<HD>(kv, kv + PF_KEYS * HD, pool, pm, v_off, lo, hi);
   cp_async_commit();
 
   uint32_t qf[KSTEPS][4];
@@ -92,7 +94,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, bf16
     bf16* vs = ks + PF_KEYS * HD;
     if (it + 1 < n_tiles) {
       bf16* kn = kv + ((it + 1) & 1) * 2 * PF_KEYS * HD;
-      load_kv_tile<HD>(kn, kn + PF_KEYS * HD, pool, bt, kt + PF_KEYS, hi, kvh, nkv, page_size);
+      load_kv_tile<HD>(kn, kn + PF_KEYS * HD, pool, pm, v_off, kt + PF_KEYS, hi);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -216,7 +218,7 @@ int launch_prefill(const void* qkv, int64_t q_row_stride, void* out, int64_t out
     attr_set = true;
   }
   dim3 grid(num_tiles, nkv * (nh / nkv / gp));
-  attn_prefill_mma_kernel<HD><<<grid, PF_THREADS, smem, stream>>>(
+  me_launch(attn_prefill_mma_kernel<HD>, grid, dim3(PF_THREADS), smem, stream,
       (const bf16*)qkv, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)pool, block_tables, bt_stride, cu_seqlens,
       context_lens, tiles, nh, nkv, gp, page_size, scale * 1.4426950408889634f, window);
   return 0;

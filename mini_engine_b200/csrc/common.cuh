@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include <stdarg.h>
 #include <math.h>
+#include <utility>
 
 #define ME_API extern "C" __attribute__((visibility("default")))
 
@@ -65,6 +66,34 @@ __device__ __forceinline__ float block_sum(float x, float* red /* >= 32 floats o
   float total = 0.f;
   for (int w = 0; w < nwarps; ++w) total += red[w];
   return total;
+}
+
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// Every kernel is launched so that it may start while its predecessor in the stream is still running
+// (cudaLaunchAttributeProgrammaticStreamSerialization).  A kernel first fetches what no earlier kernel
+// of the step writes (weights, block tables), then calls pdl_wait(), which returns once the predecessor
+// has finished and its writes are visible, and only then touches activations or the cache; it writes
+// nothing before pdl_wait().  pdl_launch_dependents() lets the successor be scheduled.  In a launch
+// without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+bool me_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t me_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = me_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // Run `body` with T bound to the C type of a dtype code.

@@ -8,6 +8,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int V, int* __restrict__ err) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < V;
@@ -23,7 +25,7 @@ ME_API int me_embed(const int* ids, const void* table, int table_dtype, float* o
   ME_REQUIRE(T > 0 && H > 0 && V > 0, "me_embed: bad sizes T=%d H=%d V=%d", T, H, V);
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   ME_DISPATCH_DTYPE(table_dtype, TW,
-                    embed_kernel<TW><<<T, threads, 0, stream>>>(ids, (const TW*)table, out, H, V, err));
+                    me_launch(embed_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, (const TW*)table, out, H, V, err));
   ME_LAUNCH_CHECK("me_embed");
   return 0;
 }
@@ -37,6 +39,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const TD* __restrict
                                    const int* __restrict__ rows, int H, int write_res, int splits,
                                    int64_t split_stride) {
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int r_out = blockIdx.x;
   const int64_t r = rows ? rows[r_out] : r_out;
   float* rr = res + r * H;
@@ -66,22 +70,74 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const TD* __restrict
   }
 }
 
+// The same in one pass for rows of up to NV * blockDim elements: a thread keeps its NV sums in registers.
+template <typename TD, typename TO, int NV>
+__global__ void add_rmsnorm_regs_kernel(float* __restrict__ res, const TD* __restrict__ delta,
+                                        const float* __restrict__ w, float eps, TO* __restrict__ out,
+                                        const int* __restrict__ rows, int H, int write_res, int splits,
+                                        int64_t split_stride) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r_out = blockIdx.x;
+  const int64_t r = rows ? rows[r_out] : r_out;
+  float* rr = res + r * H;
+  const TD* dd = delta ? delta + r * H : nullptr;
+  float v[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int h = threadIdx.x + i * blockDim.x;
+    v[i] = 0.f;
+    if (h < H) {
+      v[i] = rr[h];
+      if (dd) {
+        float d = to_f<TD>(dd[h]);
+        for (int s = 1; s < splits; ++s) d += to_f<TD>(dd[h + s * split_stride]);
+        v[i] += d;
+      }
+      ss += v[i] * v[i];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* oo = out + (int64_t)r_out * H;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int h = threadIdx.x + i * blockDim.x;
+    if (h < H) {
+      if (write_res) rr[h] = v[i];
+      oo[h] = from_f<TO>((v[i] * inv) * w[h]);
+    }
+  }
+}
+
 ME_API int me_add_rmsnorm(float* res, const void* delta, int delta_dtype, const float* w, float eps,
                           void* out, int out_dtype, const int* rows, int n_rows, int H, int splits,
                           int64_t split_stride, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   ME_REQUIRE(n_rows > 0 && H > 0 && splits >= 1, "me_add_rmsnorm: bad sizes rows=%d H=%d splits=%d", n_rows, H, splits);
-  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : (H >= 128 ? 128 : 64));
   const int write_res = rows == nullptr;     // gathered rows leave the residual as it is
-  ME_DISPATCH_DTYPE(delta_dtype, TD, ME_DISPATCH_DTYPE(out_dtype, TO,
-      (add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(
-          res, (const TD*)delta, w, eps, (TO*)out, rows, H, write_res, splits, split_stride))));
+  constexpr int NV = 8;
+  if (H <= NV * 1024) {
+    int threads = ((H + NV - 1) / NV + 31) / 32 * 32;
+    if (threads < 64) threads = 64;
+    ME_DISPATCH_DTYPE(delta_dtype, TD, ME_DISPATCH_DTYPE(out_dtype, TO,
+        (me_launch(add_rmsnorm_regs_kernel<TD, TO, NV>, dim3(n_rows), dim3(threads), 0, stream,
+                   res, (const TD*)delta, w, eps, (TO*)out, rows, H, write_res, splits, split_stride))));
+  } else {
+    ME_DISPATCH_DTYPE(delta_dtype, TD, ME_DISPATCH_DTYPE(out_dtype, TO,
+        (me_launch(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(1024), 0, stream,
+                   res, (const TD*)delta, w, eps, (TO*)out, rows, H, write_res, splits, split_stride))));
+  }
   ME_LAUNCH_CHECK("me_add_rmsnorm");
   return 0;
 }
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int I) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int64_t t = i / I;
@@ -99,7 +155,7 @@ ME_API int me_silu_mul(const void* x, void* out, int dtype, int T, int I, cudaSt
   const int64_t blocks = (n + threads - 1) / threads;
   ME_REQUIRE(blocks < 2147483647LL, "me_silu_mul: too many elements");
   ME_DISPATCH_DTYPE(dtype, TT,
-                    silu_mul_kernel<TT><<<(unsigned)blocks, threads, 0, stream>>>((const TT*)x, (TT*)out, n, I));
+                    me_launch(silu_mul_kernel<TT>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const TT*)x, (TT*)out, n, I));
   ME_LAUNCH_CHECK("me_silu_mul");
   return 0;
 }

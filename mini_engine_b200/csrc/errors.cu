@@ -14,3 +14,8 @@ void me_set_error(const char* fmt, ...) {
 ME_API const char* me_last_error() { return g_error; }
 
 ME_API int me_abi_version() { return 1; }
+
+static bool g_pdl = true;
+bool me_pdl_enabled() { return g_pdl; }
+// Switch programmatic dependent launch on (default) or off for all later launches.
+ME_API void me_set_pdl(int on) { g_pdl = on != 0; }

@@ -17,6 +17,8 @@ gemm_simt_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict__ W
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   __shared__ float Us[EPI == 1 ? BK : 1][BN + 4];
+  pdl_wait();
+  pdl_launch_dependents();
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   float acc[4][4] = {}, acu[4][4] = {};
@@ -72,9 +74,9 @@ static int launch_simt(const void* A, int64_t lda, const void* W, void* C, int64
                        int K, int epi, cudaStream_t stream) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (epi == 0)
-    gemm_simt_kernel<TA, TW, TO, 0><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, (TO*)C, ldc, M, N, K);
+    me_launch(gemm_simt_kernel<TA, TW, TO, 0>, grid, dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, (TO*)C, ldc, M, N, K);
   else
-    gemm_simt_kernel<TA, TW, TO, 1><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, (TO*)C, ldc, M, N, K);
+    me_launch(gemm_simt_kernel<TA, TW, TO, 1>, grid, dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, (TO*)C, ldc, M, N, K);
   return 0;
 }
 

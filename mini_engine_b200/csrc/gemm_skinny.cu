@@ -37,12 +37,19 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int64_t ldx, const bf16* __restri
     return (int64_t)strip * 16 + r;
   };
   const int n_rows = EPI == 1 ? 2 * N : N;
+  // The weights do not depend on the kernel before this one: they are on their way before it has finished.
   for (int c = lane; c < 16 * SK_PIECES; c += 32) {
     const int row = c / SK_PIECES, piece = c % SK_PIECES;
     const int k = k0 + piece * 8;
     const int64_t wr = w_row(row);
     const bool okw = k < K && wr < n_rows && (EPI == 0 || strip * 8 + (row & 7) < N);
     cp_async16(sk_ptr(ws, row, piece), okw ? W + wr * K + k : W, okw);
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int c = lane; c < 16 * SK_PIECES; c += 32) {
+    const int row = c / SK_PIECES, piece = c % SK_PIECES;
+    const int k = k0 + piece * 8;
     const bool okx = k < K && row < M;
     cp_async16(sk_ptr(xs, row, piece), okx ? X + (int64_t)row * ldx + k : X, okx);
   }
@@ -102,7 +109,7 @@ int launch_skinny(const void* X, int64_t ldx, const void* W, void* Y, int64_t ld
     ME_REQUIRE(e == cudaSuccess, "me_gemm_skinny: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  gemm_skinny_kernel<EPI, TO><<<dim3(strips, splits), SK_THREADS, smem, stream>>>(
+  me_launch(gemm_skinny_kernel<EPI, TO>, dim3(strips, splits), dim3(SK_THREADS), smem, stream,
       (const bf16*)X, ldx, (const bf16*)W, (TO*)Y, ldy, partial, M, N, K);
   return 0;
 }

@@ -39,4 +39,28 @@ __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int piece) {
   return base + row * HD + ((piece ^ (row & 7)) << 3);
 }
 
+// Where a key's row lives in a paged pool [page][k|v][kv_head][offset][head_dim]: the element offset of
+// K's row for key j (V's row is ``v_off`` further), or -1 if the page was given back.  ``page_shift`` is
+// log2(page_size) for powers of two (a shift and a mask replace the division), else -1.
+struct PageMap {
+  const int* bt;
+  int page_size, page_shift;
+  int64_t page_stride, head_off;     // 2 * nkv * page_size * hd;  kv_head * page_size * hd
+  int hd;
+  __device__ __forceinline__ int64_t row(int j) const {
+    int pi, off;
+    if (page_shift >= 0) {
+      pi = j >> page_shift;
+      off = j & (page_size - 1);
+    } else {
+      pi = j / page_size;
+      off = j - pi * page_size;
+    }
+    const int page = bt[pi];
+    return page < 0 ? -1 : (int64_t)page * page_stride + head_off + (int64_t)off * hd;
+  }
+};
+
+__device__ __forceinline__ int log2_if_pow2(int x) { return (x & (x - 1)) == 0 ? 31 - __clz(x) : -1; }
+
 }  // namespace mma_prims

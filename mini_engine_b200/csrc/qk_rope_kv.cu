@@ -19,6 +19,8 @@ qk_rope_kv_kernel(T* __restrict__ qkv, int64_t row_stride, int n_tokens, int nh,
                   const float* __restrict__ qw, const float* __restrict__ kw, float eps,
                   const float* __restrict__ cos_sin, const int* __restrict__ positions,
                   const int* __restrict__ slot_mapping, T* __restrict__ pool, int page_size) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int heads = nh + 2 * nkv;
   const int64_t gw = (int64_t)blockIdx.x * QK_WARPS + warp;
@@ -101,7 +103,7 @@ ME_API int me_qk_norm_rope_kv_write(void* qkv, int dtype, int64_t row_stride, in
   const int64_t warps = (int64_t)n_tokens * (nh + 2 * nkv);
   const int64_t blocks = (warps + QK_WARPS - 1) / QK_WARPS;
   ME_REQUIRE(blocks < 2147483647LL, "me_qk_norm_rope_kv_write: too many tokens");
-  ME_DISPATCH_DTYPE(dtype, T, (qk_rope_kv_kernel<T><<<(unsigned)blocks, QK_WARPS * 32, 0, stream>>>(
+  ME_DISPATCH_DTYPE(dtype, T, (me_launch(qk_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(QK_WARPS * 32), 0, stream,
       (T*)qkv, row_stride, n_tokens, nh, nkv, hd, qw, kw, eps, cos_sin, positions, slot_mapping,
       (T*)pool, page_size)));
   ME_LAUNCH_CHECK("me_qk_norm_rope_kv_write");

@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_partial_kernel(const float* __restrict__ logits, int64_t row_stride, const float* __restrict__ temperature,
                       const int* __restrict__ seeds, const int* __restrict__ positions,
                       float* __restrict__ part_key, int* __restrict__ part_idx, int V, int chunks) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x, chunk = blockIdx.y;
   const float* x = logits + (int64_t)row * row_stride;
   const float T = temperature[row];
@@ -83,6 +85,8 @@ sample_partial_kernel(const float* __restrict__ logits, int64_t row_stride, cons
 // Pass 2: one block per row picks the best of the chunks.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_final_kernel(const float* __restrict__ part_key, const int* __restrict__ part_idx, int* __restrict__ out, int chunks) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -108,10 +112,10 @@ ME_API int me_sample(const float* logits, int64_t row_stride, const float* tempe
   ME_REQUIRE(S > 0 && V > 0, "me_sample: bad sizes S=%d V=%d", S, V);
   const int chunks = me_sample_chunks(V);
   ME_REQUIRE(chunks <= 65535, "me_sample: vocabulary %d is too large", V);
-  sample_partial_kernel<<<dim3(S, chunks), SAMPLE_THREADS, 0, stream>>>(logits, row_stride, temperature, seeds, positions,
-                                                                       part_key, part_idx, V, chunks);
+  me_launch(sample_partial_kernel, dim3(S, chunks), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride, temperature, seeds,
+            positions, part_key, part_idx, V, chunks);
   ME_LAUNCH_CHECK("me_sample (pass 1)");
-  sample_final_kernel<<<S, SAMPLE_THREADS, 0, stream>>>(part_key, part_idx, out, chunks);
+  me_launch(sample_final_kernel, dim3(S), dim3(SAMPLE_THREADS), 0, stream, part_key, part_idx, out, chunks);
   ME_LAUNCH_CHECK("me_sample (pass 2)");
   return 0;
 }

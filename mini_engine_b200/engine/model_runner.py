@@ -15,6 +15,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Optional, Sequence
 
+import gc
+
 import numpy as np
 import torch
 
@@ -391,8 +393,15 @@ class ModelRunner:
             g.ctx.frozen = True
             before = ops.launches
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                g.logits, g.tokens = self._forward(token_ids, g.ctx, True)
+            # Nothing may free device or pinned memory while the stream is capturing: Python's collector is
+            # paused, and calls that have nothing to do with the capture do not invalidate it.
+            gc.collect()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="relaxed"):
+                    g.logits, g.tokens = self._forward(token_ids, g.ctx, True)
+            finally:
+                gc.enable()
             g.launches = ops.launches - before
             g.graph = graph
         g.graph.replay()

@@ -11,6 +11,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
+import weakref
+
 import torch
 
 
@@ -50,7 +52,7 @@ class HostMeta:
 
 class StepContext:
     def __init__(self, runner, arena: Optional[dict] = None):
-        self.runner = runner
+        self._runner = weakref.ref(runner)       # no cycle: a dropped runner frees its memory at once
         self.act_dtype: torch.dtype = runner.act_dtype
         self.device = runner.device
         self.error_flag: torch.Tensor = runner.error_flag
@@ -69,8 +71,13 @@ class StepContext:
         self._bt: list[torch.Tensor] = []
         self._sm: list[torch.Tensor] = []
 
-    def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
-        """A work buffer by name: the same storage every step, grown when a step needs more."""
+    @property
+    def runner(self):
+        return self._runner()
+
+    def buffer(self, name: str, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A work buffer by name: the same storage every step, grown when a step needs more.
+        ``zero``: the storage is zeroed when it is made (for counters that kernels leave at zero)."""
         n = 1
         for s in shape:
             n *= int(s)
@@ -79,7 +86,7 @@ class StepContext:
         if flat is None or flat.numel() < nbytes:
             if self.frozen:
                 raise RuntimeError(f"work buffer {name!r} would move under a captured graph")
-            flat = torch.empty(nbytes + (-nbytes) % 256, dtype=torch.uint8, device=self.device)
+            flat = (torch.zeros if zero else torch.empty)(nbytes + (-nbytes) % 256, dtype=torch.uint8, device=self.device)
             self._arena[name] = flat
         return flat[:n * dtype.itemsize].view(dtype).view(*shape)
 

@@ -28,7 +28,8 @@ _PROTOS = {
     "me_gemm_simt": [_P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P],
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
-    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P],
+    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
+    "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
 }
@@ -63,6 +64,12 @@ def require_extension() -> ctypes.CDLL:
     lib.me_gemm_skinny_splits.argtypes = [_I]
     _lib = lib
     return lib
+
+
+def set_programmatic_launch(on: bool) -> None:
+    """Switch programmatic dependent launch (a kernel may start, and fetch weights, while its predecessor
+    still runs) on or off for all later launches; it is on by default."""
+    (_lib or require_extension()).me_set_pdl(1 if on else 0)
 
 
 def library_file() -> str:
@@ -271,24 +278,55 @@ def attention_prefill(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_si
           int(window or 0), _stream())
 
 
-DECODE_KINDS = {"auto": 0, "cuda_cores": 1, "bulk_copy": 2, "tensor_cores": 3}
+DECODE_KINDS = {"auto": 0, "cuda_cores": 1, "bulk_copy": 2, "tensor_cores": 3, "tensor_cores_tma": 4}
+
+_tensor_maps: dict = {}
+
+
+class TensorMap:
+    """A CUtensorMap (128 bytes, 64-byte aligned) kept alive on the host for kernels that take it by value."""
+
+    def __init__(self):
+        self._raw = ctypes.create_string_buffer(128 + 64)
+        self.ptr = (ctypes.addressof(self._raw) + 63) & ~63
+
+
+def kv_tensor_map(pool: torch.Tensor, page_size: int) -> Optional[TensorMap]:
+    """The tensor map of one cache slot [pages, 2, kv_heads, page_size, head_dim] (bfloat16) as the 2-D tensor
+    [pages * 2 * kv_heads * page_size, head_dim] with boxes of one page x 64 columns, 128-byte swizzle;
+    None where the tensor-map kernels do not apply."""
+    hd = pool.shape[-1]
+    if pool.dtype != torch.bfloat16 or hd not in (64, 128) or page_size < 8 or DECODE_PARTITION % page_size:
+        return None
+    key = (pool.data_ptr(), tuple(pool.shape))
+    tm = _tensor_maps.get(key)
+    if tm is None:
+        tm = TensorMap()
+        rows = pool.shape[0] * 2 * pool.shape[2] * page_size
+        lib = _lib or require_extension()
+        if lib.me_tma_encode_2d(tm.ptr, pool.data_ptr(), rows, hd, hd * 2, page_size, 64, 128) != 0:
+            raise KernelError(lib.me_last_error().decode())
+        _tensor_maps[key] = tm
+    return tm
 
 
 def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
                      scale, window, kind: str = "auto") -> None:
     """The split-K decode kernel and its merge over requests [0, meta.num_decodes).
 
-    ``kind`` picks the partition kernel: "auto" (tensor cores for bfloat16 with head_dim 64 or 128, else
-    CUDA cores), or one of them by name (tests run each)."""
+    ``kind`` picks the partition kernel: "auto" (for bfloat16 with head_dim 64 or 128 the tensor cores, fed by
+    tensor-map loads where the page size divides 128, else by cp.async; otherwise the CUDA cores), or one
+    of them by name (tests run each)."""
     D = meta.num_decodes
     parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
     tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * parts * head_dim,), torch.float32)
     tmp_ml = meta.workspace("decode_tmp_ml", (2, D * num_heads * parts), torch.float32)
+    tm = kv_tensor_map(pool, page_size) if kind in ("auto", "tensor_cores_tma") else None
     _call("me_attn_decode", qkv.data_ptr(), _dt(qkv), qkv.stride(0), out.data_ptr(), out.stride(0),
           pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
           meta.context_lens.data_ptr(), D, num_heads, num_kv_heads, head_dim, page_size, float(scale),
           int(window or 0), tmp_out.data_ptr(), tmp_ml[0].data_ptr(), tmp_ml[1].data_ptr(), parts,
-          _ptr(meta.error_flag), DECODE_KINDS[kind], _stream())
+          _ptr(meta.error_flag), DECODE_KINDS[kind], tm.ptr if tm is not None else 0, _stream())
     global launches
     launches += 1          # partition kernel + merge kernel
 

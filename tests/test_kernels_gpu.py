@@ -241,10 +241,11 @@ class Batch:
         self.pool, self.qkv, self.bt = self.pool.to(DEV), self.qkv.to(DEV), bt.to(DEV)
         self._ws = {}
 
-        def workspace(name, shape, dt):
+        def workspace(name, shape, dt, zero=False):
             key = (name, tuple(shape), dt)
             if key not in self._ws:
-                self._ws[key] = torch.full(tuple(shape), float("nan"), dtype=dt, device=DEV)
+                self._ws[key] = (torch.zeros(tuple(shape), dtype=dt, device=DEV) if zero
+                                 else torch.full(tuple(shape), float("nan"), dtype=dt, device=DEV))
             return self._ws[key]
         self.meta = AttnMeta(num_reqs=B, num_tokens=T, num_decodes=D,
                              cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV),
@@ -306,14 +307,14 @@ def test_attention_tensor_core_prefill(ops, nh, nkv, hd, page, window):
     assert ops.prefill_heads_per_block(8, 2, 32) == 0 and ops.prefill_heads_per_block(8, 2, 96) == 0
 
 
-@pytest.mark.parametrize("kind", ["cuda_cores", "bulk_copy", "tensor_cores"])
+@pytest.mark.parametrize("kind", ["cuda_cores", "bulk_copy", "tensor_cores", "tensor_cores_tma"])
 @pytest.mark.parametrize("nh, nkv, hd, page", [(16, 8, 128, 16), (8, 1, 64, 32), (4, 4, 64, 8), (12, 4, 128, 16),
                                                   (40, 2, 64, 16), (6, 3, 48, 16), (8, 2, 32, 8)])
 @pytest.mark.parametrize("window", [None, 200])
 def test_attention_decode_kernels_by_name(ops, kind, nh, nkv, hd, page, window):
     # every decode kernel on single tokens: contexts at partition (128) and page edges, groups of 1 to 20 heads
-    if kind == "tensor_cores" and hd not in (64, 128):
-        pytest.skip("the tensor-core decode kernel takes head_dim 64 and 128")
+    if kind.startswith("tensor_cores") and hd not in (64, 128):
+        pytest.skip("the tensor-core decode kernels take head_dim 64 and 128")
     ctx = [1, 127, 128, 129, 300, 1000, 16, 255, 256, 257, 513]
     b = Batch(ctx, [1] * len(ctx), nh, nkv, hd, page, torch.bfloat16, seed=nh + hd, window=window,
               standout=lambda r, L, n: (L // 2, 0))
