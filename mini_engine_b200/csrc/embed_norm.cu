@@ -112,6 +112,55 @@ __global__ void add_rmsnorm_regs_kernel(float* __restrict__ res, const TD* __res
   }
 }
 
+// The same with four consecutive elements per access (H a multiple of 4, up to 8 * blockDim).
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ res, const TD* __restrict__ delta,
+                                        const float* __restrict__ w, float eps, TO* __restrict__ out,
+                                        const int* __restrict__ rows, int H, int write_res, int splits,
+                                        int64_t split_stride) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r_out = blockIdx.x;
+  const int64_t r = rows ? rows[r_out] : r_out;
+  float* rr = res + r * H;
+  const TD* dd = delta ? delta + r * H : nullptr;
+  float v[2][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int h = (threadIdx.x + i * blockDim.x) * 4;
+    v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
+    if (h < H) {
+      const float4 a = *reinterpret_cast<const float4*>(rr + h);
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+      if (dd) {
+        for (int s = 0; s < splits; ++s) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[i][e] += to_f<TD>(dd[h + e + s * split_stride]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss += v[i][e] * v[i][e];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* oo = out + (int64_t)r_out * H;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int h = (threadIdx.x + i * blockDim.x) * 4;
+    if (h < H) {
+      if (write_res) *reinterpret_cast<float4*>(rr + h) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+      const float4 ww = *reinterpret_cast<const float4*>(w + h);
+      oo[h] = from_f<TO>((v[i][0] * inv) * ww.x);
+      oo[h + 1] = from_f<TO>((v[i][1] * inv) * ww.y);
+      oo[h + 2] = from_f<TO>((v[i][2] * inv) * ww.z);
+      oo[h + 3] = from_f<TO>((v[i][3] * inv) * ww.w);
+    }
+  }
+}
+
 ME_API int me_add_rmsnorm(float* res, const void* delta, int delta_dtype, const float* w, float eps,
                           void* out, int out_dtype, const int* rows, int n_rows, int H, int splits,
                           int64_t split_stride, cudaStream_t stream) {
@@ -119,7 +168,13 @@ ME_API int me_add_rmsnorm(float* res, const void* delta, int delta_dtype, const 
   ME_REQUIRE(n_rows > 0 && H > 0 && splits >= 1, "me_add_rmsnorm: bad sizes rows=%d H=%d splits=%d", n_rows, H, splits);
   const int write_res = rows == nullptr;     // gathered rows leave the residual as it is
   constexpr int NV = 8;
-  if (H <= NV * 1024) {
+  if (H % 4 == 0 && H <= 8 * 1024 && ((uintptr_t)res & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+    int threads = ((H / 4 + 1) / 2 + 31) / 32 * 32;
+    if (threads < 32) threads = 32;
+    ME_DISPATCH_DTYPE(delta_dtype, TD, ME_DISPATCH_DTYPE(out_dtype, TO,
+        (me_launch(add_rmsnorm_vec4_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream,
+                   res, (const TD*)delta, w, eps, (TO*)out, rows, H, write_res, splits, split_stride))));
+  } else if (H <= NV * 1024) {
     int threads = ((H + NV - 1) / NV + 31) / 32 * 32;
     if (threads < 64) threads = 64;
     ME_DISPATCH_DTYPE(delta_dtype, TD, ME_DISPATCH_DTYPE(out_dtype, TO,
@@ -147,9 +202,39 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
   out[i] = from_f<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// Eight elements per thread with 16-byte accesses (bfloat16, I a multiple of 8).
+__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, int64_t n8, int I8) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const int64_t t = i / I8;
+  const int c = (int)(i - t * I8);
+  const uint4 g = *reinterpret_cast<const uint4*>(x + (t * 2 * I8 + c) * 8);
+  const uint4 u = *reinterpret_cast<const uint4*>(x + (t * 2 * I8 + I8 + c) * 8);
+  const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+  const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+  uint4 r;
+  __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 gf = __bfloat1622float2(gp[k]), uf = __bfloat1622float2(up[k]);
+    rp[k] = __floats2bfloat162_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x, gf.y / (1.0f + expf(-gf.y)) * uf.y);
+  }
+  *reinterpret_cast<uint4*>(out + i * 8) = r;
+}
+
 ME_API int me_silu_mul(const void* x, void* out, int dtype, int T, int I, cudaStream_t stream) {
   if (T == 0) return 0;
   ME_REQUIRE(T > 0 && I > 0, "me_silu_mul: bad sizes T=%d I=%d", T, I);
+  if (dtype == ME_BF16 && I % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const int64_t n8 = (int64_t)T * (I / 8);
+    const int64_t blocks8 = (n8 + 255) / 256;
+    ME_REQUIRE(blocks8 < 2147483647LL, "me_silu_mul: too many elements");
+    me_launch(silu_mul_vec8_kernel, dim3((unsigned)blocks8), dim3(256), 0, stream, (const bf16*)x, (bf16*)out, n8, I / 8);
+    ME_LAUNCH_CHECK("me_silu_mul");
+    return 0;
+  }
   const int64_t n = (int64_t)T * I;
   const int threads = 256;
   const int64_t blocks = (n + threads - 1) / threads;

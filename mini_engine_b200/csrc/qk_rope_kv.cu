@@ -90,6 +90,95 @@ qk_rope_kv_kernel(T* __restrict__ qkv, int64_t row_stride, int n_tokens, int nh,
   }
 }
 
+// The same with vector accesses, for head sizes that are multiples of 64: lane l owns VEC consecutive
+// elements of each half (VEC = head_dim / 64), so a warp reads and writes whole 128-byte lines.
+template <typename T, int VEC> struct PackOf;
+template <> struct PackOf<bf16, 1> { typedef unsigned short type; };
+template <> struct PackOf<bf16, 2> { typedef uint32_t type; };
+template <> struct PackOf<bf16, 4> { typedef uint2 type; };
+template <> struct PackOf<float, 1> { typedef float type; };
+template <> struct PackOf<float, 2> { typedef float2 type; };
+template <> struct PackOf<float, 4> { typedef float4 type; };
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(QK_WARPS * 32)
+qk_rope_kv_vec_kernel(T* __restrict__ qkv, int64_t row_stride, int n_tokens, int nh, int nkv,
+                      const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                      const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                      const int* __restrict__ slot_mapping, T* __restrict__ pool, int page_size) {
+  typedef typename PackOf<T, VEC>::type P;
+  constexpr int hd = 64 * VEC, half = 32 * VEC;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int heads = nh + 2 * nkv;
+  const int64_t gw = (int64_t)blockIdx.x * QK_WARPS + warp;
+  if (gw >= (int64_t)n_tokens * heads) return;
+  const int t = (int)(gw / heads), head = (int)(gw % heads);
+  T* x = qkv + (int64_t)t * row_stride + (int64_t)head * hd;
+  const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+  const int kvh = is_q ? 0 : (is_k ? head - nh : head - nh - nkv);
+  T* dst = nullptr;
+  if (!is_q) {
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    if (slot >= 0) {
+      const int page = slot / page_size, off = slot - page * page_size;
+      dst = pool + ((((int64_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * hd;
+    }
+  }
+  const int i0 = lane * VEC;
+  P pa = *reinterpret_cast<const P*>(x + i0), pb = *reinterpret_cast<const P*>(x + half + i0);
+  if (!is_q && !is_k) {                   // v: copy to the cache
+    if (dst) {
+      *reinterpret_cast<P*>(dst + i0) = pa;
+      *reinterpret_cast<P*>(dst + half + i0) = pb;
+    }
+    return;
+  }
+  const T* ea = reinterpret_cast<const T*>(&pa);
+  const T* eb = reinterpret_cast<const T*>(&pb);
+  float a[VEC], b[VEC], ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) {
+    a[j] = to_f<T>(ea[j]);
+    b[j] = to_f<T>(eb[j]);
+    ss += a[j] * a[j] + b[j] * b[j];
+  }
+  const float* w = is_q ? qw : kw;
+  float inv = 1.f;
+  if (w) {
+    ss = warp_sum(ss);
+    inv = 1.0f / sqrtf(ss / (float)hd + eps);
+  }
+  const int pos = positions[t];
+  P ra, rb;
+  T* oa = reinterpret_cast<T*>(&ra);
+  T* ob = reinterpret_cast<T*>(&rb);
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) {
+    const int i = i0 + j;
+    float y1 = a[j], y2 = b[j];
+    if (w) {
+      y1 = (y1 * inv) * w[i];
+      y2 = (y2 * inv) * w[i + half];
+    }
+    float o1 = y1, o2 = y2;
+    if (cos_sin) {
+      const float c = cos_sin[(int64_t)pos * hd + i], sn = cos_sin[(int64_t)pos * hd + half + i];
+      o1 = y1 * c - y2 * sn;
+      o2 = y2 * c + y1 * sn;
+    }
+    oa[j] = from_f<T>(o1);
+    ob[j] = from_f<T>(o2);
+  }
+  *reinterpret_cast<P*>(x + i0) = ra;
+  *reinterpret_cast<P*>(x + half + i0) = rb;
+  if (dst) {
+    *reinterpret_cast<P*>(dst + i0) = ra;
+    *reinterpret_cast<P*>(dst + half + i0) = rb;
+  }
+}
+
 ME_API int me_qk_norm_rope_kv_write(void* qkv, int dtype, int64_t row_stride, int n_tokens, int nh,
                                     int nkv, int hd, const float* qw, const float* kw, float eps,
                                     const float* cos_sin, const int* positions,
@@ -103,6 +192,19 @@ ME_API int me_qk_norm_rope_kv_write(void* qkv, int dtype, int64_t row_stride, in
   const int64_t warps = (int64_t)n_tokens * (nh + 2 * nkv);
   const int64_t blocks = (warps + QK_WARPS - 1) / QK_WARPS;
   ME_REQUIRE(blocks < 2147483647LL, "me_qk_norm_rope_kv_write: too many tokens");
+  const int esize = dtype == ME_BF16 ? 2 : 4;
+  const bool vec_ok = (hd == 64 || hd == 128 || hd == 256) && (row_stride * esize) % 16 == 0 && ((uintptr_t)qkv & 15) == 0;
+#define ME_QK_VEC(V_)                                                                                   \
+  ME_DISPATCH_DTYPE(dtype, T, (me_launch(qk_rope_kv_vec_kernel<T, V_>, dim3((unsigned)blocks), dim3(QK_WARPS * 32), 0, \
+      stream, (T*)qkv, row_stride, n_tokens, nh, nkv, qw, kw, eps, cos_sin, positions, slot_mapping, (T*)pool, page_size)))
+  if (vec_ok) {
+    if (hd == 64) ME_QK_VEC(1);
+    else if (hd == 128) ME_QK_VEC(2);
+    else ME_QK_VEC(4);
+    ME_LAUNCH_CHECK("me_qk_norm_rope_kv_write");
+    return 0;
+  }
+#undef ME_QK_VEC
   ME_DISPATCH_DTYPE(dtype, T, (me_launch(qk_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(QK_WARPS * 32), 0, stream,
       (T*)qkv, row_stride, n_tokens, nh, nkv, hd, qw, kw, eps, cos_sin, positions, slot_mapping,
       (T*)pool, page_size)));

@@ -46,7 +46,7 @@ def test_embed(ops, wd):
 
 
 # ---- residual add + RMSNorm --------------------------------------------------------------------
-@pytest.mark.parametrize("H", [64, 96, 1000, 4104])
+@pytest.mark.parametrize("H", [64, 96, 1000, 1001, 4104, 8200, 9001])
 @pytest.mark.parametrize("od", ["float32", "bfloat16"])
 def test_add_rmsnorm(ops, H, od):
     T = 19
