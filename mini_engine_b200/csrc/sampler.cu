@@ -119,3 +119,56 @@ ME_API int me_sample(const float* logits, int64_t row_stride, const float* tempe
   ME_LAUNCH_CHECK("me_sample (pass 2)");
   return 0;
 }
+
+// ---- the same two passes with the work buffer inside the library (see sampler_static.h) -------------
+#include "sampler_static.h"
+#include <mutex>
+
+constexpr int SAMPLE_STATIC_ENTRIES = ME_SAMPLE_STATIC_MAX_ROWS * (ME_SAMPLE_STATIC_MAX_VOCAB / SAMPLE_CHUNK);
+
+// Partial results of pass 1: SAMPLE_STATIC_ENTRIES keys (float) followed by as many indices (int).
+// In host code this name is only a handle; the address a kernel can use comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_sample_static_scratch[SAMPLE_STATIC_ENTRIES * 8];
+
+static void* sample_static_scratch_of_current_device(int* device_out) {
+  constexpr int MAX_DEVICES = 64;
+  static void* ptrs[MAX_DEVICES] = {};
+  static std::mutex lock;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+  *device_out = dev;
+  std::lock_guard<std::mutex> guard(lock);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_sample_static_scratch);     // once per device, that device current
+    if (e != cudaSuccess) {
+      me_set_error("me_sample_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return nullptr;
+    }
+    ptrs[dev] = p;
+  }
+  return ptrs[dev];
+}
+
+ME_API int me_sample_static(const float* logits, int64_t row_stride, const float* temperature, const int* seeds,
+                            const int* positions, int* out, int S, int V, cudaStream_t stream) {
+  if (S == 0) return 0;
+  ME_REQUIRE(S > 0 && V > 0, "me_sample_static: bad sizes S=%d V=%d", S, V);
+  ME_REQUIRE(S <= ME_SAMPLE_STATIC_MAX_ROWS, "me_sample_static: %d rows, the built-in work buffer holds %d; use me_sample()",
+             S, ME_SAMPLE_STATIC_MAX_ROWS);
+  ME_REQUIRE(V <= ME_SAMPLE_STATIC_MAX_VOCAB, "me_sample_static: vocabulary %d, the built-in work buffer holds %d; use me_sample()",
+             V, ME_SAMPLE_STATIC_MAX_VOCAB);
+  int dev = -1;
+  me_set_error("me_sample_static: no usable CUDA device is current");
+  void* scratch = sample_static_scratch_of_current_device(&dev);
+  if (scratch == nullptr) return 1;
+  const int chunks = me_sample_chunks(V);
+  float* part_key = static_cast<float*>(scratch);
+  int* part_idx = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + sizeof(float) * SAMPLE_STATIC_ENTRIES);
+  me_launch(sample_partial_kernel, dim3(S, chunks), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride, temperature, seeds,
+            positions, part_key, part_idx, V, chunks);
+  ME_LAUNCH_CHECK("me_sample_static (pass 1)");
+  me_launch(sample_final_kernel, dim3(S), dim3(SAMPLE_THREADS), 0, stream, part_key, part_idx, out, chunks);
+  ME_LAUNCH_CHECK("me_sample_static (pass 2)");
+  return 0;
+}
