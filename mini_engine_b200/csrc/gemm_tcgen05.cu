@@ -1,0 +1,217 @@
+// C[M,N] = A[M,K] W[N,K]^T in bfloat16 on the 5th-generation tensor cores (tcgen05), for many rows
+// (portions of prompts).  The reference leaves these products to cuBLAS through F.linear
+// (layers/linear.py:26,45); this kernel is the engine's own, with SiLU-and-multiply
+// (layers/activation.py:4-7) in its epilogue and float32 results for the output head.
+//
+// One block computes a 128 x BN tile.  Warp 0: one thread streams A and W tiles of 64 K-elements
+// through a ring of shared-memory stages by TMA (128-byte swizzle, zero fill at the edges).
+// Warp 1: allocates BN columns of tensor memory; one thread issues tcgen05.mma (M 128, N BN, K 16,
+// four per stage) and hands stages back through tcgen05.commit.  Warps 2..5: when the accumulator is
+// complete, each thread reads its row from tensor memory (tcgen05.ld), applies the epilogue and writes
+// it.  Every wait is bounded; a wait that gives up sets flag 1 of ``err`` and the block still frees its
+// tensor memory and exits.
+//
+// EPI 1: W has rows gate | up; a stage's W tile holds BN/2 gate rows and the matching BN/2 up rows, so
+// the accumulator's first half is gate and its second half up, and the block writes BN/2 columns of
+// silu(gate) * up.
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int TG_BM = 128, TG_BK = 64, TG_THREADS = 192;
+constexpr int TG_A_BYTES = TG_BM * TG_BK * 2;
+
+// Stages sized so that two blocks fit on an SM (about 96 KB each): one block's epilogue overlaps the other's main loop.
+template <int BN> constexpr int tg_stages() { return BN <= 64 ? 4 : (BN <= 128 ? 3 : 2); }
+
+// 32 consecutive results of one row: 16-byte stores where the row's place allows, else one by one.
+__device__ __forceinline__ void store_row32(bf16* dst, const float (&v)[32], int n_left, bool vec) {
+  if (vec && n_left >= 32) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint4 pk;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+      *reinterpret_cast<uint4*>(dst + q * 8) = pk;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < n_left) dst[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+__device__ __forceinline__ void store_row32(float* dst, const float (&v)[32], int n_left, bool vec) {
+  if (vec && n_left >= 32) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < n_left) dst[j] = v[j];
+  }
+}
+
+template <int BN, int EPI, typename TO>
+__global__ void __launch_bounds__(TG_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    TO* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err) {
+  constexpr int STAGES = tg_stages<BN>();
+  constexpr int B_BYTES = BN * TG_BK * 2, STAGE_BYTES = TG_A_BYTES + B_BYTES;
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
+  extern __shared__ unsigned char tg_smem_raw[];
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
+  __shared__ uint32_t tmem_slot;
+  unsigned char* smem = tg_smem_raw + ((1024u - (tma::smem_addr(tg_smem_raw) & 1023u)) & 1023u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * OUT_COLS;
+  const int num_kb = (K + TG_BK - 1) / TG_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tma::mbar_init(&full_bar[s], 1);
+      tma::mbar_init(&empty_bar[s], 1);
+    }
+    tma::mbar_init(&done_bar, 1);
+    tma::mbar_fence_init();
+    tma::prefetch_map(&map_a);
+    tma::prefetch_map(&map_w);
+  }
+  if (warp == 1) tc5::tmem_alloc(&tmem_slot, BN < 32 ? 32 : BN);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // The weights are no output of the kernel before this one; the activations are.
+      bool waited = false;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        ok = tma::mbar_wait(&empty_bar[s], ((kb / STAGES) & 1) ^ 1);
+        if (!ok) break;
+        unsigned char* a_dst = smem + s * STAGE_BYTES;
+        unsigned char* b_dst = a_dst + TG_A_BYTES;
+        tma::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        if (EPI == 1) {
+          tma::load_2d(b_dst, &map_w, kb * TG_BK, n0, &full_bar[s]);
+          tma::load_2d(b_dst + B_BYTES / 2, &map_w, kb * TG_BK, N + n0, &full_bar[s]);
+        } else {
+          tma::load_2d(b_dst, &map_w, kb * TG_BK, n0, &full_bar[s]);
+        }
+        if (!waited && (kb == STAGES - 1 || kb == num_kb - 1)) {
+          // first ring of weights requested: now wait for the predecessor and send the held-back A tiles
+          pdl_wait();
+          waited = true;
+          for (int k2 = 0; k2 <= kb; ++k2)
+            tma::load_2d(smem + (k2 % STAGES) * STAGE_BYTES, &map_a, k2 * TG_BK, m0, &full_bar[k2 % STAGES]);
+        } else if (waited) {
+          tma::load_2d(a_dst, &map_a, kb * TG_BK, m0, &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc5::instr_desc_bf16(TG_BM, BN);
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        ok = tma::mbar_wait(&full_bar[s], (kb / STAGES) & 1);
+        if (!ok) break;
+        tc5::fence_after_sync();
+        const uint64_t a_desc = tc5::smem_desc_k_major_sw128(smem + s * STAGE_BYTES);
+        const uint64_t b_desc = tc5::smem_desc_k_major_sw128(smem + s * STAGE_BYTES + TG_A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TG_BK / 16; ++k)       // 32 bytes further along K per step: +2 in units of 16 bytes
+          tc5::mma_f16(tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > 0 || k > 0);
+        tc5::commit(&empty_bar[s]);                // the stage is free once these MMAs have read it
+      }
+      tc5::commit(&done_bar);                      // the accumulator is complete
+    }
+  } else {
+    // Epilogue: warp w reads lanes 32 (w % 4) .. +31 of tensor memory; a lane is a row of the tile.
+    ok = tma::mbar_wait(&done_bar, 0);
+    tc5::fence_after_sync();
+    const int lane_base = (warp & 3) * 32;
+    const int m = m0 + lane_base + lane;
+    const bool vec = (ldc * sizeof(TO)) % 16 == 0 && (n0 * sizeof(TO)) % 16 == 0 && ((uintptr_t)C & 15) == 0;
+    if (ok) {
+      if (EPI == 1) {
+#pragma unroll 1
+        for (int c = 0; c < OUT_COLS; c += 32) {
+          float g[32], u[32];
+          tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + c, g);
+          tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + OUT_COLS + c, u);
+          tc5::wait_ld();
+          if (m < M && n0 + c < N) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
+            store_row32(C + (int64_t)m * ldc + n0 + c, g, N - n0 - c, vec);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < OUT_COLS; c += 32) {
+          float v[32];
+          tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + c, v);
+          tc5::wait_ld();
+          if (m < M && n0 + c < N) store_row32(C + (int64_t)m * ldc + n0 + c, v, N - n0 - c, vec);
+        }
+      }
+    }
+  }
+  if (!ok) atomicOr(err + 1, 1);
+  pdl_launch_dependents();
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tc5::tmem_dealloc(tmem, BN < 32 ? 32 : BN);
+}
+
+template <int BN, int EPI, typename TO>
+int launch_tg(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, int* err, cudaStream_t stream) {
+  constexpr int STAGES = tg_stages<BN>();
+  const size_t smem = (size_t)STAGES * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ME_REQUIRE(e == cudaSuccess, "me_gemm_tcgen05: cannot raise shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
+  dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (M + TG_BM - 1) / TG_BM);
+  me_launch(gemm_tcgen05_kernel<BN, EPI, TO>, grid, dim3(TG_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(map_a),
+            *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, err);
+  return 0;
+}
+
+}  // namespace
+
+// Rows of W that one block's TMA box covers for a given tile width and epilogue (the caller encodes the map so).
+ME_API int me_gemm_tcgen05_w_box_rows(int bn, int epi) { return epi == 1 ? bn / 2 : bn; }
+
+// map_a: X as [M][K], boxes 128 x 64, 128-byte swizzle; map_w: W as [rows][K], boxes
+// me_gemm_tcgen05_w_box_rows(bn, epi) x 64.  N counts output columns (epi 1: W has 2N rows).
+// bn is the accumulator's width: 64, 128 or 256.
+ME_API int me_gemm_tcgen05(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, int M, int N,
+                           int K, int epi, int bn, int* err, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  ME_REQUIRE(M > 0 && N > 0 && K > 0 && K % 8 == 0, "me_gemm_tcgen05: bad sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
+  ME_REQUIRE(map_a != nullptr && map_w != nullptr && err != nullptr, "me_gemm_tcgen05: tensor maps and the error word are required");
+  ME_REQUIRE(epi == 0 || (epi == 1 && c_dtype == ME_BF16), "me_gemm_tcgen05: epilogue %d", epi);
+  ME_REQUIRE((M + TG_BM - 1) / TG_BM <= 65535, "me_gemm_tcgen05: M=%d is too large", M);
+  int rc = 1;
+#define ME_TG_CASE(BN_)                                                                                              \
+  if (bn == BN_) {                                                                                                   \
+    if (epi == 1) rc = launch_tg<BN_, 1, bf16>(map_a, map_w, C, ldc, M, N, K, err, stream);                          \
+    else if (c_dtype == ME_BF16) rc = launch_tg<BN_, 0, bf16>(map_a, map_w, C, ldc, M, N, K, err, stream);           \
+    else rc = launch_tg<BN_, 0, float>(map_a, map_w, C, ldc, M, N, K, err, stream);                                  \
+  }
+  ME_TG_CASE(64) ME_TG_CASE(128) ME_TG_CASE(256)
+#undef ME_TG_CASE
+  ME_REQUIRE(bn == 64 || bn == 128 || bn == 256, "me_gemm_tcgen05: tile width %d is not 64, 128 or 256", bn);
+  if (rc) return rc;
+  ME_LAUNCH_CHECK("me_gemm_tcgen05");
+  return 0;
+}

@@ -29,6 +29,7 @@ _PROTOS = {
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
+    "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
@@ -183,15 +184,73 @@ def linear_partials(x: torch.Tensor, weight: torch.Tensor, workspace, name: str)
     return part
 
 
+TCGEN05_MIN_ROWS = 128    # rows from which bfloat16 products run csrc/gemm_tcgen05.cu (17..127: cuBLAS)
+use_tcgen05_gemm = True   # False: such products go to cuBLAS instead (a switch for comparisons)
+
+
+def matrix_tensor_map(t: torch.Tensor, box_rows: int) -> "TensorMap":
+    """The tensor map of a row-major bfloat16 matrix [rows, cols] (row pitch ``t.stride(0)``) with boxes of
+    ``box_rows`` x 64 columns and the 128-byte swizzle; cached by address and shape."""
+    key = (t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows)
+    tm = _tensor_maps.get(key)
+    if tm is None:
+        if len(_tensor_maps) > 8192:
+            _tensor_maps.clear()
+        tm = TensorMap()
+        lib = _lib or require_extension()
+        if lib.me_tma_encode_2d(tm.ptr, t.data_ptr(), t.shape[0], t.shape[1], t.stride(0) * 2, box_rows, 64, 128) != 0:
+            raise KernelError(lib.me_last_error().decode())
+        _tensor_maps[key] = tm
+    return tm
+
+
+def tcgen05_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    M, K = x.shape
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M >= TCGEN05_MIN_ROWS
+            and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str, err: torch.Tensor,
+                   tile_n: Optional[int] = None) -> None:
+    """The tcgen05 product of csrc/gemm_tcgen05.cu: TMA -> swizzled shared memory -> tcgen05.mma -> tensor memory."""
+    M, K = x.shape
+    epi = {"none": 0, "silu_mul": 1}[epilogue]
+    N = weight.shape[0] // 2 if epi else weight.shape[0]
+    if tile_n is None:
+        # The widest accumulator that still gives every SM about two tiles; the SiLU epilogue (half as many
+        # output columns per tile) does best at 128 until there are very many rows.
+        m_tiles = (M + 127) // 128
+        if epi:
+            tile_n = 256 if M >= 4096 else 128
+        else:
+            tile_n = next((bn for bn in (256, 128) if m_tiles * ((N + bn - 1) // bn) >= 200), 64)
+    bn = tile_n
+    _need(tcgen05_takes(x, weight) or M < TCGEN05_MIN_ROWS, "linear_tcgen05: operands not taken")
+    box_w = bn // 2 if epi else bn
+    _call("me_gemm_tcgen05", matrix_tensor_map(x, 128).ptr, matrix_tensor_map(weight, box_w).ptr, out.data_ptr(), _dt(out),
+          out.stride(0), M, N, K, epi, bn, err.data_ptr(), _stream())
+
+
+_gemm_err: dict = {}
+
+
+def _gemm_error_word(device) -> torch.Tensor:
+    t = _gemm_err.get(device)
+    if t is None:
+        t = _gemm_err[device] = torch.zeros(4, dtype=torch.int32, device=device)
+    return t
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "none",
-           workspace=None) -> None:
+           workspace=None, err: Optional[torch.Tensor] = None) -> None:
     """``out = x @ weight.T`` with float32 accumulation; ``epilogue="silu_mul"`` takes a weight of
     rows gate | up and writes ``silu(x Wg^T) * (x Wu^T)``.
 
     float32 operands (and any mix of dtypes) run the CUDA-core kernel of csrc/gemm_simt.cu: plain
-    FMA, no reduced-precision matrix mode.  bfloat16 x bfloat16 products go to cuBLAS, as the
-    reference's do through ``F.linear`` (layers/linear.py:26,45), with SiLU-and-multiply as a
-    kernel of ours behind it."""
+    FMA, no reduced-precision matrix mode.  bfloat16 x bfloat16 products run csrc/gemm_skinny.cu for up
+    to 16 rows (decode) and the tcgen05 kernel of csrc/gemm_tcgen05.cu above that; shapes those refuse
+    (K no multiple of 8) go to cuBLAS, as all the reference's products do through ``F.linear``
+    (layers/linear.py:26,45), with SiLU-and-multiply as a kernel of ours behind it."""
     global library_calls
     M, K = x.shape
     _need(weight.dim() == 2 and weight.shape[1] == K and weight.is_contiguous(), "linear: weight shape")
@@ -204,6 +263,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
     if skinny_splits(M, K, x, weight) == 1 and (epi == 0 or out.dtype == torch.bfloat16):
         _call("me_gemm_skinny", x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), _dt(out), out.stride(0),
               0, M, N, K, epi, _stream())
+        return
+    if use_tcgen05_gemm and tcgen05_takes(x, weight) and (epi == 0 or out.dtype == torch.bfloat16):
+        linear_tcgen05(x, weight, out, epilogue, err if err is not None else _gemm_error_word(x.device))
         return
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.is_cuda:
         if epi == 0 and out.dtype == torch.bfloat16:

@@ -46,5 +46,5 @@ class Linear(Part):
                 return part
         n_out = self.out_features // 2 if epilogue == "silu_mul" else self.out_features
         out = ctx.buffer(out_name, (x.shape[0], n_out), out_dtype or ctx.act_dtype)
-        ops.linear(x, self.weight, out, epilogue=epilogue, workspace=ctx.buffer)
+        ops.linear(x, self.weight, out, epilogue=epilogue, workspace=ctx.buffer, err=ctx.error_flag)
         return out

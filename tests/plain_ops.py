@@ -55,7 +55,7 @@ def linear_partials(x, weight, workspace, name):
     return None
 
 
-def linear(x, weight, out, epilogue="none", workspace=None):
+def linear(x, weight, out, epilogue="none", workspace=None, err=None):
     # layers/linear.py:26,45 (F.linear), float32 accumulate
     y = x.float() @ weight.float().T
     if epilogue == "silu_mul":

@@ -146,6 +146,28 @@ def test_small_batch_products(ops, M, N, K):
         close(out, ref2, torch.bfloat16, scale=4)
 
 
+@pytest.mark.parametrize("M, N, K", [(128, 64, 64), (128, 128, 64), (129, 200, 136), (300, 4096, 1024), (2048, 1024, 2048),
+                                     (1000, 1032, 3072), (64, 151936 // 16, 1024)])
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+def test_tcgen05_products(ops, M, N, K, tile_n):
+    # the tcgen05 kernel by name: every tile width, edges in M, N and K, bfloat16 and float32 results, SiLU epilogue
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    for od in (torch.bfloat16, torch.float32):
+        out, ref = torch.full((M, N), float("nan"), dtype=od, device=DEV), torch.empty(M, N, dtype=od, device=DEV)
+        ops.linear_tcgen05(x, w, out, "none", err, tile_n=tile_n)
+        plain_ops.linear(x, w, ref)
+        assert err.tolist() == [0, 0, 0, 0]
+        close(out, ref, od, scale=4)
+    if N % 2 == 0:
+        I = N // 2
+        out, ref = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV), torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+        ops.linear_tcgen05(x, w, out, "silu_mul", err, tile_n=tile_n)
+        plain_ops.linear(x, w, ref, epilogue="silu_mul")
+        assert err.tolist() == [0, 0, 0, 0]
+        close(out, ref, torch.bfloat16, scale=4)
+
+
 def test_linear_rows_do_not_depend_on_the_batch(ops):
     x, w = rnd(70, 96, seed=1), rnd(224, 96, seed=2)
     full, one = torch.empty(70, 224, device=DEV), torch.empty(1, 224, device=DEV)
