@@ -1,0 +1,393 @@
+// Paged attention for portions of prompts on tcgen05 / tensor memory (bfloat16, head_dim 64 or 128,
+// page sizes that divide 128).
+//
+// Semantics as in csrc/attention_prefill_mma.cu and the reference's csrc/paged_prefill.cu:177-247:
+// a tile of queries against tiles of cached keys found through the block table, online softmax in
+// float32, P rounded to bfloat16 before P V, O / l at the end; optional window.
+//
+// One block = 128 rows = (128 / GP query tokens) x (GP heads of one key/value head), row r being head
+// r / TQ, token r % TQ.  Key tiles of 128 keys at absolute multiples of 128.
+//   warp 0, one thread: TMA.  Q once (a box per head and 64-column half), then per key tile the pages
+//     of K and V (a box per page and half, 128-byte swizzle) into two buffers.
+//   warp 1, one thread: tcgen05.mma.  S[128x128] = Q K^T into one of two S buffers in tensor memory
+//     (K-major operands), one tile ahead of the softmax; after the softmax warps have written P:
+//     O_tile[128 x head_dim] = P V, with V as an MN-major operand.
+//   warps 2..9 (256 threads, two per row, each with half of the columns): read S from tensor memory, mask,
+//     maximum and sum, write P (bfloat16) into one of two buffers in shared memory in the swizzled K-major
+//     layout.  O stays in tensor memory, where P V accumulates over the key tiles; a row's reference
+//     maximum is only raised when the new maximum exceeds it by more than 2^8 (the values of P stay below
+//     256 meanwhile), and then the row of O is rescaled in tensor memory.  So the softmax of a tile does not
+//     wait for the P V of the tile before; at the end O is read once and divided by the row's sum.
+// Blocks take the query tiles from the last to the first, the ones with most keys first.
+// All waits are bounded; a wait that gives up sets flag 1 of ``err`` and the block frees its tensor
+// memory and exits.
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int TA_ROWS = 128, TA_THREADS = 352;      // warp 0: K loads, 1: MMA, 2..9: softmax, 10: V loads
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tma::smem_addr(bar)) : "memory");
+}
+
+template <int HD, int TA_KEYS>
+__global__ void __launch_bounds__(TA_THREADS)
+attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+                            bf16* __restrict__ out, int64_t out_row_stride, const int* __restrict__ block_tables,
+                            int bt_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
+                            const int* __restrict__ tiles, int nh, int nkv, int gp, int page_size, float scale_log2,
+                            int window, int* __restrict__ err) {
+  constexpr int HALVES = HD / 64;
+  constexpr int Q_BYTES = TA_ROWS * HD * 2, KV_BYTES = TA_KEYS * HD * 2, P_BYTES = TA_ROWS * TA_KEYS * 2;
+  constexpr int HALF_BYTES = 128 * 128;                 // one [128][64] bfloat16 block
+  constexpr int KB_BYTES = TA_KEYS * 128;               // one [TA_KEYS][64] bfloat16 block of K or V
+  constexpr uint32_t TMEM_COLS = TA_KEYS == 128 ? 512 : 256;   // two S buffers of TA_KEYS columns, then the O tile
+  extern __shared__ unsigned char ta_smem_raw[];
+  __shared__ __align__(8) unsigned long long q_bar, kv_full[2], kv_empty[2], s_ready[2], p_ready, p_free[2], o_ready;
+  __shared__ uint32_t tmem_slot;
+  __shared__ float l_other[TA_ROWS];
+  __shared__ float m_half[2][TA_ROWS];                  // the two threads of a row tell each other their half's maximum
+  unsigned char* smem = ta_smem_raw + ((1024u - (tma::smem_addr(ta_smem_raw) & 1023u)) & 1023u);
+  unsigned char* q_s = smem;
+  unsigned char* k_s = q_s + Q_BYTES;                   // 2 buffers
+  unsigned char* v_s = k_s + 2 * KV_BYTES;              // 2 buffers
+  unsigned char* p_s = v_s + 2 * KV_BYTES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int G = nh / nkv, packs = G / gp, tq = TA_ROWS / gp;
+  // grid.x runs over the head packs and grid.y over the query tiles from the last to the first, so blocks are
+  // handed out with the most keys first across all heads.
+  const int tile = gridDim.y - 1 - blockIdx.y;
+  const int b = tiles[2 * tile], q0 = tiles[2 * tile + 1];
+  const int kvh = blockIdx.x / packs, head0 = kvh * G + (blockIdx.x % packs) * gp;
+  const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0;
+  const int L = context_lens[b], start = L - q_len;
+  const int n_tok = min(tq, q_len - q0);
+  const int p_lo = start + q0, p_hi = p_lo + n_tok - 1, hi = p_hi + 1;
+  int lo = window > 0 ? max(0, p_lo - window + 1) : 0;
+  const int lo_seen = lo;                                // keys below this are seen by no row of the tile
+  lo = (lo / TA_KEYS) * TA_KEYS;
+  const int n_tiles = (hi - lo + TA_KEYS - 1) / TA_KEYS;
+  const int* bt = block_tables + (int64_t)b * bt_stride;
+
+  if (threadIdx.x == 0) {
+    tma::mbar_init(&q_bar, 1);
+    for (int s = 0; s < 2; ++s) {
+      tma::mbar_init(&kv_full[s], 2);                     // the K producer and the V producer each announce their bytes
+      tma::mbar_init(&kv_empty[s], 1);
+    }
+    tma::mbar_init(&s_ready[0], 1);
+    tma::mbar_init(&s_ready[1], 1);
+    tma::mbar_init(&p_ready, 8);                          // one arrival per softmax warp
+    tma::mbar_init(&p_free[0], 1);
+    tma::mbar_init(&p_free[1], 1);
+    tma::mbar_init(&o_ready, 1);
+    tma::mbar_fence_init();
+    tma::prefetch_map(&q_map);
+    tma::prefetch_map(&kv_map);
+  }
+  if (warp == 1) tc5::tmem_alloc(&tmem_slot, TMEM_COLS);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + 2 * TA_KEYS;
+  pdl_wait();                                            // q, and the newest keys and values, come from the kernel before
+  bool ok = true;
+
+  if (warp == 0 || warp == 10) {
+    if (lane == 0) {
+      const bool is_v = warp == 10;
+      if (!is_v) {
+        // Q: head h of the pack, 64-column half c -> block c of the A operand, rows h * tq ...
+        tma::mbar_expect_tx(&q_bar, (unsigned)(gp * HALVES * tq * 128));
+        for (int h = 0; h < gp; ++h)
+          for (int c = 0; c < HALVES; ++c)
+            tma::load_2d(q_s + c * HALF_BYTES + h * tq * 128, &q_map, (head0 + h) * HD + c * 64, tok0 + q0, &q_bar);
+      }
+      // Two threads stream the pages of a key tile: this one K (warp 0) or V (warp 10).
+      const int pages_per_tile = TA_KEYS / page_size;
+      const unsigned box_bytes = (unsigned)page_size * 128;
+      const int row_off = is_v ? nkv * page_size : 0;
+      unsigned char* dst0 = is_v ? v_s : k_s;
+      for (int it = 0; it < n_tiles && ok; ++it) {
+        const int s = it & 1, kt = lo + it * TA_KEYS;
+        ok = tma::mbar_wait(&kv_empty[s], ((it >> 1) & 1) ^ 1);
+        if (!ok) break;
+        int first_row[TA_KEYS / 8];
+        unsigned bytes = 0;
+        for (int i = 0; i < pages_per_tile; ++i) {
+          const int j0 = kt + i * page_size;
+          int page = -1;
+          if (j0 < hi && j0 + page_size > lo_seen) page = bt[j0 / page_size];
+          first_row[i] = page < 0 ? -1 : ((page * 2) * nkv + kvh) * page_size + row_off;
+          if (page >= 0) bytes += HALVES * box_bytes;
+        }
+        tma::mbar_expect_tx(&kv_full[s], bytes);
+        for (int i = 0; i < pages_per_tile; ++i) {
+          if (first_row[i] < 0) continue;
+          for (int c = 0; c < HALVES; ++c)
+            tma::load_2d(dst0 + s * KV_BYTES + c * KB_BYTES + i * page_size * 128, &kv_map, c * 64, first_row[i], &kv_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = tc5::instr_desc_bf16(TA_ROWS, TA_KEYS);
+      constexpr uint32_t idesc_o = tc5::instr_desc_bf16(TA_ROWS, HD, true);
+      ok = tma::mbar_wait(&q_bar, 0);
+      // S(it) = Q K(it)^T into S buffer it % 2.  The buffer was last read by the softmax of tile it - 2, which
+      // arrived on p_ready(it - 2) before this thread issued P V (it - 2).
+      auto issue_qk = [&](int it) -> bool {
+        const int s = it & 1;
+        if (!tma::mbar_wait(&kv_full[s], (it >> 1) & 1)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < HALVES; ++c) {
+          const uint64_t a_desc = tc5::smem_desc_k_major_sw128(q_s + c * HALF_BYTES);
+          const uint64_t b_desc = tc5::smem_desc_k_major_sw128(k_s + s * KV_BYTES + c * KB_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc5::mma_f16(tmem_s + s * TA_KEYS, a_desc + 2 * k, b_desc + 2 * k, idesc_s, c > 0 || k > 0);
+        }
+        tc5::commit(&s_ready[s]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int it = 0; it < n_tiles && ok; ++it) {
+        const int s = it & 1;
+        if (it + 1 < n_tiles) {                            // one tile ahead: runs while the softmax works on tile it
+          ok = issue_qk(it + 1);
+          if (!ok) break;
+        }
+        ok = tma::mbar_wait(&p_ready, it & 1);             // P(it) is in shared memory, O is rescaled if it had to be
+        if (!ok) break;
+        tc5::fence_after_sync();
+        // O += P V: A = P [128 rows][TA_KEYS] K-major (blocks of 64 keys); B = V [TA_KEYS][HD], MN-major:
+        // 16 keys per MMA are 2048 bytes further in every 64-column half, the halves are KB_BYTES apart.
+#pragma unroll
+        for (int k = 0; k < TA_KEYS / 16; ++k) {
+          const uint64_t a_desc = tc5::smem_desc_k_major_sw128(p_s + s * P_BYTES + (k >> 2) * HALF_BYTES) + 2 * (k & 3);
+          const uint64_t b_desc = tc5::smem_desc_mn_major_sw128(v_s + s * KV_BYTES + k * 2048, KB_BYTES);
+          tc5::mma_f16(tmem_o, a_desc, b_desc, idesc_o, it > 0 || k > 0);     // O accumulates over the key tiles
+        }
+        tc5::commit(&o_ready);                             // P V (it) and everything before it are done
+        tc5::commit(&p_free[s]);
+        tc5::commit(&kv_empty[s]);
+      }
+    }
+  } else {
+    // Two threads per row: warps 2..5 take columns 0..63 of S, P and the first half of O's columns, warps 6..9
+    // the other halves.  (A warp may read the 32 lanes of tensor memory given by its index modulo 4.)
+    constexpr int OC = HD / 2;                            // O columns per thread
+    const int lane_base = (warp & 3) * 32, half = (warp - 2) >> 2;
+    const int r = lane_base + lane;
+    const int hh = r / tq, tk = r % tq;
+    const bool row_ok = tk < n_tok;
+    const int pos = p_lo + tk;
+    const uint32_t t_o = tmem_o + ((uint32_t)lane_base << 16) + half * OC;
+    float m = -INFINITY, l = 0.f;                          // m: the row's reference maximum (may lag behind the true one)
+    const float neg_inf = -INFINITY;
+    // Every softmax warp runs every tile's barriers, also after a wait has given up (ok == false): then only the
+    // work is skipped, so no warp is left waiting at a barrier for a partner that has gone.
+    for (int it = 0; it < n_tiles; ++it) {
+      const int s = it & 1, kt = lo + it * TA_KEYS;
+      const uint32_t t_s = tmem_s + s * TA_KEYS + ((uint32_t)lane_base << 16);
+      constexpr int KH = TA_KEYS / 2;
+      float sv[KH];
+      float mx = neg_inf;
+      const bool need_mask = kt + TA_KEYS - 1 > p_lo || (window > 0 && kt <= p_hi - window) || n_tok * gp < TA_ROWS;
+      if (ok) ok = tma::mbar_wait(&kv_full[s], (it >> 1) & 1);
+      if (ok && (kt + TA_KEYS > hi || kt < lo_seen)) {
+        // Rows of V that hold no key this tile may use must be zero (0 * anything-else would not be 0):
+        // thread (r, half) clears its 64-column half of key row r.
+        const int j = kt + r;
+        if (r < TA_KEYS && (j >= hi || j < lo_seen) && half < HALVES) {
+          uint4* row = reinterpret_cast<uint4*>(v_s + s * KV_BYTES + half * KB_BYTES + r * 128);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) row[q] = make_uint4(0, 0, 0, 0);
+        }
+      }
+      if (ok) ok = tma::mbar_wait(&s_ready[s], (it >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc5::fence_after_sync();
+        // This thread's half of the row's scores, read once and kept.
+        if (KH == 64) {
+          tc5::ld_64cols(t_s + half * KH, *reinterpret_cast<float(*)[64]>(sv));
+        } else {
+          tc5::ld_32cols(t_s + half * KH, *reinterpret_cast<float(*)[32]>(sv));
+        }
+        tc5::wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int jj = 0; jj < KH; ++jj) {
+            const int j = kt + half * KH + jj;
+            if (!(row_ok && j <= pos && (window <= 0 || j > pos - window))) sv[jj] = neg_inf;
+            mx = fmaxf(mx, sv[jj]);
+          }
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < KH; ++jj) mx = fmaxf(mx, sv[jj]);
+        }
+      }
+      // The half's maximum goes to the partner thread (same row, other half: four warps further).
+      m_half[half][r] = mx;
+      asm volatile("bar.sync %0, 64;\n" ::"r"(2 + (warp & 3)) : "memory");
+      mx = fmaxf(mx, m_half[half ^ 1][r]);
+      asm volatile("bar.sync %0, 64;\n" ::"r"(2 + (warp & 3)) : "memory");      // read before the next tile overwrites
+      if (ok) {
+        // Raise the reference maximum only on the first tile with a seen key and when the new maximum is more
+        // than 2^8 (in the exponent's units) above it; both threads of a row decide alike.
+        const bool raise = mx > neg_inf && (m == neg_inf || (mx - m) * scale_log2 > 8.0f);
+        float alpha = 1.f;
+        if (raise) {
+          alpha = ex2((m - mx) * scale_log2);                // m = -inf gives 0
+          m = mx;
+          l *= alpha;
+        }
+        if (it > 0 && __any_sync(0xffffffffu, raise)) {
+          // Rescale this thread's half of its row of O in tensor memory, after P V (it - 1) has finished.
+          ok = tma::mbar_wait(&o_ready, (it - 1) & 1);
+          if (ok) {
+            tc5::fence_after_sync();
+            float v[OC];
+            if (OC == 64) tc5::ld_64cols(t_o, *reinterpret_cast<float(*)[64]>(v));
+            else tc5::ld_32cols(t_o, *reinterpret_cast<float(*)[32]>(v));
+            tc5::wait_ld();
+#pragma unroll
+            for (int jj = 0; jj < OC; ++jj) v[jj] *= alpha;
+            if (OC == 64) tc5::st_64cols(t_o, *reinterpret_cast<float(*)[64]>(v));
+            else tc5::st_32cols(t_o, *reinterpret_cast<float(*)[32]>(v));
+            tc5::wait_st();
+          }
+        }
+      }
+      if (ok) ok = tma::mbar_wait(&p_free[s], ((it >> 1) & 1) ^ 1);      // P V (it - 2) has read this P buffer
+      if (ok) {
+        const float mu_s = (m == neg_inf ? 0.f : m) * scale_log2;
+        // p = 2^(s * scale - reference * scale) (masked scores are -inf and give 0), rounded to bfloat16 into P:
+        // keys c .. c+31 of row r are in block c / 64, 16-byte pieces (c % 64) / 8 .. +3, swizzled by the row
+#pragma unroll
+        for (int c0 = 0; c0 < KH; c0 += 32) {
+          const int c = half * KH + c0;
+          uint32_t pk[16];
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 2) {
+            const float p0 = ex2(fmaf(sv[c0 + jj], scale_log2, -mu_s)), p1 = ex2(fmaf(sv[c0 + jj + 1], scale_log2, -mu_s));
+            l += p0 + p1;
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+            pk[jj >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+          }
+          unsigned char* row = p_s + s * P_BYTES + (c >> 6) * HALF_BYTES + r * 128;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int piece = ((c & 63) >> 3) + q;
+            *reinterpret_cast<uint4*>(row + ((piece ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+          }
+        }
+        // P (and the zeroed rows of V) were written by ordinary stores: make them visible to the tensor core's reads.
+        fence_async_smem();
+        tc5::fence_before_sync();
+      }
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(&p_ready);            // ok is the same in all lanes of a warp here
+    }
+    // the row's sum is the two threads' sums; softmax warps meet at a named barrier of their own
+    if (half == 1) l_other[r] = l;
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (half == 0) l += l_other[r];
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (half == 0) l_other[r] = l;
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    l = l_other[r];
+    if (ok) ok = tma::mbar_wait(&o_ready, (n_tiles - 1) & 1);          // the last P V is done
+    float o_acc[OC];
+    if (ok) {
+      tc5::fence_after_sync();
+      if (OC == 64) tc5::ld_64cols(t_o, *reinterpret_cast<float(*)[64]>(o_acc));
+      else tc5::ld_32cols(t_o, *reinterpret_cast<float(*)[32]>(o_acc));
+      tc5::wait_ld();
+    }
+    if (ok && row_ok) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = out + (int64_t)(tok0 + q0 + tk) * out_row_stride + (int64_t)(head0 + hh) * HD + half * OC;
+#pragma unroll
+      for (int q = 0; q < OC / 8; ++q) {
+        uint4 pk;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) h2[jj] = __floats2bfloat162_rn(o_acc[q * 8 + 2 * jj] * inv, o_acc[q * 8 + 2 * jj + 1] * inv);
+        *reinterpret_cast<uint4*>(dst + q * 8) = pk;
+      }
+    }
+  }
+  if (!ok) atomicOr(err + 1, 1);
+  pdl_launch_dependents();
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tc5::tmem_dealloc(tmem_slot, TMEM_COLS);
+}
+
+template <int HD, int KT>
+int launch_ta(const void* q_map, const void* kv_map, void* out, int64_t out_row_stride, const int* block_tables, int bt_stride,
+              const int* cu_seqlens, const int* context_lens, const int* tiles, int num_tiles, int nh, int nkv, int gp,
+              int page_size, float scale, int window, int* err, cudaStream_t stream) {
+  const size_t smem = (size_t)TA_ROWS * HD * 2 + 4 * (size_t)KT * HD * 2 + 2 * (size_t)TA_ROWS * KT * 2 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<HD, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ME_REQUIRE(e == cudaSuccess, "me_attn_prefill_tcgen05: cannot raise shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  dim3 grid(nkv * (nh / nkv / gp), num_tiles);
+  me_launch(attn_prefill_tcgen05_kernel<HD, KT>, grid, dim3(TA_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(q_map),
+            *reinterpret_cast<const CUtensorMap*>(kv_map), (bf16*)out, out_row_stride, block_tables, bt_stride, cu_seqlens,
+            context_lens, tiles, nh, nkv, gp, page_size, scale * 1.4426950408889634f, window, err);
+  return 0;
+}
+
+}  // namespace
+
+// How many heads of a group share a block of the tcgen05 prefill kernel (a block covers 128 / that many
+// query tokens); 0 if the kernel refuses the shape.
+ME_API int me_attn_prefill_tcgen05_heads_per_block(int nh, int nkv, int hd, int page_size) {
+  if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size < 8 || 128 % page_size) return 0;
+  const int G = nh / nkv;
+  for (int gp = 16; gp >= 1; gp >>= 1)
+    if (G % gp == 0) return gp;
+  return 1;
+}
+
+// q_map: the step's packed q|k|v rows as [tokens][row width], boxes (128 / heads-per-block) x 64; kv_map: the cache
+// slot as [pages * 2 * kv_heads * page_size][head_dim], boxes page_size x 64; both with the 128-byte swizzle.
+// ``tiles``: (request, first local query) per block, each covering 128 / heads-per-block query tokens.
+ME_API int me_attn_prefill_tcgen05(const void* q_map, const void* kv_map, void* out, int64_t out_row_stride,
+                                   const int* block_tables, int bt_stride, const int* cu_seqlens, const int* context_lens,
+                                   const int* tiles, int num_tiles, int nh, int nkv, int hd, int page_size, float scale,
+                                   int window, int key_tile, int* err, cudaStream_t stream) {
+  if (num_tiles == 0) return 0;
+  const int gp = me_attn_prefill_tcgen05_heads_per_block(nh, nkv, hd, page_size);
+  ME_REQUIRE(gp > 0, "me_attn_prefill_tcgen05: head_dim %d, %d/%d heads, pages of %d are not taken", hd, nh, nkv, page_size);
+  ME_REQUIRE(q_map != nullptr && kv_map != nullptr && err != nullptr, "me_attn_prefill_tcgen05: tensor maps and the error word are required");
+  ME_REQUIRE((out_row_stride * 2) % 16 == 0 && ((uintptr_t)out & 15) == 0, "me_attn_prefill_tcgen05: output rows must be 16-byte aligned");
+  ME_REQUIRE(num_tiles <= 65535, "me_attn_prefill_tcgen05: %d query tiles in one step are too many", num_tiles);
+  // key_tile: keys per step of the loop, 64 or 128 (0: 128, the faster one; 64 needs less shared and tensor memory).
+  if (key_tile == 0) key_tile = 128;
+  ME_REQUIRE((key_tile == 64 || key_tile == 128) && key_tile % page_size == 0, "me_attn_prefill_tcgen05: key tile %d with pages of %d",
+             key_tile, page_size);
+  int rc;
+#define ME_TA_ARGS q_map, kv_map, out, out_row_stride, block_tables, bt_stride, cu_seqlens, context_lens, tiles, num_tiles, nh, nkv, gp, \
+                   page_size, scale, window, err, stream
+  if (hd == 64) rc = key_tile == 64 ? launch_ta<64, 64>(ME_TA_ARGS) : launch_ta<64, 128>(ME_TA_ARGS);
+  else rc = key_tile == 64 ? launch_ta<128, 64>(ME_TA_ARGS) : launch_ta<128, 128>(ME_TA_ARGS);
+#undef ME_TA_ARGS
+  if (rc) return rc;
+  ME_LAUNCH_CHECK("me_attn_prefill_tcgen05");
+  return 0;
+}

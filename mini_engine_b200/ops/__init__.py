@@ -15,7 +15,7 @@ import torch
 from . import build as _build
 
 ATTN_TILE_Q = 16          # query tokens per block of the CUDA-core chunk kernel (csrc/attention_chunk.cu)
-ATTN_TILE_SIZES = (8, 16, 32, 64)   # query tokens per block that some attention kernel may ask for
+ATTN_TILE_SIZES = (8, 16, 32, 64, 128)   # query tokens per block that some attention kernel may ask for
 DECODE_PARTITION = 128    # keys per partition of the decode kernel (csrc/attention_decode.cu)
 MAX_HEAD_DIM = 256
 
@@ -30,6 +30,7 @@ _PROTOS = {
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
+    "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
@@ -61,6 +62,7 @@ def require_extension() -> ctypes.CDLL:
     if lib.me_attn_chunk_tile_q() != ATTN_TILE_Q or lib.me_attn_decode_partition() != DECODE_PARTITION:
         raise KernelError("the kernel library and ops/__init__.py disagree on tile sizes")
     lib.me_attn_prefill_heads_per_block.argtypes = [_I, _I, _I]
+    lib.me_attn_prefill_tcgen05_heads_per_block.argtypes = [_I, _I, _I, _I]
     lib.me_sample_chunks.argtypes = [_I]
     lib.me_gemm_skinny_splits.argtypes = [_I]
     _lib = lib
@@ -372,6 +374,30 @@ def kv_tensor_map(pool: torch.Tensor, page_size: int) -> Optional[TensorMap]:
     return tm
 
 
+def prefill_tcgen05_heads_per_block(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> int:
+    """How many heads of a group share a block of the tcgen05 prefill kernel; 0 if it refuses the shape."""
+    return (_lib or require_extension()).me_attn_prefill_tcgen05_heads_per_block(num_heads, num_kv_heads, head_dim, page_size)
+
+
+def attention_prefill_tcgen05(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
+                              scale, window, tiles=None, num_tiles=None, key_tile: int = 0) -> None:
+    """The tcgen05 / tensor-memory prefill kernel (bfloat16, head_dim 64 or 128, page sizes dividing 128) over
+    tiles of 128 / heads-per-block tokens; Q, K and V arrive by tensor-map loads."""
+    gp = prefill_tcgen05_heads_per_block(num_heads, num_kv_heads, head_dim, page_size)
+    _need(gp > 0 and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and qkv.data_ptr() % 16 == 0,
+          "attention_prefill_tcgen05: shape or dtype not taken by the kernel")
+    tq = 128 // gp
+    if tiles is None:
+        tiles, num_tiles = meta.tile_lists[tq]
+    _call("me_attn_prefill_tcgen05", matrix_tensor_map(qkv, tq).ptr, kv_tensor_map(pool, page_size).ptr, out.data_ptr(),
+          out.stride(0), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
+          meta.context_lens.data_ptr(), tiles.data_ptr(), num_tiles, num_heads, num_kv_heads, head_dim, page_size,
+          float(scale), int(window or 0), key_tile, meta.error_flag.data_ptr(), _stream())
+
+
+use_tcgen05_attention = True   # False: portions of prompts use the mma.sync kernel instead (a switch for comparisons)
+
+
 def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
                      scale, window, kind: str = "auto") -> None:
     """The split-K decode kernel and its merge over requests [0, meta.num_decodes).
@@ -406,8 +432,13 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv
     if meta.num_decodes > 0:
         attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window)
     if meta.num_tiles > 0:
-        fn = attention_prefill if (qkv.dtype == torch.bfloat16
-                                   and prefill_heads_per_block(num_heads, num_kv_heads, head_dim) > 0) else attention_chunks
+        fn = attention_chunks
+        if qkv.dtype == torch.bfloat16:
+            if (use_tcgen05_attention and meta.error_flag is not None and qkv.is_contiguous()
+                    and prefill_tcgen05_heads_per_block(num_heads, num_kv_heads, head_dim, page_size) > 0):
+                fn = attention_prefill_tcgen05
+            elif prefill_heads_per_block(num_heads, num_kv_heads, head_dim) > 0:
+                fn = attention_prefill
         fn(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window)
 
 

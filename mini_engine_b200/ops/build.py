@@ -24,7 +24,7 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 LIB_NAME = "libmini_engine_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-              "--expt-relaxed-constexpr"]
+              "--expt-relaxed-constexpr"] + os.environ.get("MINI_ENGINE_NVCC_FLAGS", "").split()
 
 
 class BuildError(RuntimeError):

@@ -12,7 +12,7 @@ import numpy as np
 import torch
 
 ATTN_TILE_Q = 16
-ATTN_TILE_SIZES = (8, 16, 32, 64)
+ATTN_TILE_SIZES = (8, 16, 32, 64, 128)
 DECODE_PARTITION = 128
 
 

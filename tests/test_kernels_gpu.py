@@ -290,9 +290,13 @@ def run_attention(ops, bt: Batch, dtype, window, which="split"):
     elif which == "chunks":                                                # everything through the CUDA-core chunk kernel
         tiles, n = bt.all_tiles[ops.ATTN_TILE_Q]
         ops.attention_chunks(bt.qkv, out, *args, tiles=tiles, num_tiles=n)
-    else:                                                                  # everything through the tensor-core kernel
+    elif which == "tensor":                                                # everything through the mma.sync kernel
         tiles, n = bt.all_tiles[64 // ops.prefill_heads_per_block(bt.nh, bt.nkv, bt.hd)]
         ops.attention_prefill(bt.qkv, out, *args, tiles=tiles, num_tiles=n)
+    else:                                                                  # everything through the tcgen05 kernel
+        tiles, n = bt.all_tiles[128 // ops.prefill_tcgen05_heads_per_block(bt.nh, bt.nkv, bt.hd, bt.page)]
+        key_tile = 128 if which.endswith("128") or bt.page > 64 else 64
+        ops.attention_prefill_tcgen05(bt.qkv, out, *args, tiles=tiles, num_tiles=n, key_tile=key_tile)
     plain_ops.paged_attention(bt.qkv, ref, *args)
     assert not out.isnan().any(), "the kernel read a slot that no request owns (NaN-filled pool)"
     assert bt.meta.error_flag.tolist() == [0, 0, 0, 0]
@@ -323,10 +327,12 @@ def test_attention_tensor_core_prefill(ops, nh, nkv, hd, page, window):
     ctx = [1, 300, 257, 31, 33, 64, 150, 16, 512, 129, 65]
     ql = [1, 1, 1, 31, 17, 64, 2, 16, 130, 129, 64]
     b = Batch(ctx, ql, nh, nkv, hd, page, torch.bfloat16, seed=hd + nh, window=window)
-    for which in ("split", "tensor"):
+    kinds = ["split", "tensor"] + (["tcgen05", "tcgen05_128"] if ops.prefill_tcgen05_heads_per_block(nh, nkv, hd, page) else [])
+    for which in kinds:
         out, ref = run_attention(ops, b, torch.bfloat16, window, which)
         close(out, ref, torch.bfloat16)
     assert ops.prefill_heads_per_block(8, 2, 32) == 0 and ops.prefill_heads_per_block(8, 2, 96) == 0
+    assert ops.prefill_tcgen05_heads_per_block(16, 8, 128, 16) == 2 and ops.prefill_tcgen05_heads_per_block(16, 8, 128, 24) == 0
 
 
 @pytest.mark.parametrize("kind", ["cuda_cores", "bulk_copy", "tensor_cores", "tensor_cores_tma"])
@@ -351,10 +357,10 @@ def test_attention_decode_kernels_by_name(ops, kind, nh, nkv, hd, page, window):
 
 
 @pytest.mark.parametrize("dt", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["split", "chunks", "tensor"])
+@pytest.mark.parametrize("which", ["split", "chunks", "tensor", "tcgen05"])
 def test_attention_finds_one_far_key_among_hundreds(ops, dt, which):
-    if which == "tensor" and dt != "bfloat16":
-        pytest.skip("the tensor-core kernel is bfloat16 only")
+    if which in ("tensor", "tcgen05") and dt != "bfloat16":
+        pytest.skip("the tensor-core kernels are bfloat16 only")
     # one key far back gets a score that stands out: the output must be (nearly) its value
     ctx, ql = [700, 1000, 520, 300], [1, 1, 40, 16]
     far = {0: 3, 1: 511, 2: 256, 3: 15}                                  # page edges, partition edges, the start
@@ -370,11 +376,11 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dt, which):
 
 
 @pytest.mark.parametrize("dt", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["split", "chunks", "tensor"])
+@pytest.mark.parametrize("which", ["split", "chunks", "tensor", "tcgen05"])
 @pytest.mark.parametrize("edge", [0, 1])
 def test_attention_window_edge(ops, dt, which, edge):
-    if which == "tensor" and dt != "bfloat16":
-        pytest.skip("the tensor-core kernel is bfloat16 only")
+    if which in ("tensor", "tcgen05") and dt != "bfloat16":
+        pytest.skip("the tensor-core kernels are bfloat16 only")
     # the standout key sits exactly at the window's edge (edge=0: last key still seen, edge=1: first not seen)
     w = 40
     ctx, ql = [300, 130, 97], [1, 30, 1]
