@@ -75,7 +75,7 @@ class LLMEngine:
         for s in seqs:
             a, n = s.num_computed_tokens, s.num_scheduled_tokens
             wants = s.samples_this_step
-            items.append(StepItem(s, s.token_ids[a:a + n], a, [n - 1] if wants else [],
+            items.append(StepItem(s, s.scheduled_tokens(), a, [n - 1] if wants else [],
                                   (s.sampling_params.temperature, self._seed_of(s)) if wants else None))
             if wants:
                 samplers.append(s)
