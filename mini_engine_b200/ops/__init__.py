@@ -29,6 +29,7 @@ _PROTOS = {
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
+    "me_gemm_decode": [_I, _I, _P, _L, _P, _P, _P, _I, _F, _P, _P, _I, _L, _P, _P, _I, _I, _I, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
     "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
@@ -184,6 +185,49 @@ def linear_partials(x: torch.Tensor, weight: torch.Tensor, workspace, name: str)
     part = workspace(name, (splits, M, N), torch.float32)
     _call("me_gemm_skinny", x.data_ptr(), x.stride(0), weight.data_ptr(), 0, 0, 0, part.data_ptr(), M, N, K, 0, _stream())
     return part
+
+
+DECODE_MAX_K = 3072       # largest K of csrc/gemm_decode.cu (one block covers all of K)
+
+
+def decode_linear_takes(M: int, K: int, weight: torch.Tensor) -> bool:
+    """Whether csrc/gemm_decode.cu (products of up to 16 rows with norm / residual folded in) takes the shape."""
+    return (weight.is_cuda and weight.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0
+            and K <= DECODE_MAX_K and weight.data_ptr() % 16 == 0)
+
+
+def decode_linear(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, normed=None, out: Optional[torch.Tensor] = None,
+                  epilogue: str = "none", residual_out: Optional[torch.Tensor] = None,
+                  sumsq_out: Optional[torch.Tensor] = None) -> None:
+    """One decode product with its neighbours folded in.
+
+    Input: ``x`` (bfloat16 [M, K]) or ``normed`` = (residual float32 [M, K], norm weight float32 [K], eps, sums of
+    squares float32 [parts, M]) for X = rmsnorm(residual) * weight.  Output: ``out`` (epilogue "none" or
+    "silu_mul") or ``residual_out`` (float32 [M, N], epilogue "residual": residual_out += X W^T, and
+    ``sumsq_out`` [ceil(N/16), M] gets the new residual's sums of squares per strip of 16 columns)."""
+    epi = {"none": 0, "silu_mul": 1, "residual": 2}[epilogue]
+    if normed is not None:
+        res, nw, eps, sumsq = normed
+        M, K = res.shape
+        _need(res.dtype == torch.float32 and res.is_contiguous() and nw.dtype == torch.float32 and nw.shape == (K,)
+              and sumsq.dtype == torch.float32 and sumsq.is_contiguous() and sumsq.shape[1] == M, "decode_linear: normed input")
+        pro, xp, ldx, parts = 1, 0, 0, sumsq.shape[0]
+    else:
+        M, K = x.shape
+        _need(x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "decode_linear: x")
+        pro, xp, ldx, parts, res, nw, eps, sumsq = 0, x.data_ptr(), x.stride(0), 0, None, None, 0.0, None
+    _need(decode_linear_takes(M, K, weight) and weight.shape[1] == K and weight.is_contiguous(), "decode_linear: shape not taken")
+    N = weight.shape[0] // 2 if epi == 1 else weight.shape[0]
+    if epi == 2:
+        _need(residual_out.dtype == torch.float32 and residual_out.is_contiguous() and tuple(residual_out.shape) == (M, N)
+              and sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous()
+              and tuple(sumsq_out.shape) == ((N + 15) // 16, M), "decode_linear: residual output")
+        yp, ydt, ldy = 0, 0, 0
+    else:
+        _need(tuple(out.shape) == (M, N) and out.stride(1) == 1, "decode_linear: output shape")
+        yp, ydt, ldy = out.data_ptr(), _dt(out), out.stride(0)
+    _call("me_gemm_decode", pro, epi, xp, ldx, _ptr(res), _ptr(nw), _ptr(sumsq), parts, float(eps), weight.data_ptr(), yp, ydt, ldy,
+          _ptr(residual_out), _ptr(sumsq_out), M, N, K, _stream())
 
 
 TCGEN05_MIN_ROWS = 128    # rows from which bfloat16 products run csrc/gemm_tcgen05.cu (17..127: cuBLAS)

@@ -1,4 +1,4 @@
-from .base import (DiskSource, FeedForward, KVCacheNeed, Mixer, Norm, ParamDecl, Part,
+from .base import (AddedToResidual, PendingNorm, DiskSource, FeedForward, KVCacheNeed, Mixer, Norm, ParamDecl, Part,
                    PositionEncoding, StateNeed)
 from .registry import (PartSpec, build_part, register_feed_forward, register_mixer, register_norm,
                        register_position_encoding, registered)

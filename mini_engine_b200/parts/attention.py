@@ -24,6 +24,10 @@ from .registry import PartSpec, build_part, register_mixer
 
 class GQAAttention(Mixer):
     capturable = True
+    # The last projection adds its result into the residual stream in its own epilogue.  (Folding the norm in
+    # front into the first projection was measured and lost: hundreds of blocks each re-read and convert the
+    # residual; the kernel keeps that ability, the parts do not ask for it.)
+    adds_to_residual = True
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm_eps: Optional[float], position_encoding: Optional[PartSpec | object],
@@ -65,7 +69,7 @@ class GQAAttention(Mixer):
     def cache_needs(self):
         return [KVCacheNeed(self.num_kv_heads, self.head_dim, self.window)]
 
-    def forward(self, x, ctx, call):
+    def forward(self, x, ctx, call, residual=None):
         qkv = self.qkv_proj.forward(x, ctx, "qkv")
         kv = ctx.kv_cache(call.cache_slot)
         has_norm = self.qk_norm_eps is not None
@@ -77,11 +81,11 @@ class GQAAttention(Mixer):
             self.rope.cos_sin if self.rope is not None else None,
             ctx.positions, kv.slot_mapping if call.writes_cache else None,
             kv.pool, kv.page_size)
-        out = ctx.buffer("attn_out", (x.shape[0], self.q_size), ctx.act_dtype)
+        out = ctx.buffer("attn_out", (qkv.shape[0], self.q_size), ctx.act_dtype)
         ops.paged_attention(qkv, out, self.num_heads, self.num_kv_heads, self.head_dim,
                             kv.pool, kv.page_size, kv.block_tables, ctx.attn_meta,
                             self.scale, self.window)
-        return self.o_proj.forward(out, ctx, "mixer_out", may_split=True)
+        return self.o_proj.forward(out, ctx, "mixer_out", may_split=True, residual=residual)
 
 
 register_mixer("gqa_attention", GQAAttention)

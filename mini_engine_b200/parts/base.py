@@ -56,6 +56,31 @@ class StateNeed:
     shape: tuple[int, ...]
 
 
+@dataclass
+class AddedToResidual:
+    """What a part returns instead of its output when its last kernel has already added that output into the
+    float32 residual stream; ``sumsq`` [parts, T] holds the new residual's sums of squares per strip of
+    columns, which the next normalisation needs."""
+    sumsq: "torch.Tensor"
+
+
+@dataclass
+class PendingNorm:
+    """Rows that are ``norm(residual) * weight`` but have not been computed yet.  A consumer that can fold the
+    normalisation into its own kernel (``takes_pending_norm``) uses the pieces; any other gets a tensor from
+    ``materialize``."""
+    residual: "torch.Tensor"
+    weight: "torch.Tensor"
+    eps: float
+    sumsq: "torch.Tensor"
+
+    def materialize(self, ctx) -> "torch.Tensor":
+        from .. import ops
+        out = ctx.buffer("norm_out", tuple(self.residual.shape), ctx.act_dtype)
+        ops.add_rmsnorm(self.residual, None, self.weight, self.eps, out)
+        return out
+
+
 class Part:
     """Base of all parts.  ``params`` is filled by the weight loader.
 
@@ -65,6 +90,10 @@ class Part:
     model with such a part runs every step eagerly."""
 
     capturable = False
+    # A mixer or feed-forward that can fold the normalisation in front of it into its first kernel, and the add
+    # into the residual into its last one, says so; the block then hands it a PendingNorm and the residual.
+    takes_pending_norm = False
+    adds_to_residual = False
 
     def __init__(self):
         self.params: dict[str, torch.Tensor] = {}
@@ -93,20 +122,25 @@ class Mixer(Part):
     """Mixes information between the tokens of a request (attention, or a mixer with state)."""
 
     def forward(self, x: torch.Tensor, ctx: "Any", call: "Any") -> torch.Tensor:
+        """``x`` [T, hidden] in the working dtype -> the mixer's output, same shape (or float32 split-K partial
+        results [S, T, hidden]).  With ``adds_to_residual`` the block also passes ``residual=``, and the mixer may
+        return ``AddedToResidual``; with ``takes_pending_norm`` ``x`` may be a ``PendingNorm``."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: "Any") -> torch.Tensor:
+        """As ``Mixer.forward`` without the cache."""
         raise NotImplementedError
 
 
 class Norm(Part):
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: "Any",
-                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                rows: Optional[torch.Tensor] = None, lazy: bool = False) -> torch.Tensor:
         """``residual += delta`` (if given), then the normalised rows in the working dtype.
 
-        With ``rows`` only those rows are normalised and ``residual`` is left unchanged.
+        With ``rows`` only those rows are normalised and ``residual`` is left unchanged.  ``delta`` may be
+        ``AddedToResidual`` (nothing to add); then, with ``lazy``, a ``PendingNorm`` may be returned.
         """
         raise NotImplementedError
 

@@ -49,10 +49,13 @@ class PreNormBlock(Part):
                 (s.feed_forward_prefix, self.feed_forward)]
 
     def forward(self, residual, delta, ctx, call):
-        x = self.mixer_norm.forward(residual, delta, ctx)
-        mixed = self.mixer.forward(x, ctx, call)
-        x = self.feed_forward_norm.forward(residual, mixed, ctx)
-        return self.feed_forward.forward(x, ctx)
+        """``delta``: the output of the sub-layer before this block, not yet added to ``residual`` (or the mark
+        that it has been).  Returns this block's last output the same way."""
+        mixer, ffn = self.mixer, self.feed_forward
+        x = self.mixer_norm.forward(residual, delta, ctx, lazy=mixer.takes_pending_norm)
+        mixed = mixer.forward(x, ctx, call, residual=residual) if mixer.adds_to_residual else mixer.forward(x, ctx, call)
+        x = self.feed_forward_norm.forward(residual, mixed, ctx, lazy=ffn.takes_pending_norm)
+        return ffn.forward(x, ctx, residual=residual) if ffn.adds_to_residual else ffn.forward(x, ctx)
 
 
 @dataclass(frozen=True)

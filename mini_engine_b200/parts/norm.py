@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import Norm, ParamDecl
+from .base import AddedToResidual, Norm, ParamDecl, PendingNorm
 from .registry import register_norm
 
 
@@ -28,7 +28,11 @@ class RMSNorm(Norm):
     def param_decls(self):
         return [ParamDecl("weight", (self.size,), init="norm", role="vector")]
 
-    def forward(self, residual, delta, ctx, rows: Optional[torch.Tensor] = None):
+    def forward(self, residual, delta, ctx, rows: Optional[torch.Tensor] = None, lazy: bool = False):
+        if isinstance(delta, AddedToResidual):
+            if lazy and rows is None:
+                return PendingNorm(residual, self.p("weight"), self.eps, delta.sumsq)
+            delta = None                          # the residual already holds the sum
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer("norm_out", (n, self.size), ctx.act_dtype)
         ops.add_rmsnorm(residual, delta, self.p("weight"), self.eps, out, rows=rows)

@@ -168,6 +168,48 @@ def test_tcgen05_products(ops, M, N, K, tile_n):
         close(out, ref, torch.bfloat16, scale=4)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("N, K", [(96, 64), (1000, 200), (4096, 1024), (1024, 2048), (1032, 3072)])
+def test_decode_products_with_norm_and_residual_folded_in(ops, M, N, K):
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5)
+    assert ops.decode_linear_takes(M, K, w)
+    ref = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    plain_ops.linear(x, w, ref)
+    # plain input, float32 and bfloat16 output
+    for od in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
+        ops.decode_linear(w, x=x, out=out)
+        close(out, ref, od, scale=4)
+    # residual epilogue: residual += x W^T, and the sums of squares of the new residual per strip of 16 columns
+    res = rnd(M, N, seed=3)
+    want = res + ref
+    parts = (N + 15) // 16
+    sumsq = torch.full((parts, M), float("nan"), device=DEV)
+    ops.decode_linear(w, x=x, epilogue="residual", residual_out=res, sumsq_out=sumsq)
+    close(res, want, torch.float32, scale=50)
+    padded = torch.nn.functional.pad(res, (0, parts * 16 - N))
+    want_sq = padded.view(M, parts, 16).pow(2).sum(-1).t()
+    assert torch.allclose(sumsq, want_sq, rtol=1e-4, atol=1e-5)
+    # norm prologue: X = rmsnorm(residual) * weight from the sums of squares a product before left
+    K_parts = (K + 15) // 16
+    resk = rnd(M, K, seed=4)
+    sq_in = torch.nn.functional.pad(resk, (0, K_parts * 16 - K)).view(M, K_parts, 16).pow(2).sum(-1).t().contiguous()
+    nw = 1 + 0.1 * rnd(K, seed=5)
+    xn = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    plain_ops.add_rmsnorm(resk.clone(), None, nw, 1e-5, xn)
+    refn = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    plain_ops.linear(xn, w, refn)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.decode_linear(w, normed=(resk, nw, 1e-5, sq_in), out=out)
+    close(out, refn, torch.bfloat16, scale=4)
+    if N % 2 == 0:
+        I = N // 2
+        out2, ref2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV), torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+        ops.decode_linear(w, normed=(resk, nw, 1e-5, sq_in), out=out2, epilogue="silu_mul")
+        plain_ops.linear(xn, w, ref2, epilogue="silu_mul")
+        close(out2, ref2, torch.bfloat16, scale=4)
+
+
 def test_linear_rows_do_not_depend_on_the_batch(ops):
     x, w = rnd(70, 96, seed=1), rnd(224, 96, seed=2)
     full, one = torch.empty(70, 224, device=DEV), torch.empty(1, 224, device=DEV)
