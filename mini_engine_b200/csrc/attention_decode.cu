@@ -658,28 +658,36 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     tma::mbar_init(&bar_k, 1);
     tma::mbar_init(&bar_v, 1);
     tma::mbar_fence_init();
+  }
+  if (warp == 0) {
+    // A tensor-map copy is issued per thread, so the lanes of one warp issue the partition's boxes together:
+    // lane i looks up page i, lane 0 announces the bytes, then box x = ((k|v) * HALVES + half) * pages + page
+    // goes out from lane x % 32.
     const int n_pages = DEC_PART / page_size;
     const unsigned box_bytes = (unsigned)page_size * 64 * sizeof(bf16);
-    int first_row[DEC_PART / 8];                       // row of the pool's 2-D view where each page's K starts
-    unsigned bytes = 0;
-    for (int i = 0; i < n_pages; ++i) {
-      const int j0 = part_lo + i * page_size;
+    int first_row = -1;                                // row of the pool's 2-D view where this lane's page keeps K
+    if (lane < n_pages) {
+      const int j0 = part_lo + lane * page_size;
       int page = -1;
       if (j0 < part_hi && j0 + page_size > lo_w) page = bt[j0 / page_size];
-      first_row[i] = page < 0 ? -1 : ((page * 2) * nkv + kvh) * page_size;
-      if (page >= 0) bytes += HALVES * box_bytes;
+      if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size;
     }
-    tma::mbar_expect_tx(&bar_k, bytes);
-    for (int i = 0; i < n_pages; ++i)
-      if (first_row[i] >= 0)
-        for (int h = 0; h < HALVES; ++h)
-          tma::load_2d(ks + h * DEC_PART * 64 + i * page_size * 64, &kv_map, h * 64, first_row[i], &bar_k);
-    tma::mbar_expect_tx(&bar_v, bytes);
+    const unsigned present = __ballot_sync(0xffffffffu, first_row >= 0);
+    if (lane == 0) {
+      const unsigned bytes = (unsigned)__popc(present) * HALVES * box_bytes;
+      tma::mbar_expect_tx(&bar_k, bytes);
+      tma::mbar_expect_tx(&bar_v, bytes);
+    }
+    __syncwarp();
     const int v_rows = nkv * page_size;
-    for (int i = 0; i < n_pages; ++i)
-      if (first_row[i] >= 0)
-        for (int h = 0; h < HALVES; ++h)
-          tma::load_2d(vs + h * DEC_PART * 64 + i * page_size * 64, &kv_map, h * 64, first_row[i] + v_rows, &bar_v);
+    for (int x0 = 0; x0 < 2 * HALVES * n_pages; x0 += 32) {
+      const int x = x0 + lane;
+      const int i = x % n_pages, h = (x / n_pages) % HALVES, v = x / (n_pages * HALVES);
+      const int row = __shfl_sync(0xffffffffu, first_row, i);
+      if (x < 2 * HALVES * n_pages && row >= 0)
+        tma::load_2d((v ? vs : ks) + h * DEC_PART * 64 + i * page_size * 64, &kv_map, h * 64, row + v * v_rows,
+                     v ? &bar_v : &bar_k);
+    }
   }
   if (!has_new) {
     pdl_wait();

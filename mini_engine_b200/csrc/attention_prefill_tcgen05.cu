@@ -102,40 +102,40 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   bool ok = true;
 
   if (warp == 0 || warp == 10) {
-    if (lane == 0) {
-      const bool is_v = warp == 10;
-      if (!is_v) {
-        // Q: head h of the pack, 64-column half c -> block c of the A operand, rows h * tq ...
-        tma::mbar_expect_tx(&q_bar, (unsigned)(gp * HALVES * tq * 128));
-        for (int h = 0; h < gp; ++h)
-          for (int c = 0; c < HALVES; ++c)
-            tma::load_2d(q_s + c * HALF_BYTES + h * tq * 128, &q_map, (head0 + h) * HD + c * 64, tok0 + q0, &q_bar);
-      }
-      // Two threads stream the pages of a key tile: this one K (warp 0) or V (warp 10).
-      const int pages_per_tile = TA_KEYS / page_size;
-      const unsigned box_bytes = (unsigned)page_size * 128;
-      const int row_off = is_v ? nkv * page_size : 0;
-      unsigned char* dst0 = is_v ? v_s : k_s;
-      for (int it = 0; it < n_tiles && ok; ++it) {
-        const int s = it & 1, kt = lo + it * TA_KEYS;
-        ok = tma::mbar_wait(&kv_empty[s], ((it >> 1) & 1) ^ 1);
-        if (!ok) break;
-        int first_row[TA_KEYS / 8];
-        unsigned bytes = 0;
-        for (int i = 0; i < pages_per_tile; ++i) {
-          const int j0 = kt + i * page_size;
-          int page = -1;
-          if (j0 < hi && j0 + page_size > lo_seen) page = bt[j0 / page_size];
-          first_row[i] = page < 0 ? -1 : ((page * 2) * nkv + kvh) * page_size + row_off;
-          if (page >= 0) bytes += HALVES * box_bytes;
-        }
-        tma::mbar_expect_tx(&kv_full[s], bytes);
-        for (int i = 0; i < pages_per_tile; ++i) {
-          if (first_row[i] < 0) continue;
-          for (int c = 0; c < HALVES; ++c)
-            tma::load_2d(dst0 + s * KV_BYTES + c * KB_BYTES + i * page_size * 128, &kv_map, c * 64, first_row[i], &kv_full[s]);
+    // Two warps stream the pages of a key tile: warp 0 K (and Q, once), warp 10 V.  Lane l issues the box of page
+    // l / HALVES, half l % HALVES, so a tile's boxes leave in one warp instruction (a tensor-map copy is a
+    // per-thread instruction).
+    const bool is_v = warp == 10;
+    if (!is_v && lane == 0) {
+      // Q: head h of the pack, 64-column half c -> block c of the A operand, rows h * tq ...
+      tma::mbar_expect_tx(&q_bar, (unsigned)(gp * HALVES * tq * 128));
+      for (int h = 0; h < gp; ++h)
+        for (int c = 0; c < HALVES; ++c)
+          tma::load_2d(q_s + c * HALF_BYTES + h * tq * 128, &q_map, (head0 + h) * HD + c * 64, tok0 + q0, &q_bar);
+    }
+    const int boxes = (TA_KEYS / page_size) * HALVES;              // <= 32 for pages of 8 and more
+    const unsigned box_bytes = (unsigned)page_size * 128;
+    const int row_off = is_v ? nkv * page_size : 0;
+    unsigned char* dst0 = is_v ? v_s : k_s;
+    const int pg = lane / HALVES, hf = lane % HALVES;
+    for (int it = 0; it < n_tiles && ok; ++it) {
+      const int s = it & 1, kt = lo + it * TA_KEYS;
+      ok = tma::mbar_wait(&kv_empty[s], ((it >> 1) & 1) ^ 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      int first_row = -1;
+      if (lane < boxes) {
+        const int j0 = kt + pg * page_size;
+        if (j0 < hi && j0 + page_size > lo_seen) {
+          const int page = bt[j0 / page_size];
+          if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size + row_off;
         }
       }
+      const unsigned n_boxes = __popc(__ballot_sync(0xffffffffu, first_row >= 0));
+      if (lane == 0) tma::mbar_expect_tx(&kv_full[s], n_boxes * box_bytes);
+      __syncwarp();
+      if (first_row >= 0)
+        tma::load_2d(dst0 + s * KV_BYTES + hf * KB_BYTES + pg * page_size * 128, &kv_map, hf * 64, first_row, &kv_full[s]);
     }
   } else if (warp == 1) {
     if (lane == 0) {
