@@ -29,7 +29,7 @@ _PROTOS = {
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
-    "me_gemm_decode": [_I, _I, _P, _L, _P, _P, _P, _I, _F, _P, _P, _I, _L, _P, _P, _I, _I, _I, _P],
+    "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
     "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
@@ -196,38 +196,41 @@ def decode_linear_takes(M: int, K: int, weight: torch.Tensor) -> bool:
             and K <= DECODE_MAX_K and weight.data_ptr() % 16 == 0)
 
 
-def decode_linear(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, normed=None, out: Optional[torch.Tensor] = None,
-                  epilogue: str = "none", residual_out: Optional[torch.Tensor] = None,
-                  sumsq_out: Optional[torch.Tensor] = None) -> None:
-    """One decode product with its neighbours folded in.
+def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.Tensor] = None, epilogue: str = "none",
+                  row_scale=None, residual_out: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None,
+                  next_norm=None) -> None:
+    """One decode product with its neighbours folded in (csrc/gemm_decode.cu).
 
-    Input: ``x`` (bfloat16 [M, K]) or ``normed`` = (residual float32 [M, K], norm weight float32 [K], eps, sums of
-    squares float32 [parts, M]) for X = rmsnorm(residual) * weight.  Output: ``out`` (epilogue "none" or
-    "silu_mul") or ``residual_out`` (float32 [M, N], epilogue "residual": residual_out += X W^T, and
-    ``sumsq_out`` [ceil(N/16), M] gets the new residual's sums of squares per strip of 16 columns)."""
+    ``x``: bfloat16 [M, K].  ``row_scale`` = (sums of squares float32 [parts, M], eps): x is a residual times a
+    norm's weight, and the float32 results of row m are multiplied by rsqrt(sum / K + eps), which completes that
+    RMSNorm.  Output: ``out`` (epilogue "none" or "silu_mul") or ``residual_out`` (float32 [M, N], epilogue
+    "residual": residual_out += x W^T; ``sumsq_out`` [ceil(N/16), M] gets the new residual's sums of squares per
+    strip of 16 columns, and with ``next_norm`` = (weight float32 [N], xw bfloat16 [M, N]) xw gets the new
+    residual times that weight)."""
     epi = {"none": 0, "silu_mul": 1, "residual": 2}[epilogue]
-    if normed is not None:
-        res, nw, eps, sumsq = normed
-        M, K = res.shape
-        _need(res.dtype == torch.float32 and res.is_contiguous() and nw.dtype == torch.float32 and nw.shape == (K,)
-              and sumsq.dtype == torch.float32 and sumsq.is_contiguous() and sumsq.shape[1] == M, "decode_linear: normed input")
-        pro, xp, ldx, parts = 1, 0, 0, sumsq.shape[0]
-    else:
-        M, K = x.shape
-        _need(x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "decode_linear: x")
-        pro, xp, ldx, parts, res, nw, eps, sumsq = 0, x.data_ptr(), x.stride(0), 0, None, None, 0.0, None
+    M, K = x.shape
+    _need(x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "decode_linear: x")
     _need(decode_linear_takes(M, K, weight) and weight.shape[1] == K and weight.is_contiguous(), "decode_linear: shape not taken")
+    sumsq, eps = row_scale if row_scale is not None else (None, 0.0)
+    if sumsq is not None:
+        _need(sumsq.dtype == torch.float32 and sumsq.is_contiguous() and sumsq.dim() == 2 and sumsq.shape[1] == M,
+              "decode_linear: sums of squares")
     N = weight.shape[0] // 2 if epi == 1 else weight.shape[0]
+    nw, xw = next_norm if next_norm is not None else (None, None)
     if epi == 2:
         _need(residual_out.dtype == torch.float32 and residual_out.is_contiguous() and tuple(residual_out.shape) == (M, N)
               and sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous()
               and tuple(sumsq_out.shape) == ((N + 15) // 16, M), "decode_linear: residual output")
+        if nw is not None:
+            _need(nw.dtype == torch.float32 and tuple(nw.shape) == (N,) and nw.is_contiguous() and xw.dtype == torch.bfloat16
+                  and tuple(xw.shape) == (M, N) and xw.is_contiguous(), "decode_linear: pre-weighted output")
         yp, ydt, ldy = 0, 0, 0
     else:
+        _need(next_norm is None, "decode_linear: the pre-weighted output belongs to the residual epilogue")
         _need(tuple(out.shape) == (M, N) and out.stride(1) == 1, "decode_linear: output shape")
         yp, ydt, ldy = out.data_ptr(), _dt(out), out.stride(0)
-    _call("me_gemm_decode", pro, epi, xp, ldx, _ptr(res), _ptr(nw), _ptr(sumsq), parts, float(eps), weight.data_ptr(), yp, ydt, ldy,
-          _ptr(residual_out), _ptr(sumsq_out), M, N, K, _stream())
+    _call("me_gemm_decode", epi, x.data_ptr(), x.stride(0), _ptr(sumsq), sumsq.shape[0] if sumsq is not None else 0, float(eps),
+          weight.data_ptr(), yp, ydt, ldy, _ptr(residual_out), _ptr(sumsq_out), _ptr(nw), _ptr(xw), M, N, K, _stream())
 
 
 TCGEN05_MIN_ROWS = 128    # rows from which bfloat16 products run csrc/gemm_tcgen05.cu (17..127: cuBLAS)

@@ -24,9 +24,9 @@ from .registry import PartSpec, build_part, register_mixer
 
 class GQAAttention(Mixer):
     capturable = True
-    # The last projection adds its result into the residual stream in its own epilogue.  (Folding the norm in
-    # front into the first projection was measured and lost: hundreds of blocks each re-read and convert the
-    # residual; the kernel keeps that ability, the parts do not ask for it.)
+    # In a decode step the q|k|v projection finishes the norm in front of it (the rows' factors applied to its
+    # results) and the output projection adds into the residual stream and starts the next norm, in their epilogues.
+    takes_pending_norm = True
     adds_to_residual = True
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -69,7 +69,7 @@ class GQAAttention(Mixer):
     def cache_needs(self):
         return [KVCacheNeed(self.num_kv_heads, self.head_dim, self.window)]
 
-    def forward(self, x, ctx, call, residual=None):
+    def forward(self, x, ctx, call, residual=None, next_norm=None):
         qkv = self.qkv_proj.forward(x, ctx, "qkv")
         kv = ctx.kv_cache(call.cache_slot)
         has_norm = self.qk_norm_eps is not None
@@ -85,7 +85,7 @@ class GQAAttention(Mixer):
         ops.paged_attention(qkv, out, self.num_heads, self.num_kv_heads, self.head_dim,
                             kv.pool, kv.page_size, kv.block_tables, ctx.attn_meta,
                             self.scale, self.window)
-        return self.o_proj.forward(out, ctx, "mixer_out", may_split=True, residual=residual)
+        return self.o_proj.forward(out, ctx, "mixer_out", may_split=True, residual=residual, next_norm=next_norm)
 
 
 register_mixer("gqa_attention", GQAAttention)

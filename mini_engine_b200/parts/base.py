@@ -60,19 +60,25 @@ class StateNeed:
 class AddedToResidual:
     """What a part returns instead of its output when its last kernel has already added that output into the
     float32 residual stream; ``sumsq`` [parts, T] holds the new residual's sums of squares per strip of
-    columns, which the next normalisation needs."""
+    columns, which the next normalisation needs.  If that kernel was told the next norm's weight it has also
+    written ``preweighted`` = residual * ``weight`` (in the activations' dtype), the half of that norm that needs
+    no statistics."""
     sumsq: "torch.Tensor"
+    preweighted: "Optional[torch.Tensor]" = None
+    weight: "Optional[torch.Tensor]" = None
 
 
 @dataclass
 class PendingNorm:
-    """Rows that are ``norm(residual) * weight`` but have not been computed yet.  A consumer that can fold the
-    normalisation into its own kernel (``takes_pending_norm``) uses the pieces; any other gets a tensor from
-    ``materialize``."""
+    """Rows that are ``norm(residual) * weight`` but have not been computed yet: ``preweighted`` holds
+    residual * weight, and each row still lacks its factor rsqrt(sum of ``sumsq`` / width + eps).  A consumer
+    whose product can apply that factor to its own results (``takes_pending_norm``) uses the pieces; any other
+    gets a tensor from ``materialize``."""
     residual: "torch.Tensor"
     weight: "torch.Tensor"
     eps: float
     sumsq: "torch.Tensor"
+    preweighted: "torch.Tensor"
 
     def materialize(self, ctx) -> "torch.Tensor":
         from .. import ops
@@ -90,8 +96,8 @@ class Part:
     model with such a part runs every step eagerly."""
 
     capturable = False
-    # A mixer or feed-forward that can fold the normalisation in front of it into its first kernel, and the add
-    # into the residual into its last one, says so; the block then hands it a PendingNorm and the residual.
+    # A mixer or feed-forward whose first kernel can finish a PendingNorm, and whose last kernel can add into the
+    # residual (``forward(..., residual=, next_norm=)``), says so; the block then hands it those.
     takes_pending_norm = False
     adds_to_residual = False
 
@@ -135,6 +141,12 @@ class FeedForward(Part):
 
 
 class Norm(Part):
+    def separable_weight(self) -> "Optional[torch.Tensor]":
+        """The weight w, if the norm is ``x * f(row) * w`` with one factor per row taken from the row's sum of
+        squares (RMSNorm): the kernel that writes the residual may then write x * w beside it (``AddedToResidual``)
+        and the product after the norm applies the factor.  None: the norm cannot be split that way."""
+        return None
+
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: "Any",
                 rows: Optional[torch.Tensor] = None, lazy: bool = False) -> torch.Tensor:
         """``residual += delta`` (if given), then the normalised rows in the working dtype.

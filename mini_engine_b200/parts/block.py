@@ -48,14 +48,24 @@ class PreNormBlock(Part):
                 (s.feed_forward_norm_prefix, self.feed_forward_norm),
                 (s.feed_forward_prefix, self.feed_forward)]
 
-    def forward(self, residual, delta, ctx, call):
+    def first_norm(self):
+        """The norm that reads the residual stream first in this block (the block before may prepare for it)."""
+        return self.mixer_norm
+
+    def forward(self, residual, delta, ctx, call, next_norm=None):
         """``delta``: the output of the sub-layer before this block, not yet added to ``residual`` (or the mark
-        that it has been).  Returns this block's last output the same way."""
+        that it has been).  Returns this block's last output the same way.  ``next_norm``: the norm that reads
+        the residual after this block, if the caller knows it."""
         mixer, ffn = self.mixer, self.feed_forward
         x = self.mixer_norm.forward(residual, delta, ctx, lazy=mixer.takes_pending_norm)
-        mixed = mixer.forward(x, ctx, call, residual=residual) if mixer.adds_to_residual else mixer.forward(x, ctx, call)
+        if mixer.adds_to_residual:
+            mixed = mixer.forward(x, ctx, call, residual=residual, next_norm=self.feed_forward_norm)
+        else:
+            mixed = mixer.forward(x, ctx, call)
         x = self.feed_forward_norm.forward(residual, mixed, ctx, lazy=ffn.takes_pending_norm)
-        return ffn.forward(x, ctx, residual=residual) if ffn.adds_to_residual else ffn.forward(x, ctx)
+        if ffn.adds_to_residual:
+            return ffn.forward(x, ctx, residual=residual, next_norm=next_norm)
+        return ffn.forward(x, ctx)
 
 
 @dataclass(frozen=True)

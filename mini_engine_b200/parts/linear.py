@@ -37,37 +37,42 @@ class Linear(Part):
         return self.p(self.name)
 
     def forward(self, x, ctx, out_name: str, *, out_dtype: Optional[torch.dtype] = None,
-                epilogue: str = "none", may_split: bool = False, residual: Optional[torch.Tensor] = None):
+                epilogue: str = "none", may_split: bool = False, residual: Optional[torch.Tensor] = None,
+                next_norm=None):
         """``x W^T``.
 
-        ``x`` is a tensor or a ``PendingNorm`` (the normalisation is then folded into the product's kernel where
-        that kernel takes the shape, else computed first).  With ``residual`` the product may add its result
-        into that float32 tensor itself and return ``AddedToResidual``.  With ``may_split`` the result may come as
-        float32 partial results [splits, T, N] of a split-K product; only a consumer that adds them (the next
-        norm) may ask for that."""
+        ``x`` is a tensor or a ``PendingNorm`` (the product then applies the rows' factors to its results where
+        its kernel takes the shape, else the norm is computed first).  With ``residual`` the product may add its
+        result into that float32 tensor itself and return ``AddedToResidual``; ``next_norm`` is the norm that
+        will read that residual next, whose element-wise half the same kernel then writes.  With ``may_split`` the
+        result may come as float32 partial results [splits, T, N] of a split-K product; only a consumer that adds
+        them (the next norm) may ask for that."""
         pending = x if isinstance(x, PendingNorm) else None
         M = pending.residual.shape[0] if pending is not None else x.shape[0]
         fused = ctx.act_dtype == torch.bfloat16 and ops.decode_linear_takes(M, self.in_features, self.weight)
-        normed = (pending.residual, pending.weight, pending.eps, pending.sumsq) if pending is not None else None
-        if fused and residual is not None and epilogue == "none":
-            sumsq = ctx.buffer(out_name + "_sumsq", ((self.out_features + 15) // 16, M), torch.float32)
-            ops.decode_linear(self.weight, x=None if pending is not None else x, normed=normed, epilogue="residual",
-                              residual_out=residual, sumsq_out=sumsq)
-            return AddedToResidual(sumsq)
-        n_out = self.out_features // 2 if epilogue == "silu_mul" else self.out_features
+        row_scale = None
         if pending is not None:
             if fused:
-                out = ctx.buffer(out_name, (M, n_out), out_dtype or ctx.act_dtype)
-                ops.decode_linear(self.weight, normed=normed, out=out, epilogue=epilogue)
-                return out
-            x = pending.materialize(ctx)
+                x, row_scale = pending.preweighted, (pending.sumsq, pending.eps)
+            else:
+                x = pending.materialize(ctx)
+        fused = fused and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+        assert fused or row_scale is None, "a pre-weighted residual can only go through the kernel that finishes its norm"
+        if fused and residual is not None and epilogue == "none":
+            sumsq = ctx.buffer(out_name + "_sumsq", ((self.out_features + 15) // 16, M), torch.float32)
+            nw = next_norm.separable_weight() if next_norm is not None else None
+            xw = ctx.buffer(out_name + "_preweighted", (M, self.out_features), torch.bfloat16) if nw is not None else None
+            ops.decode_linear(self.weight, x, row_scale=row_scale, epilogue="residual", residual_out=residual,
+                              sumsq_out=sumsq, next_norm=(nw, xw) if nw is not None else None)
+            return AddedToResidual(sumsq, xw, nw)
+        n_out = self.out_features // 2 if epilogue == "silu_mul" else self.out_features
         if may_split and epilogue == "none" and not fused:
             part = ops.linear_partials(x, self.weight, ctx.buffer, out_name + "_partials")
             if part is not None:
                 return part
-        out = ctx.buffer(out_name, (x.shape[0], n_out), out_dtype or ctx.act_dtype)
-        if fused and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
-            ops.decode_linear(self.weight, x=x, out=out, epilogue=epilogue)
+        out = ctx.buffer(out_name, (M, n_out), out_dtype or ctx.act_dtype)
+        if fused:
+            ops.decode_linear(self.weight, x, out=out, epilogue=epilogue, row_scale=row_scale)
             return out
         ops.linear(x, self.weight, out, epilogue=epilogue, workspace=ctx.buffer, err=ctx.error_flag)
         return out

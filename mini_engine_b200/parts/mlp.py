@@ -13,9 +13,9 @@ from .registry import register_feed_forward
 
 class SwiGLU(FeedForward):
     capturable = True
-    # The last projection adds its result into the residual stream in its own epilogue.  (Folding the norm in
-    # front into the first projection was measured and lost: hundreds of blocks each re-read and convert the
-    # residual; the kernel keeps that ability, the parts do not ask for it.)
+    # In a decode step the first projection finishes the norm in front of it (the rows' factors applied to its
+    # results) and the last one adds into the residual stream and starts the next norm, all in their epilogues.
+    takes_pending_norm = True
     adds_to_residual = True
 
     def __init__(self, hidden_size: int, intermediate_size: int):
@@ -31,9 +31,9 @@ class SwiGLU(FeedForward):
     def sub_parts(self):
         return [("", self.gate_up_proj), ("", self.down_proj)]
 
-    def forward(self, x, ctx, residual=None):
+    def forward(self, x, ctx, residual=None, next_norm=None):
         act = self.gate_up_proj.forward(x, ctx, "ffn_act", epilogue="silu_mul")
-        return self.down_proj.forward(act, ctx, "ffn_out", may_split=True, residual=residual)
+        return self.down_proj.forward(act, ctx, "ffn_out", may_split=True, residual=residual, next_norm=next_norm)
 
 
 register_feed_forward("swiglu", SwiGLU)

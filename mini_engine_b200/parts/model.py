@@ -104,8 +104,10 @@ class DecoderModel(Part):
         """Hidden states of the wanted rows, normalised: ``[len(ctx.logits_rows), hidden]``."""
         residual = self.embed.forward(token_ids, ctx)
         delta = None
-        for call in self.schedule:
-            delta = self.blocks[call.block].forward(residual, delta, ctx, call)
+        for i, call in enumerate(self.schedule):
+            # the block learns which norm reads the residual after it, so that its last kernel can prepare for it
+            after = self.blocks[self.schedule[i + 1].block].first_norm() if i + 1 < len(self.schedule) else None
+            delta = self.blocks[call.block].forward(residual, delta, ctx, call, next_norm=after)
         return self.final_norm.forward(residual, delta, ctx, rows=ctx.logits_rows)
 
     def compute_logits(self, hidden: torch.Tensor, ctx) -> torch.Tensor:

@@ -28,10 +28,15 @@ class RMSNorm(Norm):
     def param_decls(self):
         return [ParamDecl("weight", (self.size,), init="norm", role="vector")]
 
+    def separable_weight(self):
+        """y = x * rsqrt(mean(x^2) + eps) * w splits into an element-wise x * w and one factor per row, so the part
+        in front may write x * w itself."""
+        return self.p("weight")
+
     def forward(self, residual, delta, ctx, rows: Optional[torch.Tensor] = None, lazy: bool = False):
         if isinstance(delta, AddedToResidual):
-            if lazy and rows is None:
-                return PendingNorm(residual, self.p("weight"), self.eps, delta.sumsq)
+            if lazy and rows is None and delta.preweighted is not None and delta.weight is self.p("weight"):
+                return PendingNorm(residual, self.p("weight"), self.eps, delta.sumsq, delta.preweighted)
             delta = None                          # the residual already holds the sum
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer("norm_out", (n, self.size), ctx.act_dtype)

@@ -178,34 +178,51 @@ def test_decode_products_with_norm_and_residual_folded_in(ops, M, N, K):
     # plain input, float32 and bfloat16 output
     for od in (torch.bfloat16, torch.float32):
         out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
-        ops.decode_linear(w, x=x, out=out)
+        ops.decode_linear(w, x, out=out)
         close(out, ref, od, scale=4)
-    # residual epilogue: residual += x W^T, and the sums of squares of the new residual per strip of 16 columns
+    # residual epilogue: residual += x W^T, the sums of squares of the new residual per strip of 16 columns, and
+    # the new residual times the next norm's weight
     res = rnd(M, N, seed=3)
     want = res + ref
     parts = (N + 15) // 16
     sumsq = torch.full((parts, M), float("nan"), device=DEV)
-    ops.decode_linear(w, x=x, epilogue="residual", residual_out=res, sumsq_out=sumsq)
+    next_w = 1 + 0.3 * rnd(N, seed=6)
+    xw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.decode_linear(w, x, epilogue="residual", residual_out=res, sumsq_out=sumsq, next_norm=(next_w, xw))
     close(res, want, torch.float32, scale=50)
     padded = torch.nn.functional.pad(res, (0, parts * 16 - N))
     want_sq = padded.view(M, parts, 16).pow(2).sum(-1).t()
     assert torch.allclose(sumsq, want_sq, rtol=1e-4, atol=1e-5)
-    # norm prologue: X = rmsnorm(residual) * weight from the sums of squares a product before left
+    assert torch.equal(xw, (res * next_w).to(torch.bfloat16))
+    res2, sumsq2 = rnd(M, N, seed=3), torch.empty_like(sumsq)
+    ops.decode_linear(w, x, epilogue="residual", residual_out=res2, sumsq_out=sumsq2)        # without a next norm
+    assert torch.equal(res2, res) and torch.equal(sumsq2, sumsq)
+    # the other half of that norm: a product over a pre-weighted residual applies the rows' factors to its results
     K_parts = (K + 15) // 16
-    resk = rnd(M, K, seed=4)
+    resk = rnd(M, K, seed=4, scale=3.0)
     sq_in = torch.nn.functional.pad(resk, (0, K_parts * 16 - K)).view(M, K_parts, 16).pow(2).sum(-1).t().contiguous()
     nw = 1 + 0.1 * rnd(K, seed=5)
+    pre = (resk * nw).to(torch.bfloat16)
     xn = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
     plain_ops.add_rmsnorm(resk.clone(), None, nw, 1e-5, xn)
     refn = torch.empty(M, N, dtype=torch.float32, device=DEV)
     plain_ops.linear(xn, w, refn)
-    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.decode_linear(w, normed=(resk, nw, 1e-5, sq_in), out=out)
-    close(out, refn, torch.bfloat16, scale=4)
+    # (the same arithmetic in float64 for the tight comparison, the plain norm-then-product for the meaning)
+    factor = (resk.double().pow(2).mean(-1, keepdim=True) + 1e-5).rsqrt()
+    sharp = ((pre.double() @ w.double().t()) * factor).float()
+    for od in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
+        ops.decode_linear(w, pre, out=out, row_scale=(sq_in, 1e-5))
+        close(out, sharp, od, scale=4)
+        close(out, refn, torch.bfloat16, scale=4)
+    res3, sumsq3 = rnd(M, N, seed=7), torch.empty_like(sumsq)
+    want3 = res3 + sharp
+    ops.decode_linear(w, pre, epilogue="residual", residual_out=res3, sumsq_out=sumsq3, row_scale=(sq_in, 1e-5))
+    close(res3, want3, torch.float32, scale=50)
     if N % 2 == 0:
         I = N // 2
         out2, ref2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV), torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
-        ops.decode_linear(w, normed=(resk, nw, 1e-5, sq_in), out=out2, epilogue="silu_mul")
+        ops.decode_linear(w, pre, out=out2, epilogue="silu_mul", row_scale=(sq_in, 1e-5))
         plain_ops.linear(xn, w, ref2, epilogue="silu_mul")
         close(out2, ref2, torch.bfloat16, scale=4)
 
