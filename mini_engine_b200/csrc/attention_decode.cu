@@ -608,14 +608,65 @@ static int launch_partition_mma(int num_reqs, int max_parts, cudaStream_t stream
 // so the block has its 64 KB in flight as a few dozen requests instead of four thousand 16-byte copies.
 // Rows of V that are not keys of the request (a page's tail, keys behind the window) are zeroed before
 // P V, because 0 * (whatever the page holds there) must be 0.  Page sizes that divide 128.
+// RMSNorm over one head and the rotary embedding, exactly as csrc/qk_rope_kv.cu does them for a whole step
+// (models/qwen3.py:34-36 and layers/rotary_embedding.py:20-25 in the reference): one warp per head, lane l owns
+// HD/64 consecutive elements of each half.  The lane's norm weights (wa, wb) and its cosines and sines of the
+// token's position were read ahead; ``norm`` / ``rope`` say which of the two steps exist.
 template <int HD>
+__device__ __forceinline__ void norm_rope_head(const bf16* __restrict__ x, bool norm, const float (&wa)[HD / 64],
+                                               const float (&wb)[HD / 64], float eps, bool rope, const float (&c)[HD / 64],
+                                               const float (&sn)[HD / 64], int lane, bf16 (&ra)[HD / 64], bf16 (&rb)[HD / 64]) {
+  constexpr int VEC = HD / 64, half = HD / 2;
+  const int i0 = lane * VEC;
+  float a[VEC], b[VEC], ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) {
+    a[j] = __bfloat162float(x[i0 + j]);
+    b[j] = __bfloat162float(x[half + i0 + j]);
+    ss += a[j] * a[j] + b[j] * b[j];
+  }
+  float inv = 1.f;
+  if (norm) {
+    ss = warp_sum(ss);
+    inv = 1.0f / sqrtf(ss / (float)HD + eps);
+  }
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) {
+    float y1 = a[j], y2 = b[j];
+    if (norm) {
+      y1 = (y1 * inv) * wa[j];
+      y2 = (y2 * inv) * wb[j];
+    }
+    float o1 = y1, o2 = y2;
+    if (rope) {
+      o1 = y1 * c[j] - y2 * sn[j];
+      o2 = y2 * c[j] + y1 * sn[j];
+    }
+    ra[j] = __float2bfloat16_rn(o1);
+    rb[j] = __float2bfloat16_rn(o2);
+  }
+}
+
+// What the kernel needs to prepare q and the newest key and value itself (FUSED): then no kernel runs between
+// the q|k|v product and this one, and no block's loads depend on the kernel before it.
+struct DecodePrep {
+  const float* qw;            // q and k norm weights [HD] (both null: no norm)
+  const float* kw;
+  float eps;
+  const float* cos_sin;       // rotary table [positions][HD] (cos | sin) or null
+  const int* positions;       // [tokens]
+  const int* slot_mapping;    // [tokens] cache slot of the token's key and value; null: another layer wrote them
+  bf16* pool;                 // the cache slot, [page][k|v][kv_head][offset][HD]
+};
+
+template <int HD, bool FUSED>
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ qkv,
                                 int64_t q_row_stride, const int* __restrict__ block_tables, int bt_stride,
                                 const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
                                 int nh, int nkv, int page_size, float scale, int window,
                                 float* __restrict__ tmp_out, float* __restrict__ tmp_m,
-                                float* __restrict__ tmp_l, int max_parts, int* __restrict__ err) {
+                                float* __restrict__ tmp_l, int max_parts, int* __restrict__ err, DecodePrep prep) {
   using namespace mma_prims;
   extern __shared__ unsigned char dec_smem_raw[];
   __shared__ float w_m[4][16], w_l[4][16];
@@ -648,9 +699,13 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   const int* bt = block_tables + (int64_t)b * bt_stride;
   const int64_t tok = cu_seqlens[b];
   // Only the partition that holds the request's newest key depends on the kernel before this one (which
-  // wrote that key); the others fetch their keys and values while that kernel is still running.
+  // wrote that key); the others fetch their keys and values while that kernel is still running.  A block
+  // that makes the newest key and value itself (FUSED) loads the slot's old content and replaces it in
+  // shared memory, so it does not wait either.
   const bool has_new = part_hi == L;
-  if (has_new) {
+  const bool makes_new = FUSED && has_new && prep.slot_mapping != nullptr;
+  const bool wait_first = has_new && !makes_new;
+  if (wait_first) {
     pdl_wait();
     pdl_launch_dependents();
   }
@@ -689,20 +744,94 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
                      v ? &bar_v : &bar_k);
     }
   }
-  if (!has_new) {
+  constexpr int VEC = HD / 64;
+  // what the preparation of q and of the newest key needs besides the rows themselves is no kernel's output:
+  // read it while the kernel before this one is still running
+  float qwa[VEC], qwb[VEC], kwa[VEC], kwb[VEC], rc[VEC], rs[VEC];
+  const bool norm = FUSED && prep.qw != nullptr, rope = FUSED && prep.cos_sin != nullptr;
+  if (FUSED) {
+    const float* cs = rope ? prep.cos_sin + (int64_t)prep.positions[tok] * HD : nullptr;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const int i = lane * VEC + j;
+      qwa[j] = norm ? prep.qw[i] : 1.f;
+      qwb[j] = norm ? prep.qw[HD / 2 + i] : 1.f;
+      kwa[j] = norm ? prep.kw[i] : 1.f;
+      kwb[j] = norm ? prep.kw[HD / 2 + i] : 1.f;
+      rc[j] = rope ? cs[i] : 1.f;
+      rs[j] = rope ? cs[HD / 2 + i] : 0.f;
+    }
+  }
+  if (!wait_first) {
     pdl_wait();
     pdl_launch_dependents();
   }
-  for (int c = tid; c < 16 * PIECES; c += DEC_THREADS) {       // q is written by the kernel before this one
-    const int row = c / PIECES, piece = c % PIECES;
-    const bool ok = row < n_g;
-    cp_async16(tile_ptr<HD>(qs, row, piece),
-               ok ? qkv + tok * q_row_stride + (int64_t)(kvh * G + g0 + row) * HD + piece * 8 : qkv, ok);
+  bf16 new_a[VEC], new_b[VEC];                       // warp 0: the newest key; warp 1: the newest value (makes_new)
+  if (FUSED) {
+    // q as the product before left it: norm and rotation here, one warp per head, into the swizzled tile
+    for (int row = warp; row < 16; row += 4) {
+      bf16 ra[VEC], rb[VEC];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) ra[j] = rb[j] = __float2bfloat16_rn(0.f);
+      if (row < n_g)
+        norm_rope_head<HD>(qkv + tok * q_row_stride + (int64_t)(kvh * G + g0 + row) * HD, norm, qwa, qwb, prep.eps, rope, rc, rs,
+                           lane, ra, rb);
+      const int i0 = lane * VEC;
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        tile_ptr<HD>(qs, row, (i0 + j) >> 3)[(i0 + j) & 7] = ra[j];
+        tile_ptr<HD>(qs, row, (HD / 2 + i0 + j) >> 3)[(HD / 2 + i0 + j) & 7] = rb[j];
+      }
+    }
+    if (makes_new) {
+      if (warp == 0) {
+        norm_rope_head<HD>(qkv + tok * q_row_stride + (int64_t)(nh + kvh) * HD, norm, kwa, kwb, prep.eps, rope, rc, rs, lane,
+                           new_a, new_b);
+      } else if (warp == 1) {
+        const bf16* v = qkv + tok * q_row_stride + (int64_t)(nh + nkv + kvh) * HD;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          new_a[j] = v[lane * VEC + j];
+          new_b[j] = v[HD / 2 + lane * VEC + j];
+        }
+      }
+    }
+  } else {
+    for (int c = tid; c < 16 * PIECES; c += DEC_THREADS) {     // q is written by the kernel before this one
+      const int row = c / PIECES, piece = c % PIECES;
+      const bool ok = row < n_g;
+      cp_async16(tile_ptr<HD>(qs, row, piece),
+                 ok ? qkv + tok * q_row_stride + (int64_t)(kvh * G + g0 + row) * HD + piece * 8 : qkv, ok);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
   }
-  cp_async_commit();
-  cp_async_wait<0>();
   __syncthreads();                                   // barriers initialised, Q in place
   bool landed = tma::mbar_wait(&bar_k, 0);
+  // The newest key and value go to their row of the tiles (over whatever the slot held) and to the cache.
+  auto put_new = [&](bf16* tile, int kv) {
+    const int row = L - 1 - part_lo, i0 = lane * VEC;
+    const int slot = prep.slot_mapping[tok];
+    bf16* dst = nullptr;
+    if (slot >= 0 && g0 == 0) {
+      const int page = slot / page_size, off = slot - page * page_size;
+      dst = prep.pool + ((((int64_t)page * 2 + kv) * nkv + kvh) * page_size + off) * HD;
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const int ia = i0 + j, ib = HD / 2 + i0 + j;
+      tma::swz128(tile + (ia >> 6) * DEC_PART * 64, row, (ia & 63) >> 3)[ia & 7] = new_a[j];
+      tma::swz128(tile + (ib >> 6) * DEC_PART * 64, row, (ib & 63) >> 3)[ib & 7] = new_b[j];
+      if (dst) {
+        dst[ia] = new_a[j];
+        dst[ib] = new_b[j];
+      }
+    }
+  };
+  if (makes_new) {
+    if (warp == 0) put_new(ks, 0);
+    __syncthreads();                                 // the row is in place before any warp reads K
+  }
   const float sl2 = scale * 1.4426950408889634f;
   const int mi = lane >> 3;
   float s[4][4];
@@ -753,6 +882,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   landed = tma::mbar_wait(&bar_v, 0) && landed;
+  if (makes_new && warp == 1) put_new(vs, 1);
   {                                                  // rows of V that are no keys of this request: zero
     const int j = part_lo + tid;                     // 128 threads, 128 rows
     if (j >= part_hi || j < lo_w)
@@ -812,22 +942,23 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   }
 }
 
-template <int HD>
+template <int HD, bool FUSED>
 static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_parts, cudaStream_t stream, const void* qkv,
                                     int64_t q_row_stride, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
-                                    int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int* err) {
+                                    int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int* err,
+                                    const DecodePrep& prep) {
   const size_t smem = (size_t)(16 + 2 * DEC_PART) * HD * sizeof(bf16) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   const int G = nh / nkv;
   dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
-  me_launch(decode_partition_tma_mma_kernel<HD>, grid, dim3(DEC_THREADS), smem, stream,
+  me_launch(decode_partition_tma_mma_kernel<HD, FUSED>, grid, dim3(DEC_THREADS), smem, stream,
       *reinterpret_cast<const CUtensorMap*>(kv_map), (const bf16*)qkv, q_row_stride, bt, bt_stride, cu, cl, nh, nkv, page_size,
-      scale, window, to, tm, tl, max_parts, err);
+      scale, window, to, tm, tl, max_parts, err, prep);
   return 0;
 }
 
@@ -908,10 +1039,11 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   const bool mma = !tma_mma && (kind == 3 || (kind == 0 && mma_ok));
   const bool tma = kind == 2;
   if (tma_mma) {
-    int rc = hd == 64 ? launch_partition_tma_mma<64>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
-                                                     cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err)
-                      : launch_partition_tma_mma<128>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
-                                                      cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err);
+    const DecodePrep none = {};
+    int rc = hd == 64 ? launch_partition_tma_mma<64, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                                                            cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none)
+                      : launch_partition_tma_mma<128, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none);
     if (rc) return rc;
   }
   if (mma) {
@@ -949,5 +1081,45 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   ME_DISPATCH_DTYPE(dtype, T, (me_launch(decode_merge_kernel<T>, mgrid, dim3(mthreads), 0, stream,
       (T*)out, out_row_stride, cu_seqlens, context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts)));
   ME_LAUNCH_CHECK("me_attn_decode (merge)");
+  return 0;
+}
+
+// Whether me_attn_decode_fused takes the shape (bfloat16 only; the tensor map is the caller's to provide).
+ME_API int me_attn_decode_fused_takes(int hd, int page_size) {
+  return (hd == 64 || hd == 128) && page_size >= 8 && DEC_PART % page_size == 0;
+}
+
+// Decode attention straight from the q|k|v product's bfloat16 rows: the per-head norm of q and k, the rotary
+// embedding and the write of the newest key and value to the cache (what me_qk_norm_rope_kv_write does for a
+// whole step) happen inside the partition kernel, for requests [0, num_reqs) that bring one token each
+// (token row = cu_seqlens[request]).  q_weight/k_weight (both or neither), cos_sin and slot_mapping may be
+// null; with a null slot_mapping the newest key and value are expected in the cache already.  The q rows of
+// ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.
+ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out, int64_t out_row_stride, void* pool,
+                                const void* kv_map, const int* block_tables, int bt_stride, const int* cu_seqlens,
+                                const int* context_lens, int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
+                                int window, const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
+                                const int* positions, const int* slot_mapping, float* tmp_out, float* tmp_m, float* tmp_l,
+                                int max_parts, int* err, cudaStream_t stream) {
+  if (num_reqs == 0) return 0;
+  ME_REQUIRE(me_attn_decode_fused_takes(hd, page_size), "me_attn_decode_fused: head_dim %d with pages of %d is not taken", hd, page_size);
+  ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "me_attn_decode_fused: %d heads, %d kv heads", nh, nkv);
+  ME_REQUIRE(max_parts >= 1 && max_parts <= 65535, "me_attn_decode_fused: max_parts %d", max_parts);
+  ME_REQUIRE(kv_map != nullptr && err != nullptr && pool != nullptr && positions != nullptr, "me_attn_decode_fused: missing operand");
+  ME_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "me_attn_decode_fused: q and k norm weights go together");
+  ME_REQUIRE((q_row_stride * 2) % 16 == 0, "me_attn_decode_fused: rows must be 16-byte aligned");
+  const int G = nh / nkv;
+  ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode_fused: too many heads");
+  DecodePrep prep = {q_weight, k_weight, eps, cos_sin, positions, slot_mapping, (bf16*)pool};
+  int rc = hd == 64 ? launch_partition_tma_mma<64, true>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                                                         cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, prep)
+                    : launch_partition_tma_mma<128, true>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                                                          cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, prep);
+  if (rc) return rc;
+  ME_LAUNCH_CHECK("me_attn_decode_fused (partitions)");
+  dim3 mgrid(num_reqs, nh);
+  me_launch(decode_merge_kernel<bf16>, mgrid, dim3(hd >= 128 ? 128 : 64), 0, stream, (bf16*)out, out_row_stride, cu_seqlens,
+            context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts);
+  ME_LAUNCH_CHECK("me_attn_decode_fused (merge)");
   return 0;
 }

@@ -29,6 +29,8 @@ _PROTOS = {
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
+    "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P,
+                             _I, _P, _P],
     "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
     "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
@@ -65,6 +67,7 @@ def require_extension() -> ctypes.CDLL:
     lib.me_attn_prefill_heads_per_block.argtypes = [_I, _I, _I]
     lib.me_attn_prefill_tcgen05_heads_per_block.argtypes = [_I, _I, _I, _I]
     lib.me_sample_chunks.argtypes = [_I]
+    lib.me_attn_decode_fused_takes.argtypes = [_I, _I]
     lib.me_gemm_skinny_splits.argtypes = [_I]
     _lib = lib
     return lib
@@ -466,17 +469,54 @@ def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_siz
     launches += 1          # partition kernel + merge kernel
 
 
+def decode_fused_takes(qkv: torch.Tensor, head_dim: int, pool: torch.Tensor, page_size: int, meta) -> bool:
+    """Whether ``attention_decode_fused`` takes the step: bfloat16, head size 64 or 128, pages of 8 to 128 tokens
+    that divide 128, and a tensor map over the cache."""
+    lib = _lib or require_extension()
+    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and meta.error_flag is not None
+            and bool(lib.me_attn_decode_fused_takes(head_dim, page_size)) and (qkv.stride(0) * 2) % 16 == 0
+            and kv_tensor_map(pool, page_size) is not None)
+
+
+def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window,
+                           q_weight, k_weight, eps, cos_sin, positions, slot_mapping) -> None:
+    """Decode attention over requests [0, meta.num_decodes) straight from the q|k|v product's rows: the kernel
+    applies the q/k norm and the rotary embedding to q and to the newest key itself and writes that key and the
+    newest value into the cache (``slot_mapping``; None if another layer wrote them), so the step needs no
+    ``qk_norm_rope_kv_write`` for these rows.  Arguments as for that function and ``attention_decode``."""
+    D = meta.num_decodes
+    parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
+    tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * parts * head_dim,), torch.float32)
+    tmp_ml = meta.workspace("decode_tmp_ml", (2, D * num_heads * parts), torch.float32)
+    tm = kv_tensor_map(pool, page_size)
+    _need(tm is not None and tuple(pool.shape[1:]) == (2, num_kv_heads, page_size, head_dim) and pool.is_contiguous(),
+          "attention_decode_fused: cache slot")
+    for w in (q_weight, k_weight):
+        _need(w is None or (w.dtype == torch.float32 and tuple(w.shape) == (head_dim,)), "attention_decode_fused: norm weights")
+    _need(cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == head_dim),
+          "attention_decode_fused: the rotary table must be float32 [positions, head_dim]")
+    _need(positions.dtype == torch.int32 and (slot_mapping is None or slot_mapping.dtype == torch.int32),
+          "attention_decode_fused: positions and slots are int32")
+    _call("me_attn_decode_fused", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), pool.data_ptr(), tm.ptr,
+          block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), D,
+          num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), _ptr(q_weight), _ptr(k_weight),
+          float(eps), _ptr(cos_sin), positions.data_ptr(), _ptr(slot_mapping), tmp_out.data_ptr(), tmp_ml[0].data_ptr(),
+          tmp_ml[1].data_ptr(), parts, meta.error_flag.data_ptr(), _stream())
+    global launches
+    launches += 1          # partition kernel + merge kernel
+
+
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                     pool: torch.Tensor, page_size: int, block_tables: torch.Tensor, meta, scale: float,
-                    window: Optional[int]) -> None:
+                    window: Optional[int], decodes: bool = True) -> None:
     """Attention of one step over the paged cache: requests that bring one token go to the decode
-    kernel, portions of prompts to the chunk kernel; both write their rows of ``out``
-    (the split of layers/attention.py:64-76)."""
+    kernel (unless ``decodes`` is False: the caller has run them), portions of prompts to the chunk kernel;
+    both write their rows of ``out`` (the split of layers/attention.py:64-76)."""
     check_attention_sizes(head_dim, num_heads, num_kv_heads)
     _need(qkv.stride(1) == 1 and out.stride(1) == 1 and out.shape[1] == num_heads * head_dim, "paged_attention: shapes")
     _need(pool.dtype == qkv.dtype == out.dtype and pool.is_contiguous(), "paged_attention: dtypes")
     _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "paged_attention: block tables")
-    if meta.num_decodes > 0:
+    if decodes and meta.num_decodes > 0:
         attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window)
     if meta.num_tiles > 0:
         fn = attention_chunks

@@ -72,19 +72,27 @@ class GQAAttention(Mixer):
     def forward(self, x, ctx, call, residual=None, next_norm=None):
         qkv = self.qkv_proj.forward(x, ctx, "qkv")
         kv = ctx.kv_cache(call.cache_slot)
+        meta = ctx.attn_meta
         has_norm = self.qk_norm_eps is not None
-        ops.qk_norm_rope_kv_write(
-            qkv, self.num_heads, self.num_kv_heads, self.head_dim,
-            self.p("q_norm.weight") if has_norm else None,
-            self.p("k_norm.weight") if has_norm else None,
-            self.qk_norm_eps if has_norm else 0.0,
-            self.rope.cos_sin if self.rope is not None else None,
-            ctx.positions, kv.slot_mapping if call.writes_cache else None,
-            kv.pool, kv.page_size)
+        prep = (self.p("q_norm.weight") if has_norm else None, self.p("k_norm.weight") if has_norm else None,
+                self.qk_norm_eps if has_norm else 0.0, self.rope.cos_sin if self.rope is not None else None)
+        slots = kv.slot_mapping if call.writes_cache else None
+        # Requests that bring one token come first in the batch.  Where the decode kernel takes the shape it
+        # prepares q and the newest key and value itself; the other rows get the separate pass.
+        D = meta.num_decodes
+        fused = D > 0 and ops.decode_fused_takes(qkv, self.head_dim, kv.pool, kv.page_size, meta)
+        first = D if fused else 0
+        if first < qkv.shape[0]:
+            ops.qk_norm_rope_kv_write(qkv[first:], self.num_heads, self.num_kv_heads, self.head_dim, *prep,
+                                      ctx.positions[first:], slots[first:] if slots is not None else None,
+                                      kv.pool, kv.page_size)
         out = ctx.buffer("attn_out", (qkv.shape[0], self.q_size), ctx.act_dtype)
+        if fused:
+            ops.attention_decode_fused(qkv, out, self.num_heads, self.num_kv_heads, self.head_dim, kv.pool, kv.page_size,
+                                       kv.block_tables, meta, self.scale, self.window, *prep, ctx.positions, slots)
         ops.paged_attention(qkv, out, self.num_heads, self.num_kv_heads, self.head_dim,
-                            kv.pool, kv.page_size, kv.block_tables, ctx.attn_meta,
-                            self.scale, self.window)
+                            kv.pool, kv.page_size, kv.block_tables, meta,
+                            self.scale, self.window, decodes=not fused)
         return self.o_proj.forward(out, ctx, "mixer_out", may_split=True, residual=residual, next_norm=next_norm)
 
 

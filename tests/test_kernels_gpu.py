@@ -415,6 +415,56 @@ def test_attention_decode_kernels_by_name(ops, kind, nh, nkv, hd, page, window):
     close(out, ref, torch.bfloat16)
 
 
+@pytest.mark.parametrize("nh, nkv, hd, page", [(16, 8, 128, 16), (8, 1, 64, 32), (4, 4, 64, 8), (12, 4, 128, 16),
+                                                  (40, 2, 64, 16), (16, 8, 128, 128)])
+@pytest.mark.parametrize("window", [None, 200])
+@pytest.mark.parametrize("norm, rope, writes", [(True, True, True), (False, True, True), (True, False, True), (True, True, False)])
+def test_attention_decode_that_prepares_q_and_the_newest_key_itself(ops, nh, nkv, hd, page, window, norm, rope, writes):
+    # the same batch through (norm, rotation, cache write) as a pass of its own followed by plain attention, and
+    # through the decode kernel that does all of it; the newest slots of its cache start as NaN
+    ctx = [1, 127, 128, 129, 300, 1000, 16, 255, 256, 257, 513]
+    b = Batch(ctx, [1] * len(ctx), nh, nkv, hd, page, torch.bfloat16, seed=nh + hd, window=window)
+    B = len(ctx)
+    L = b.meta.context_lens.tolist()
+    pos = torch.tensor([n - 1 for n in L], dtype=torch.int32, device=DEV)
+    bt = b.bt.tolist()
+    slots = torch.tensor([bt[r][(L[r] - 1) // page] * page + (L[r] - 1) % page for r in range(B)], dtype=torch.int32, device=DEV)
+    qw = (1 + 0.1 * rnd(hd, seed=2)) if norm else None
+    kw = (1 + 0.1 * rnd(hd, seed=3)) if norm else None
+    inv = 1.0 / (5000.0 ** (torch.arange(0, hd, 2).float() / hd))
+    fr = torch.outer(torch.arange(1100).float(), inv)
+    cs = torch.cat((fr.cos(), fr.sin()), -1).to(DEV) if rope else None
+    ref_qkv, ref_pool = b.qkv.clone(), b.pool.clone()
+    plain_ops.qk_norm_rope_kv_write(ref_qkv, nh, nkv, hd, qw, kw, 1e-5, cs, pos, slots, ref_pool, page)
+    ref = torch.empty(B, nh * hd, dtype=torch.bfloat16, device=DEV)
+    args = (nh, nkv, hd)
+    plain_ops.paged_attention(ref_qkv, ref, *args, ref_pool, page, b.bt, b.meta, hd ** -0.5, window)
+    pool = b.pool.clone()
+    if writes:
+        for r in range(B):
+            s_ = int(slots[r])
+            pool[s_ // page, :, :, s_ % page] = float("nan")
+    else:
+        pool = ref_pool.clone()                      # another layer wrote the newest key and value
+    before = pool.clone()
+    qkv = b.qkv.clone()
+    out = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert ops.decode_fused_takes(qkv, hd, pool, page, b.meta)
+    ops.attention_decode_fused(qkv, out, *args, pool, page, b.bt, b.meta, hd ** -0.5, window, qw, kw, 1e-5, cs, pos,
+                               slots if writes else None)
+    assert not out.isnan().any() and b.meta.error_flag.tolist() == [0, 0, 0, 0]
+    close(out, ref, torch.bfloat16)
+    assert torch.equal(qkv, b.qkv)                   # the rows of the product are left alone
+    if writes:
+        assert torch.equal(pool.isnan(), ref_pool.isnan())
+        close(pool.nan_to_num(0), ref_pool.nan_to_num(0), torch.bfloat16, scale=4)
+        for r in range(B):                           # the value is copied bit for bit
+            s_ = int(slots[r])
+            assert torch.equal(pool[s_ // page, 1, :, s_ % page].reshape(-1), qkv[r, (nh + nkv) * hd:])
+    else:
+        assert torch.equal(pool.nan_to_num(7), before.nan_to_num(7))
+
+
 @pytest.mark.parametrize("dt", ["float32", "bfloat16"])
 @pytest.mark.parametrize("which", ["split", "chunks", "tensor", "tcgen05"])
 def test_attention_finds_one_far_key_among_hundreds(ops, dt, which):
