@@ -653,8 +653,7 @@ struct DecodePrep {
   const float* qw;            // q and k norm weights [HD] (both null: no norm)
   const float* kw;
   float eps;
-  const float* cos_sin;       // rotary table [positions][HD] (cos | sin) or null
-  const int* positions;       // [tokens]
+  const float* cos_sin;       // rotary table [positions][HD] (cos | sin) or null; the token's position is context - 1
   const int* slot_mapping;    // [tokens] cache slot of the token's key and value; null: another layer wrote them
   bf16* pool;                 // the cache slot, [page][k|v][kv_head][offset][HD]
 };
@@ -750,7 +749,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   float qwa[VEC], qwb[VEC], kwa[VEC], kwb[VEC], rc[VEC], rs[VEC];
   const bool norm = FUSED && prep.qw != nullptr, rope = FUSED && prep.cos_sin != nullptr;
   if (FUSED) {
-    const float* cs = rope ? prep.cos_sin + (int64_t)prep.positions[tok] * HD : nullptr;
+    const float* cs = rope ? prep.cos_sin + (int64_t)(L - 1) * HD : nullptr;
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       const int i = lane * VEC + j;
@@ -1092,25 +1091,25 @@ ME_API int me_attn_decode_fused_takes(int hd, int page_size) {
 // Decode attention straight from the q|k|v product's bfloat16 rows: the per-head norm of q and k, the rotary
 // embedding and the write of the newest key and value to the cache (what me_qk_norm_rope_kv_write does for a
 // whole step) happen inside the partition kernel, for requests [0, num_reqs) that bring one token each
-// (token row = cu_seqlens[request]).  q_weight/k_weight (both or neither), cos_sin and slot_mapping may be
+// (token row = cu_seqlens[request], position = context_lens[request] - 1).  q_weight/k_weight (both or neither), cos_sin and slot_mapping may be
 // null; with a null slot_mapping the newest key and value are expected in the cache already.  The q rows of
 // ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.
 ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out, int64_t out_row_stride, void* pool,
                                 const void* kv_map, const int* block_tables, int bt_stride, const int* cu_seqlens,
                                 const int* context_lens, int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
                                 int window, const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
-                                const int* positions, const int* slot_mapping, float* tmp_out, float* tmp_m, float* tmp_l,
-                                int max_parts, int* err, cudaStream_t stream) {
+                                const int* slot_mapping, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts, int* err,
+                                cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   ME_REQUIRE(me_attn_decode_fused_takes(hd, page_size), "me_attn_decode_fused: head_dim %d with pages of %d is not taken", hd, page_size);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "me_attn_decode_fused: %d heads, %d kv heads", nh, nkv);
   ME_REQUIRE(max_parts >= 1 && max_parts <= 65535, "me_attn_decode_fused: max_parts %d", max_parts);
-  ME_REQUIRE(kv_map != nullptr && err != nullptr && pool != nullptr && positions != nullptr, "me_attn_decode_fused: missing operand");
+  ME_REQUIRE(kv_map != nullptr && err != nullptr && pool != nullptr, "me_attn_decode_fused: missing operand");
   ME_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "me_attn_decode_fused: q and k norm weights go together");
   ME_REQUIRE((q_row_stride * 2) % 16 == 0, "me_attn_decode_fused: rows must be 16-byte aligned");
   const int G = nh / nkv;
   ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode_fused: too many heads");
-  DecodePrep prep = {q_weight, k_weight, eps, cos_sin, positions, slot_mapping, (bf16*)pool};
+  DecodePrep prep = {q_weight, k_weight, eps, cos_sin, slot_mapping, (bf16*)pool};
   int rc = hd == 64 ? launch_partition_tma_mma<64, true>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                          cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, prep)
                     : launch_partition_tma_mma<128, true>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,

@@ -12,9 +12,10 @@
 //   epilogue SILU:  rows gate | up, writes silu(gate) * up (layers/activation.py:4-7).
 //
 // As in gemm_skinny.cu the weight rows fill the M side of mma.sync m16n8k16 and a block owns a strip of
-// 16 weight rows; but here the block covers ALL of K with one warp per 256 elements (up to 12 warps), so
-// every output element is finished inside one block and can be added to the residual by exactly one
-// thread.  Weights are requested (cp.async) before griddepcontrol.wait, activations after.
+// 16 weight rows (8 where 16 would leave most SMs without a block); but here the block covers ALL of K with
+// one warp per 256 elements (up to 12 warps), so every output element is finished inside one block and can
+// be added to the residual by exactly one thread.  Weights are requested (cp.async) before
+// griddepcontrol.wait, activations and the residual's old values after.
 #include "common.cuh"
 #include "mma_prims.cuh"
 
@@ -31,7 +32,7 @@ __device__ __forceinline__ bf16* dl_ptr(bf16* base, int row, int piece) {
 // from, over ``K`` columns) the results are multiplied by rsqrt(sum / K + eps) of their row.
 // EPI 0: Y[m][n] (bfloat16 or float32).  EPI 1: SiLU(gate) * up, bfloat16.
 // EPI 2: residual_out[m][n] += v, sumsq_out, and with ``next_w`` also xw_out[m][n] = residual_out[m][n] * next_w[n].
-template <int EPI, typename TO>
+template <int EPI, typename TO, int R /* weight rows of a strip: 16, or 8 with the upper half of the tile idle */>
 __global__ void __launch_bounds__(DL_MAX_WARPS * 32)
 gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restrict__ sumsq_in, int sumsq_parts, float eps,
                    const bf16* __restrict__ W, TO* __restrict__ Y, int64_t ldy, float* __restrict__ res_out,
@@ -50,13 +51,13 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
   const int k0 = warp * DL_KW;
   auto w_row = [&](int r) -> int64_t {
     if (EPI == 1) return r < 8 ? (int64_t)strip * 8 + r : (int64_t)N + strip * 8 + (r - 8);
-    return (int64_t)strip * 16 + r;
+    return (int64_t)strip * R + r;
   };
   const int n_rows = EPI == 1 ? 2 * N : N;
   // piece index of this lane is the same for all rows it copies: c = lane + 32 i -> row i, piece lane
   const int k = k0 + lane * 8;
 #pragma unroll
-  for (int row = 0; row < 16; ++row) {
+  for (int row = 0; row < R; ++row) {
     const int64_t wr = w_row(row);
     const bool okw = k < K && wr < n_rows && (EPI != 1 || strip * 8 + (row & 7) < N);
     cp_async16(dl_ptr(ws, row, lane), okw ? W + wr * K + k : W, okw);
@@ -70,6 +71,15 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
     cp_async16(dl_ptr(xs, row, lane), okx ? X + (int64_t)row * ldx + k : X, okx);
   }
   cp_async_commit();
+  constexpr int EPI_ITERS = 16 * R / 32;     // a block of one warp walks the strip's 16 x R results in so many rounds
+  float old[EPI_ITERS];                      // EPI 2: the residual's values this thread will add to
+  if (EPI == 2) {
+#pragma unroll
+    for (int i = 0; i < EPI_ITERS; ++i) {
+      const int idx = tid + i * (int)blockDim.x, m = idx / R, n = strip * R + idx % R;
+      old[i] = (idx < 16 * R && m < M && n < N) ? res_out[(int64_t)m * N + n] : 0.f;
+    }
+  }
   // while the rows arrive: warp w computes the factors of rows w, w + nwarps, ...; they are read after the
   // block-wide barrier in front of the epilogue
   for (int m = warp; m < 16; m += nwarps) {
@@ -97,8 +107,10 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
   for (int nt = 0; nt < 2; ++nt) {
     red[warp][g][nt * 8 + 2 * t4] = c[nt][0];
     red[warp][g][nt * 8 + 2 * t4 + 1] = c[nt][1];
-    red[warp][g + 8][nt * 8 + 2 * t4] = c[nt][2];
-    red[warp][g + 8][nt * 8 + 2 * t4 + 1] = c[nt][3];
+    if (R == 16) {
+      red[warp][g + 8][nt * 8 + 2 * t4] = c[nt][2];
+      red[warp][g + 8][nt * 8 + 2 * t4 + 1] = c[nt][3];
+    }
   }
   __syncthreads();
   auto total = [&](int r, int m) {
@@ -115,44 +127,46 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
       Y[(int64_t)m * ldy + n] = from_f<TO>(gate / (1.0f + expf(-gate)) * up);
     }
   } else if (EPI == 2) {
-    // 16 consecutive threads hold the 16 columns of one row: add into the residual, then the row's sum of squares
-    for (int idx = tid; idx < 256; idx += blockDim.x) {     // whole warps: 16 lanes per row stay together
-      const int m = idx >> 4, r = idx & 15;
-      const int n = strip * 16 + r;
+    // R consecutive threads hold the R columns of one row: add into the residual, then the row's sum of squares
+#pragma unroll
+    for (int i = 0; i < EPI_ITERS; ++i) {            // whole warps: the R lanes of a row stay together
+      const int idx = tid + i * (int)blockDim.x;
+      if (idx - lane >= 16 * R) break;
+      const int m = idx / R, r = idx % R;
+      const int n = strip * R + r;
       float sq = 0.f;
       if (m < M && n < N) {
-        float* p = res_out + (int64_t)m * N + n;
-        const float v = *p + total(r, m) * row_scale[m];
-        *p = v;
+        const float v = old[i] + total(r, m) * row_scale[m];
+        res_out[(int64_t)m * N + n] = v;
         sq = v * v;
         if (xw_out != nullptr) xw_out[(int64_t)m * N + n] = __float2bfloat16(v * next_w[n]);
       }
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      for (int o = R / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
       if (r == 0 && m < M) sumsq_out[(int64_t)strip * M + m] = sq;
     }
   } else {
-    for (int idx = tid; idx < 16 * 16; idx += blockDim.x) {
-      const int m = idx >> 4, r = idx & 15;
-      const int n = strip * 16 + r;
+    for (int idx = tid; idx < 16 * R; idx += blockDim.x) {
+      const int m = idx / R, r = idx % R;
+      const int n = strip * R + r;
       if (m >= M || n >= N) continue;
       Y[(int64_t)m * ldy + n] = from_f<TO>(total(r, m) * row_scale[m]);
     }
   }
 }
 
-template <int EPI, typename TO>
+template <int EPI, typename TO, int R>
 int launch_dl(int strips, int warps, cudaStream_t stream, const void* X, int64_t ldx, const float* sumsq_in, int sumsq_parts,
               float eps, const void* W, void* Y, int64_t ldy, float* res_out, float* sumsq_out, const float* next_w,
               void* xw_out, int M, int N, int K) {
   const size_t smem = (size_t)warps * (2 * 16 * DL_KW * sizeof(bf16) + 16 * 17 * sizeof(float));
   static size_t attr = 0;
   if (smem > attr) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<EPI, TO, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_gemm_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr = smem;
   }
-  me_launch(gemm_decode_kernel<EPI, TO>, dim3(strips), dim3(warps * 32), smem, stream, (const bf16*)X, ldx, sumsq_in,
+  me_launch(gemm_decode_kernel<EPI, TO, R>, dim3(strips), dim3(warps * 32), smem, stream, (const bf16*)X, ldx, sumsq_in,
             sumsq_parts, eps, (const bf16*)W, (TO*)Y, ldy, res_out, sumsq_out, next_w, (bf16*)xw_out, M, N, K);
   return 0;
 }
@@ -160,8 +174,11 @@ int launch_dl(int strips, int warps, cudaStream_t stream, const void* X, int64_t
 
 // Largest K the kernel covers inside one block.
 ME_API int me_gemm_decode_max_k() { return DL_MAX_WARPS * DL_KW; }
+// Weight rows of a strip for N output columns: 16, or 8 where strips of 16 would occupy fewer than about two
+// thirds of the SMs (a block streams its weight rows alone; more blocks pull more bandwidth).
+static int strip_rows(int N) { return (N + 15) / 16 < 96 ? 8 : 16; }
 // Parts of the sums of squares that the residual epilogue writes for N output columns.
-ME_API int me_gemm_decode_sumsq_parts(int N) { return (N + 15) / 16; }
+ME_API int me_gemm_decode_sumsq_parts(int N) { const int r = strip_rows(N); return (N + r - 1) / r; }
 
 // X bfloat16 [M][ldx].  sumsq_in (or null) [sumsq_parts][M] with eps: the results of row m are multiplied by
 // rsqrt(sum_p sumsq_in[p][m] / K + eps).
@@ -181,20 +198,21 @@ ME_API int me_gemm_decode(int epi, const void* X, int64_t ldx, const float* sums
   ME_REQUIRE((next_w == nullptr) == (xw_out == nullptr) && (next_w == nullptr || epi == 2),
              "me_gemm_decode: the pre-weighted copy needs the residual epilogue, a weight and an output");
   const int warps = (K + DL_KW - 1) / DL_KW;
-  const int strips = epi == 1 ? (N + 7) / 8 : (N + 15) / 16;
+  const int rows = epi == 1 ? 16 : strip_rows(N);
+  const int strips = epi == 1 ? (N + 7) / 8 : (N + rows - 1) / rows;
   int rc = 1;
-#define ME_DL(EPI_, TO_)                                                                                            \
-  rc = launch_dl<EPI_, TO_>(strips, warps, stream, X, ldx, sumsq_in, sumsq_parts, eps, W, Y, ldy, res_out, sumsq_out, next_w, \
-                            xw_out, M, N, K)
+#define ME_DL(EPI_, TO_, R_)                                                                                        \
+  rc = launch_dl<EPI_, TO_, R_>(strips, warps, stream, X, ldx, sumsq_in, sumsq_parts, eps, W, Y, ldy, res_out, sumsq_out, \
+                                next_w, xw_out, M, N, K)
   if (epi == 2) {
-    ME_DL(2, float);
+    if (rows == 8) ME_DL(2, float, 8); else ME_DL(2, float, 16);
   } else if (epi == 1) {
     ME_REQUIRE(y_dtype == ME_BF16, "me_gemm_decode: the SiLU epilogue writes bfloat16");
-    ME_DL(1, bf16);
+    ME_DL(1, bf16, 16);
   } else if (y_dtype == ME_BF16) {
-    ME_DL(0, bf16);
+    if (rows == 8) ME_DL(0, bf16, 8); else ME_DL(0, bf16, 16);
   } else {
-    ME_DL(0, float);
+    if (rows == 8) ME_DL(0, float, 8); else ME_DL(0, float, 16);
   }
 #undef ME_DL
   if (rc) return rc;

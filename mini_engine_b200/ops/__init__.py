@@ -29,7 +29,7 @@ _PROTOS = {
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
-    "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P,
+    "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P,
                              _I, _P, _P],
     "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
@@ -67,6 +67,7 @@ def require_extension() -> ctypes.CDLL:
     lib.me_attn_prefill_heads_per_block.argtypes = [_I, _I, _I]
     lib.me_attn_prefill_tcgen05_heads_per_block.argtypes = [_I, _I, _I, _I]
     lib.me_sample_chunks.argtypes = [_I]
+    lib.me_gemm_decode_sumsq_parts.argtypes = [_I]
     lib.me_attn_decode_fused_takes.argtypes = [_I, _I]
     lib.me_gemm_skinny_splits.argtypes = [_I]
     _lib = lib
@@ -199,6 +200,11 @@ def decode_linear_takes(M: int, K: int, weight: torch.Tensor) -> bool:
             and K <= DECODE_MAX_K and weight.data_ptr() % 16 == 0)
 
 
+def decode_linear_sumsq_parts(N: int) -> int:
+    """Strips of columns for which the residual epilogue of ``decode_linear`` writes sums of squares."""
+    return (_lib or require_extension()).me_gemm_decode_sumsq_parts(N)
+
+
 def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.Tensor] = None, epilogue: str = "none",
                   row_scale=None, residual_out: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None,
                   next_norm=None) -> None:
@@ -207,8 +213,8 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
     ``x``: bfloat16 [M, K].  ``row_scale`` = (sums of squares float32 [parts, M], eps): x is a residual times a
     norm's weight, and the float32 results of row m are multiplied by rsqrt(sum / K + eps), which completes that
     RMSNorm.  Output: ``out`` (epilogue "none" or "silu_mul") or ``residual_out`` (float32 [M, N], epilogue
-    "residual": residual_out += x W^T; ``sumsq_out`` [ceil(N/16), M] gets the new residual's sums of squares per
-    strip of 16 columns, and with ``next_norm`` = (weight float32 [N], xw bfloat16 [M, N]) xw gets the new
+    "residual": residual_out += x W^T; ``sumsq_out`` [decode_linear_sumsq_parts(N), M] gets the new residual's sums
+    of squares per strip of columns, and with ``next_norm`` = (weight float32 [N], xw bfloat16 [M, N]) xw gets the new
     residual times that weight)."""
     epi = {"none": 0, "silu_mul": 1, "residual": 2}[epilogue]
     M, K = x.shape
@@ -223,7 +229,7 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
     if epi == 2:
         _need(residual_out.dtype == torch.float32 and residual_out.is_contiguous() and tuple(residual_out.shape) == (M, N)
               and sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous()
-              and tuple(sumsq_out.shape) == ((N + 15) // 16, M), "decode_linear: residual output")
+              and tuple(sumsq_out.shape) == (decode_linear_sumsq_parts(N), M), "decode_linear: residual output")
         if nw is not None:
             _need(nw.dtype == torch.float32 and tuple(nw.shape) == (N,) and nw.is_contiguous() and xw.dtype == torch.bfloat16
                   and tuple(xw.shape) == (M, N) and xw.is_contiguous(), "decode_linear: pre-weighted output")
@@ -479,11 +485,12 @@ def decode_fused_takes(qkv: torch.Tensor, head_dim: int, pool: torch.Tensor, pag
 
 
 def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window,
-                           q_weight, k_weight, eps, cos_sin, positions, slot_mapping) -> None:
+                           q_weight, k_weight, eps, cos_sin, slot_mapping) -> None:
     """Decode attention over requests [0, meta.num_decodes) straight from the q|k|v product's rows: the kernel
     applies the q/k norm and the rotary embedding to q and to the newest key itself and writes that key and the
     newest value into the cache (``slot_mapping``; None if another layer wrote them), so the step needs no
-    ``qk_norm_rope_kv_write`` for these rows.  Arguments as for that function and ``attention_decode``."""
+    ``qk_norm_rope_kv_write`` for these rows.  The token's position is its request's context length minus one.
+    Other arguments as for that function and ``attention_decode``."""
     D = meta.num_decodes
     parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
     tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * parts * head_dim,), torch.float32)
@@ -495,12 +502,11 @@ def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, pa
         _need(w is None or (w.dtype == torch.float32 and tuple(w.shape) == (head_dim,)), "attention_decode_fused: norm weights")
     _need(cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == head_dim),
           "attention_decode_fused: the rotary table must be float32 [positions, head_dim]")
-    _need(positions.dtype == torch.int32 and (slot_mapping is None or slot_mapping.dtype == torch.int32),
-          "attention_decode_fused: positions and slots are int32")
+    _need(slot_mapping is None or slot_mapping.dtype == torch.int32, "attention_decode_fused: slots are int32")
     _call("me_attn_decode_fused", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), pool.data_ptr(), tm.ptr,
           block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), D,
           num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), _ptr(q_weight), _ptr(k_weight),
-          float(eps), _ptr(cos_sin), positions.data_ptr(), _ptr(slot_mapping), tmp_out.data_ptr(), tmp_ml[0].data_ptr(),
+          float(eps), _ptr(cos_sin), _ptr(slot_mapping), tmp_out.data_ptr(), tmp_ml[0].data_ptr(),
           tmp_ml[1].data_ptr(), parts, meta.error_flag.data_ptr(), _stream())
     global launches
     launches += 1          # partition kernel + merge kernel

@@ -89,7 +89,7 @@ class GQAAttention(Mixer):
         out = ctx.buffer("attn_out", (qkv.shape[0], self.q_size), ctx.act_dtype)
         if fused:
             ops.attention_decode_fused(qkv, out, self.num_heads, self.num_kv_heads, self.head_dim, kv.pool, kv.page_size,
-                                       kv.block_tables, meta, self.scale, self.window, *prep, ctx.positions, slots)
+                                       kv.block_tables, meta, self.scale, self.window, *prep, slots)
         ops.paged_attention(qkv, out, self.num_heads, self.num_kv_heads, self.head_dim,
                             kv.pool, kv.page_size, kv.block_tables, meta,
                             self.scale, self.window, decodes=not fused)

@@ -59,7 +59,7 @@ class Linear(Part):
         fused = fused and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
         assert fused or row_scale is None, "a pre-weighted residual can only go through the kernel that finishes its norm"
         if fused and residual is not None and epilogue == "none":
-            sumsq = ctx.buffer(out_name + "_sumsq", ((self.out_features + 15) // 16, M), torch.float32)
+            sumsq = ctx.buffer(out_name + "_sumsq", (ops.decode_linear_sumsq_parts(self.out_features), M), torch.float32)
             nw = next_norm.separable_weight() if next_norm is not None else None
             xw = ctx.buffer(out_name + "_preweighted", (M, self.out_features), torch.bfloat16) if nw is not None else None
             ops.decode_linear(self.weight, x, row_scale=row_scale, epilogue="residual", residual_out=residual,

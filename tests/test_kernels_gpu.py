@@ -184,14 +184,16 @@ def test_decode_products_with_norm_and_residual_folded_in(ops, M, N, K):
     # the new residual times the next norm's weight
     res = rnd(M, N, seed=3)
     want = res + ref
-    parts = (N + 15) // 16
+    parts = ops.decode_linear_sumsq_parts(N)
+    width = 16 if parts == (N + 15) // 16 else 8             # narrow strips where 16 columns would make few blocks
+    assert parts == (N + width - 1) // width
     sumsq = torch.full((parts, M), float("nan"), device=DEV)
     next_w = 1 + 0.3 * rnd(N, seed=6)
     xw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
     ops.decode_linear(w, x, epilogue="residual", residual_out=res, sumsq_out=sumsq, next_norm=(next_w, xw))
     close(res, want, torch.float32, scale=50)
-    padded = torch.nn.functional.pad(res, (0, parts * 16 - N))
-    want_sq = padded.view(M, parts, 16).pow(2).sum(-1).t()
+    padded = torch.nn.functional.pad(res, (0, parts * width - N))
+    want_sq = padded.view(M, parts, width).pow(2).sum(-1).t()
     assert torch.allclose(sumsq, want_sq, rtol=1e-4, atol=1e-5)
     assert torch.equal(xw, (res * next_w).to(torch.bfloat16))
     res2, sumsq2 = rnd(M, N, seed=3), torch.empty_like(sumsq)
@@ -450,7 +452,7 @@ def test_attention_decode_that_prepares_q_and_the_newest_key_itself(ops, nh, nkv
     qkv = b.qkv.clone()
     out = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
     assert ops.decode_fused_takes(qkv, hd, pool, page, b.meta)
-    ops.attention_decode_fused(qkv, out, *args, pool, page, b.bt, b.meta, hd ** -0.5, window, qw, kw, 1e-5, cs, pos,
+    ops.attention_decode_fused(qkv, out, *args, pool, page, b.bt, b.meta, hd ** -0.5, window, qw, kw, 1e-5, cs,
                                slots if writes else None)
     assert not out.isnan().any() and b.meta.error_flag.tolist() == [0, 0, 0, 0]
     close(out, ref, torch.bfloat16)
