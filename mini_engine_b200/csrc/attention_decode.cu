@@ -961,33 +961,70 @@ static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_pa
   return 0;
 }
 
+// One block per (request, head) adds the partitions' results.  Loads that do not depend on one another are
+// issued together (a partition per thread for the maxima and sums, eight partitions at a time for the
+// outputs): a loop of dependent loads would pay the L2 latency once per partition.
 template <typename T>
 __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
                                     const int* __restrict__ cu_seqlens,
                                     const int* __restrict__ context_lens,
                                     const float* __restrict__ tmp_out, const float* __restrict__ tmp_m,
                                     const float* __restrict__ tmp_l, int nh, int hd, int max_parts) {
+  constexpr int CHUNK = 128;                         // partitions whose factors are held in shared memory at a time
+  __shared__ float f_s[CHUNK], red[32];
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int L = context_lens[b];                     // written by the host, not by a kernel of this step
+  const int64_t tok = cu_seqlens[b];
   pdl_wait();
   pdl_launch_dependents();
-  const int b = blockIdx.x, h = blockIdx.y;
-  const int L = context_lens[b];
   const int P = max(1, min(max_parts, (L + DEC_PART - 1) / DEC_PART));
   const int64_t row0 = ((int64_t)b * nh + h) * max_parts;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = (blockDim.x + 31) >> 5;
+  // the largest maximum: a partition per thread, then lanes, then warps
+  float mx = -INFINITY;
+  for (int p = tid; p < P; p += blockDim.x) mx = fmaxf(mx, tmp_m[row0 + p]);
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
   float M = -INFINITY;
-  for (int p = 0; p < P; ++p) M = fmaxf(M, tmp_m[row0 + p]);
-  T* o = out + (int64_t)cu_seqlens[b] * out_row_stride + (int64_t)h * hd;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float lt = 0.f, acc = 0.f;
-    if (M > -INFINITY) {
-      for (int p = 0; p < P; ++p) {
-        const float mp = tmp_m[row0 + p];
-        if (mp == -INFINITY) continue;
-        const float f = expf(mp - M);
-        lt += f * tmp_l[row0 + p];
-        acc += f * tmp_out[(row0 + p) * hd + d];
+  for (int w = 0; w < nwarps; ++w) M = fmaxf(M, red[w]);
+  float lt = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};      // thread t owns columns t, t + blockDim, ... (hd <= 4 blockDim)
+  for (int p0 = 0; p0 < P && M > -INFINITY; p0 += CHUNK) {
+    const int n = min(CHUNK, P - p0);
+    __syncthreads();
+    for (int p = tid; p < n; p += blockDim.x) {
+      const float mp = tmp_m[row0 + p0 + p];
+      f_s[p] = mp == -INFINITY ? 0.f : expf(mp - M);
+    }
+    __syncthreads();
+    for (int q0 = 0; q0 < n; q0 += 8) {
+      float lv[8], ov[4][8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool ok = q0 + i < n && f_s[q0 + i] != 0.f;
+        lv[i] = ok ? tmp_l[row0 + p0 + q0 + i] : 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int d = tid + c * (int)blockDim.x;
+          ov[c][i] = ok && d < hd ? tmp_out[(row0 + p0 + q0 + i) * hd + d] : 0.f;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {                  // partitions in index order
+        const float f = q0 + i < n ? f_s[q0 + i] : 0.f;
+        if (f != 0.f) {
+          lt += f * lv[i];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[c] += f * ov[c][i];
+        }
       }
     }
-    o[d] = from_f<T>(lt > 0.f ? acc / lt : 0.f);
+  }
+  T* o = out + tok * out_row_stride + (int64_t)h * hd;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int d = tid + c * (int)blockDim.x;
+    if (d < hd) o[d] = from_f<T>(lt > 0.f ? acc[c] / lt : 0.f);
   }
 }
 

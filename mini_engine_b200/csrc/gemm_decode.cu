@@ -37,8 +37,19 @@ __global__ void __launch_bounds__(DL_MAX_WARPS * 32)
 gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restrict__ sumsq_in, int sumsq_parts, float eps,
                    const bf16* __restrict__ W, TO* __restrict__ Y, int64_t ldy, float* __restrict__ res_out,
                    float* __restrict__ sumsq_out, const float* __restrict__ next_w, bf16* __restrict__ xw_out, int M,
-                   int N, int K) {
+                   int N, int K, const unsigned char* __restrict__ ahead, unsigned long long ahead_bytes) {
   extern __shared__ __align__(128) unsigned char dl_smem[];
+  // The weights of the product that runs after this one are asked into L2 now: a decode step is a chain of
+  // short dependent kernels, and without this the memory system idles while each waits for the one before.
+  if (ahead != nullptr && threadIdx.x < 32) {
+    const unsigned long long per = ((ahead_bytes + gridDim.x - 1) / gridDim.x + 15) & ~15ull;
+    const unsigned long long lo = blockIdx.x * per, hi = lo + per < ahead_bytes ? lo + per : ahead_bytes;
+    constexpr unsigned long long PIECE = 16384;
+    for (unsigned long long o = lo + threadIdx.x * PIECE; o < hi; o += 32 * PIECE) {
+      const unsigned n = (unsigned)((hi - o < PIECE ? hi - o : PIECE) & ~15ull);
+      if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ahead + o), "r"(n) : "memory");
+    }
+  }
   __shared__ float row_scale[16];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int g = lane >> 2, t4 = lane & 3;
@@ -63,16 +74,37 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
     cp_async16(dl_ptr(ws, row, lane), okw ? W + wr * K + k : W, okw);
   }
   cp_async_commit();
+  // rows of X beyond M are zero: written here, so that after the wait only real rows are asked for
+#pragma unroll
+  for (int row = 0; row < 16; ++row)
+    if (row >= M || k >= K) *reinterpret_cast<uint4*>(dl_ptr(xs, row, lane)) = make_uint4(0, 0, 0, 0);
+  constexpr int EPI_ITERS = 16 * R / 32;     // a block of one warp walks the strip's 16 x R results in so many rounds
+  float old[EPI_ITERS], nw[EPI_ITERS];       // EPI 2: the residual's values this thread will add to; the next norm's weights
+  if (EPI == 2) {
+#pragma unroll
+    for (int i = 0; i < EPI_ITERS; ++i) {
+      const int idx = tid + i * (int)blockDim.x, m = idx / R, n = strip * R + idx % R;
+      nw[i] = (idx < 16 * R && m < M && n < N && next_w != nullptr) ? next_w[n] : 0.f;
+    }
+  }
   pdl_wait();
   pdl_launch_dependents();
+  // After the wait, in the order of their latency's weight: the sums of squares and the residual's old values
+  // (plain loads, needed in registers), then the rows of X (asynchronous copies).  Warp w computes the factors
+  // of rows w, w + nwarps, ...; all sums of squares that a lane adds are requested before the first is used
+  // (one L2 latency, not one per strip) and added in strip order; the factors are read after the block-wide
+  // barrier in front of the epilogue.
+  constexpr int SQ_J = 6;                    // 32 * 6 strips at most (checked by the host)
+  float v[4][SQ_J];                          // (a block of fewer than 4 warps repeats this for rows beyond 4 * nwarps, below)
 #pragma unroll
-  for (int row = 0; row < 16; ++row) {
-    const bool okx = k < K && row < M;
-    cp_async16(dl_ptr(xs, row, lane), okx ? X + (int64_t)row * ldx + k : X, okx);
+  for (int mi = 0; mi < 4; ++mi) {
+    const int m = warp + mi * nwarps;
+#pragma unroll
+    for (int j = 0; j < SQ_J; ++j) {
+      const int p = lane + 32 * j;
+      v[mi][j] = (sumsq_in != nullptr && m < M && p < sumsq_parts) ? sumsq_in[(int64_t)p * M + m] : 0.f;
+    }
   }
-  cp_async_commit();
-  constexpr int EPI_ITERS = 16 * R / 32;     // a block of one warp walks the strip's 16 x R results in so many rounds
-  float old[EPI_ITERS];                      // EPI 2: the residual's values this thread will add to
   if (EPI == 2) {
 #pragma unroll
     for (int i = 0; i < EPI_ITERS; ++i) {
@@ -80,14 +112,32 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
       old[i] = (idx < 16 * R && m < M && n < N) ? res_out[(int64_t)m * N + n] : 0.f;
     }
   }
-  // while the rows arrive: warp w computes the factors of rows w, w + nwarps, ...; they are read after the
-  // block-wide barrier in front of the epilogue
-  for (int m = warp; m < 16; m += nwarps) {
-    float s = 0.f;
-    if (sumsq_in != nullptr && m < M)
-      for (int p = lane; p < sumsq_parts; p += 32) s += sumsq_in[(int64_t)p * M + m];
-    s = warp_sum(s);          // lanes hold strided partial sums; added in a fixed order
-    if (lane == 0) row_scale[m] = sumsq_in != nullptr ? (m < M ? 1.0f / sqrtf(s / (float)K + eps) : 0.f) : 1.0f;
+#pragma unroll
+  for (int row = 0; row < 16; ++row)
+    if (row < M && k < K) cp_async16(dl_ptr(xs, row, lane), X + (int64_t)row * ldx + k, true);
+  cp_async_commit();
+  for (int m0 = warp; m0 < 16; m0 += 4 * nwarps) {
+    if (m0 != warp) {
+#pragma unroll
+      for (int mi = 0; mi < 4; ++mi) {
+        const int m = m0 + mi * nwarps;
+#pragma unroll
+        for (int j = 0; j < SQ_J; ++j) {
+          const int p = lane + 32 * j;
+          v[mi][j] = (sumsq_in != nullptr && m < M && p < sumsq_parts) ? sumsq_in[(int64_t)p * M + m] : 0.f;
+        }
+      }
+    }
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi) {
+      const int m = m0 + mi * nwarps;
+      if (m >= 16) break;
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < SQ_J; ++j) s += v[mi][j];
+      s = warp_sum(s);
+      if (lane == 0) row_scale[m] = sumsq_in != nullptr ? (m < M ? 1.0f / sqrtf(s / (float)K + eps) : 0.f) : 1.0f;
+    }
   }
   cp_async_wait<0>();
   __syncwarp();
@@ -139,7 +189,7 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
         const float v = old[i] + total(r, m) * row_scale[m];
         res_out[(int64_t)m * N + n] = v;
         sq = v * v;
-        if (xw_out != nullptr) xw_out[(int64_t)m * N + n] = __float2bfloat16(v * next_w[n]);
+        if (xw_out != nullptr) xw_out[(int64_t)m * N + n] = __float2bfloat16(v * nw[i]);
       }
 #pragma unroll
       for (int o = R / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
@@ -158,7 +208,7 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
 template <int EPI, typename TO, int R>
 int launch_dl(int strips, int warps, cudaStream_t stream, const void* X, int64_t ldx, const float* sumsq_in, int sumsq_parts,
               float eps, const void* W, void* Y, int64_t ldy, float* res_out, float* sumsq_out, const float* next_w,
-              void* xw_out, int M, int N, int K) {
+              void* xw_out, int M, int N, int K, const void* ahead, unsigned long long ahead_bytes) {
   const size_t smem = (size_t)warps * (2 * 16 * DL_KW * sizeof(bf16) + 16 * 17 * sizeof(float));
   static size_t attr = 0;
   if (smem > attr) {
@@ -167,7 +217,8 @@ int launch_dl(int strips, int warps, cudaStream_t stream, const void* X, int64_t
     attr = smem;
   }
   me_launch(gemm_decode_kernel<EPI, TO, R>, dim3(strips), dim3(warps * 32), smem, stream, (const bf16*)X, ldx, sumsq_in,
-            sumsq_parts, eps, (const bf16*)W, (TO*)Y, ldy, res_out, sumsq_out, next_w, (bf16*)xw_out, M, N, K);
+            sumsq_parts, eps, (const bf16*)W, (TO*)Y, ldy, res_out, sumsq_out, next_w, (bf16*)xw_out, M, N, K,
+            (const unsigned char*)ahead, ahead_bytes);
   return 0;
 }
 }  // namespace
@@ -185,25 +236,30 @@ ME_API int me_gemm_decode_sumsq_parts(int N) { const int r = strip_rows(N); retu
 // epi 0: Y (y_dtype) [M][ldy]; epi 1: SiLU-and-multiply (weight rows gate | up, N = columns of Y);
 // epi 2: res_out [M][N] += X W^T, sumsq_out [me_gemm_decode_sumsq_parts(N)][M] and, with next_w [N], xw_out
 // bfloat16 [M][N] = res_out * next_w.
+// ahead (or null), ahead_bytes: memory that a later kernel will read (the next product's weights), asked into
+// L2 by this one; 16-byte aligned.
 ME_API int me_gemm_decode(int epi, const void* X, int64_t ldx, const float* sumsq_in, int sumsq_parts, float eps,
                           const void* W, void* Y, int y_dtype, int64_t ldy, float* res_out, float* sumsq_out,
-                          const float* next_w, void* xw_out, int M, int N, int K, cudaStream_t stream) {
+                          const float* next_w, void* xw_out, int M, int N, int K, const void* ahead,
+                          unsigned long long ahead_bytes, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   ME_REQUIRE(M > 0 && M <= 16, "me_gemm_decode: M=%d is not in 1..16", M);
   ME_REQUIRE(K % 8 == 0 && K > 0 && K <= DL_MAX_WARPS * DL_KW, "me_gemm_decode: K=%d must be a multiple of 8 up to %d", K,
              DL_MAX_WARPS * DL_KW);
   ME_REQUIRE(X != nullptr && (ldx * 2) % 16 == 0, "me_gemm_decode: X is missing or its rows are not 16-byte aligned");
-  ME_REQUIRE(sumsq_in == nullptr || sumsq_parts > 0, "me_gemm_decode: sums of squares without parts");
+  ME_REQUIRE(sumsq_in == nullptr || (sumsq_parts > 0 && sumsq_parts <= 192), "me_gemm_decode: sums of squares in %d parts (1..192)",
+             sumsq_parts);
   ME_REQUIRE(epi == 0 || epi == 1 || (epi == 2 && res_out != nullptr && sumsq_out != nullptr), "me_gemm_decode: epilogue %d", epi);
   ME_REQUIRE((next_w == nullptr) == (xw_out == nullptr) && (next_w == nullptr || epi == 2),
              "me_gemm_decode: the pre-weighted copy needs the residual epilogue, a weight and an output");
+  ME_REQUIRE(ahead == nullptr || ((uintptr_t)ahead & 15) == 0, "me_gemm_decode: memory to fetch ahead must be 16-byte aligned");
   const int warps = (K + DL_KW - 1) / DL_KW;
   const int rows = epi == 1 ? 16 : strip_rows(N);
   const int strips = epi == 1 ? (N + 7) / 8 : (N + rows - 1) / rows;
   int rc = 1;
 #define ME_DL(EPI_, TO_, R_)                                                                                        \
   rc = launch_dl<EPI_, TO_, R_>(strips, warps, stream, X, ldx, sumsq_in, sumsq_parts, eps, W, Y, ldy, res_out, sumsq_out, \
-                                next_w, xw_out, M, N, K)
+                                next_w, xw_out, M, N, K, ahead, ahead_bytes)
   if (epi == 2) {
     if (rows == 8) ME_DL(2, float, 8); else ME_DL(2, float, 16);
   } else if (epi == 1) {

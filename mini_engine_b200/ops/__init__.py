@@ -31,7 +31,7 @@ _PROTOS = {
     "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
     "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P,
                              _I, _P, _P],
-    "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P],
+    "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, ctypes.c_uint64, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
     "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
@@ -207,7 +207,7 @@ def decode_linear_sumsq_parts(N: int) -> int:
 
 def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.Tensor] = None, epilogue: str = "none",
                   row_scale=None, residual_out: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None,
-                  next_norm=None) -> None:
+                  next_norm=None, fetch_ahead: Optional[torch.Tensor] = None) -> None:
     """One decode product with its neighbours folded in (csrc/gemm_decode.cu).
 
     ``x``: bfloat16 [M, K].  ``row_scale`` = (sums of squares float32 [parts, M], eps): x is a residual times a
@@ -215,7 +215,8 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
     RMSNorm.  Output: ``out`` (epilogue "none" or "silu_mul") or ``residual_out`` (float32 [M, N], epilogue
     "residual": residual_out += x W^T; ``sumsq_out`` [decode_linear_sumsq_parts(N), M] gets the new residual's sums
     of squares per strip of columns, and with ``next_norm`` = (weight float32 [N], xw bfloat16 [M, N]) xw gets the new
-    residual times that weight)."""
+    residual times that weight).  ``fetch_ahead``: a tensor that a later kernel reads (the next product's weight);
+    this kernel asks it into L2."""
     epi = {"none": 0, "silu_mul": 1, "residual": 2}[epilogue]
     M, K = x.shape
     _need(x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "decode_linear: x")
@@ -239,7 +240,8 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
         _need(tuple(out.shape) == (M, N) and out.stride(1) == 1, "decode_linear: output shape")
         yp, ydt, ldy = out.data_ptr(), _dt(out), out.stride(0)
     _call("me_gemm_decode", epi, x.data_ptr(), x.stride(0), _ptr(sumsq), sumsq.shape[0] if sumsq is not None else 0, float(eps),
-          weight.data_ptr(), yp, ydt, ldy, _ptr(residual_out), _ptr(sumsq_out), _ptr(nw), _ptr(xw), M, N, K, _stream())
+          weight.data_ptr(), yp, ydt, ldy, _ptr(residual_out), _ptr(sumsq_out), _ptr(nw), _ptr(xw), M, N, K,
+          _ptr(fetch_ahead), fetch_ahead.numel() * fetch_ahead.element_size() if fetch_ahead is not None else 0, _stream())
 
 
 TCGEN05_MIN_ROWS = 128    # rows from which bfloat16 products run csrc/gemm_tcgen05.cu (17..127: cuBLAS)

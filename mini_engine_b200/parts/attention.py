@@ -69,8 +69,11 @@ class GQAAttention(Mixer):
     def cache_needs(self):
         return [KVCacheNeed(self.num_kv_heads, self.head_dim, self.window)]
 
-    def forward(self, x, ctx, call, residual=None, next_norm=None):
-        qkv = self.qkv_proj.forward(x, ctx, "qkv")
+    def first_weight(self):
+        return self.qkv_proj.weight
+
+    def forward(self, x, ctx, call, residual=None, upcoming=None):
+        qkv = self.qkv_proj.forward(x, ctx, "qkv", fetch_ahead=self.o_proj.weight)
         kv = ctx.kv_cache(call.cache_slot)
         meta = ctx.attn_meta
         has_norm = self.qk_norm_eps is not None
@@ -93,7 +96,9 @@ class GQAAttention(Mixer):
         ops.paged_attention(qkv, out, self.num_heads, self.num_kv_heads, self.head_dim,
                             kv.pool, kv.page_size, kv.block_tables, meta,
                             self.scale, self.window, decodes=not fused)
-        return self.o_proj.forward(out, ctx, "mixer_out", may_split=True, residual=residual, next_norm=next_norm)
+        return self.o_proj.forward(out, ctx, "mixer_out", may_split=True, residual=residual,
+                                   next_norm=upcoming.norm if upcoming else None,
+                                   fetch_ahead=upcoming.weight if upcoming else None)
 
 
 register_mixer("gqa_attention", GQAAttention)

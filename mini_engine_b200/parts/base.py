@@ -69,6 +69,15 @@ class AddedToResidual:
 
 
 @dataclass
+class Upcoming:
+    """What runs right after a mixer or feed-forward, as far as its last kernel can prepare for it: the norm that
+    reads the residual stream next (its element-wise half may be written with the residual) and the first weight
+    matrix used after that (it may be asked into the cache ahead of time).  Either may be None."""
+    norm: "Any" = None
+    weight: "Optional[torch.Tensor]" = None
+
+
+@dataclass
 class PendingNorm:
     """Rows that are ``norm(residual) * weight`` but have not been computed yet: ``preweighted`` holds
     residual * weight, and each row still lacks its factor rsqrt(sum of ``sumsq`` / width + eps).  A consumer
@@ -97,12 +106,17 @@ class Part:
 
     capturable = False
     # A mixer or feed-forward whose first kernel can finish a PendingNorm, and whose last kernel can add into the
-    # residual (``forward(..., residual=, next_norm=)``), says so; the block then hands it those.
+    # residual (``forward(..., residual=, upcoming=)``), says so; the block then hands it those.
     takes_pending_norm = False
     adds_to_residual = False
 
     def __init__(self):
         self.params: dict[str, torch.Tensor] = {}
+
+    def first_weight(self) -> "Optional[torch.Tensor]":
+        """The weight matrix that this part's first kernel reads, if the part wants the kernel before it to ask
+        for it ahead of time; None otherwise."""
+        return None
 
     def param_decls(self) -> list[ParamDecl]:
         return []

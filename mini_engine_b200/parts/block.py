@@ -10,7 +10,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional
 
-from .base import Part
+from .base import Part, Upcoming
 from .registry import PartSpec, build_part
 
 
@@ -48,23 +48,24 @@ class PreNormBlock(Part):
                 (s.feed_forward_norm_prefix, self.feed_forward_norm),
                 (s.feed_forward_prefix, self.feed_forward)]
 
-    def first_norm(self):
-        """The norm that reads the residual stream first in this block (the block before may prepare for it)."""
-        return self.mixer_norm
+    def upcoming(self) -> Upcoming:
+        """What this block starts with, for the block that runs before it."""
+        return Upcoming(self.mixer_norm, self.mixer.first_weight())
 
-    def forward(self, residual, delta, ctx, call, next_norm=None):
+    def forward(self, residual, delta, ctx, call, upcoming=None):
         """``delta``: the output of the sub-layer before this block, not yet added to ``residual`` (or the mark
-        that it has been).  Returns this block's last output the same way.  ``next_norm``: the norm that reads
-        the residual after this block, if the caller knows it."""
+        that it has been).  Returns this block's last output the same way.  ``upcoming``: what runs after this
+        block (``Upcoming``), if the caller knows it."""
         mixer, ffn = self.mixer, self.feed_forward
         x = self.mixer_norm.forward(residual, delta, ctx, lazy=mixer.takes_pending_norm)
         if mixer.adds_to_residual:
-            mixed = mixer.forward(x, ctx, call, residual=residual, next_norm=self.feed_forward_norm)
+            mixed = mixer.forward(x, ctx, call, residual=residual,
+                                  upcoming=Upcoming(self.feed_forward_norm, ffn.first_weight()))
         else:
             mixed = mixer.forward(x, ctx, call)
         x = self.feed_forward_norm.forward(residual, mixed, ctx, lazy=ffn.takes_pending_norm)
         if ffn.adds_to_residual:
-            return ffn.forward(x, ctx, residual=residual, next_norm=next_norm)
+            return ffn.forward(x, ctx, residual=residual, upcoming=upcoming)
         return ffn.forward(x, ctx)
 
 

@@ -36,15 +36,20 @@ class Linear(Part):
     def weight(self) -> torch.Tensor:
         return self.p(self.name)
 
+    def first_weight(self):
+        return self.weight
+
     def forward(self, x, ctx, out_name: str, *, out_dtype: Optional[torch.dtype] = None,
                 epilogue: str = "none", may_split: bool = False, residual: Optional[torch.Tensor] = None,
-                next_norm=None):
+                next_norm=None, fetch_ahead: Optional[torch.Tensor] = None):
         """``x W^T``.
 
         ``x`` is a tensor or a ``PendingNorm`` (the product then applies the rows' factors to its results where
         its kernel takes the shape, else the norm is computed first).  With ``residual`` the product may add its
         result into that float32 tensor itself and return ``AddedToResidual``; ``next_norm`` is the norm that
-        will read that residual next, whose element-wise half the same kernel then writes.  With ``may_split`` the
+        will read that residual next, whose element-wise half the same kernel then writes.  ``fetch_ahead`` is a
+        tensor that a later kernel reads (the next product's weight): a decode product asks it into L2 while it
+        runs, since the short dependent kernels of a decode step leave the memory system idle.  With ``may_split`` the
         result may come as float32 partial results [splits, T, N] of a split-K product; only a consumer that adds
         them (the next norm) may ask for that."""
         pending = x if isinstance(x, PendingNorm) else None
@@ -63,7 +68,7 @@ class Linear(Part):
             nw = next_norm.separable_weight() if next_norm is not None else None
             xw = ctx.buffer(out_name + "_preweighted", (M, self.out_features), torch.bfloat16) if nw is not None else None
             ops.decode_linear(self.weight, x, row_scale=row_scale, epilogue="residual", residual_out=residual,
-                              sumsq_out=sumsq, next_norm=(nw, xw) if nw is not None else None)
+                              sumsq_out=sumsq, next_norm=(nw, xw) if nw is not None else None, fetch_ahead=fetch_ahead)
             return AddedToResidual(sumsq, xw, nw)
         n_out = self.out_features // 2 if epilogue == "silu_mul" else self.out_features
         if may_split and epilogue == "none" and not fused:
@@ -72,7 +77,7 @@ class Linear(Part):
                 return part
         out = ctx.buffer(out_name, (M, n_out), out_dtype or ctx.act_dtype)
         if fused:
-            ops.decode_linear(self.weight, x, out=out, epilogue=epilogue, row_scale=row_scale)
+            ops.decode_linear(self.weight, x, out=out, epilogue=epilogue, row_scale=row_scale, fetch_ahead=fetch_ahead)
             return out
         ops.linear(x, self.weight, out, epilogue=epilogue, workspace=ctx.buffer, err=ctx.error_flag)
         return out

@@ -31,9 +31,14 @@ class SwiGLU(FeedForward):
     def sub_parts(self):
         return [("", self.gate_up_proj), ("", self.down_proj)]
 
-    def forward(self, x, ctx, residual=None, next_norm=None):
-        act = self.gate_up_proj.forward(x, ctx, "ffn_act", epilogue="silu_mul")
-        return self.down_proj.forward(act, ctx, "ffn_out", may_split=True, residual=residual, next_norm=next_norm)
+    def first_weight(self):
+        return self.gate_up_proj.weight
+
+    def forward(self, x, ctx, residual=None, upcoming=None):
+        act = self.gate_up_proj.forward(x, ctx, "ffn_act", epilogue="silu_mul", fetch_ahead=self.down_proj.weight)
+        return self.down_proj.forward(act, ctx, "ffn_out", may_split=True, residual=residual,
+                                      next_norm=upcoming.norm if upcoming else None,
+                                      fetch_ahead=upcoming.weight if upcoming else None)
 
 
 register_feed_forward("swiglu", SwiGLU)

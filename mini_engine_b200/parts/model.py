@@ -105,9 +105,9 @@ class DecoderModel(Part):
         residual = self.embed.forward(token_ids, ctx)
         delta = None
         for i, call in enumerate(self.schedule):
-            # the block learns which norm reads the residual after it, so that its last kernel can prepare for it
-            after = self.blocks[self.schedule[i + 1].block].first_norm() if i + 1 < len(self.schedule) else None
-            delta = self.blocks[call.block].forward(residual, delta, ctx, call, next_norm=after)
+            # the block learns what runs after it, so that its last kernel can prepare for it
+            after = self.blocks[self.schedule[i + 1].block].upcoming() if i + 1 < len(self.schedule) else None
+            delta = self.blocks[call.block].forward(residual, delta, ctx, call, upcoming=after)
         return self.final_norm.forward(residual, delta, ctx, rows=ctx.logits_rows)
 
     def compute_logits(self, hidden: torch.Tensor, ctx) -> torch.Tensor:

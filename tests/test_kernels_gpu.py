@@ -197,7 +197,8 @@ def test_decode_products_with_norm_and_residual_folded_in(ops, M, N, K):
     assert torch.allclose(sumsq, want_sq, rtol=1e-4, atol=1e-5)
     assert torch.equal(xw, (res * next_w).to(torch.bfloat16))
     res2, sumsq2 = rnd(M, N, seed=3), torch.empty_like(sumsq)
-    ops.decode_linear(w, x, epilogue="residual", residual_out=res2, sumsq_out=sumsq2)        # without a next norm
+    later = rnd(777, 40, dtype=torch.bfloat16, seed=9)                                       # asked into L2 on the way
+    ops.decode_linear(w, x, epilogue="residual", residual_out=res2, sumsq_out=sumsq2, fetch_ahead=later)    # no next norm
     assert torch.equal(res2, res) and torch.equal(sumsq2, sumsq)
     # the other half of that norm: a product over a pre-weighted residual applies the rows' factors to its results
     K_parts = (K + 15) // 16
