@@ -44,6 +44,22 @@ class CacheHolder:
         self.num_computed_tokens = 0
         self.num_cached_tokens = 0
         self.num_hashed_blocks = 0
+        self.table_version = 0                      # bumped whenever a table changes other than by growing
+        self._arrays: dict[int, tuple[int, np.ndarray]] = {}
+
+    def table_array(self, g: int) -> np.ndarray:
+        """Group ``g``'s block table as int32 (read only), kept up to date without converting the whole
+        list at every step: pages are appended far more often than anything else happens to a table."""
+        table = self.block_tables[g]
+        ent = self._arrays.get(g)
+        if ent is None or ent[0] != self.table_version or len(ent[1]) > len(table):
+            arr = np.asarray(table, dtype=np.int32)
+        else:
+            arr = ent[1]
+            if len(arr) < len(table):
+                arr = np.concatenate((arr, np.asarray(table[len(arr):], dtype=np.int32)))
+        self._arrays[g] = (self.table_version, arr)
+        return arr
 
 
 def compute_hash(token_ids: Sequence[int], prefix: int = -1) -> int:
@@ -191,6 +207,7 @@ class CacheManager:
                 if table[i] >= 0:
                     pool.release(table[i])
                     table[i] = -1
+                    holder.table_version += 1
                     released += 1
                 i += 1
             holder.num_released[g] = i
@@ -206,6 +223,7 @@ class CacheManager:
                         pool.release(p)
                 holder.block_tables[g].clear()
                 holder.num_released[g] = 0
+            holder.table_version += 1
         if holder.state_slot >= 0:
             self.state_slots.release(holder.state_slot)
             holder.state_slot = -1

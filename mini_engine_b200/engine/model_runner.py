@@ -177,13 +177,15 @@ class ModelRunner:
         return self._pins[k], dev
 
     def build_batch(self, items: Sequence[StepItem], ctx: StepContext, *, pad_reqs: int = 0,
-                    table_width: int = 0, dev: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, list[int]]:
+                    table_width: int = 0, dev: Optional[torch.Tensor] = None,
+                    fill_ctx: bool = True) -> tuple[Optional[torch.Tensor], list[int]]:
         """Lay the step's metadata out in pinned memory, copy it once, fill ``ctx``.
 
         Requests that bring one token come first (as in engine/model_runner.py:88-89).
         ``pad_reqs``/``table_width`` give a fixed shape to steps replayed from a graph: padding
         requests have no keys and write nowhere.  Returns (token ids on the device, the batch
-        order as indices into ``items``)."""
+        order as indices into ``items``).  With ``fill_ctx`` False only the copy is made: a captured graph
+        already knows where every array lies."""
         order = [i for i, it in enumerate(items) if len(it.tokens) == 1] + \
                 [i for i, it in enumerate(items) if len(it.tokens) != 1]
         D = sum(1 for it in items if len(it.tokens) == 1)
@@ -256,9 +258,14 @@ class ModelRunner:
         cu = [0]
         for k, i in enumerate(order):
             n = lens[k]
-            host[o_tok + t:o_tok + t + n] = np.asarray(items[i].tokens, dtype=np.int32)
-            host[o_pos + t:o_pos + t + n] = np.arange(starts[k], ends[k], dtype=np.int32)
-            host[o_req + t:o_req + t + n] = k
+            if n == 1:                              # single tokens: plain integers beat array calls
+                host[o_tok + t] = items[i].tokens[0]
+                host[o_pos + t] = starts[k]
+                host[o_req + t] = k
+            else:
+                host[o_tok + t:o_tok + t + n] = np.asarray(items[i].tokens, dtype=np.int32)
+                host[o_pos + t:o_pos + t + n] = np.arange(starts[k], ends[k], dtype=np.int32)
+                host[o_req + t:o_req + t + n] = k
             t += n
             cu.append(t)
         for k in range(pad):
@@ -293,8 +300,21 @@ class ModelRunner:
             sm[:] = -1
             t = 0
             for k, i in enumerate(order):
-                table = np.asarray(items[i].holder.block_tables[g], dtype=np.int32)
+                holder = items[i].holder
+                table = holder.table_array(g) if hasattr(holder, "table_array") else \
+                    np.asarray(holder.block_tables[g], dtype=np.int32)
                 bt[k, :len(table)] = table
+                if lens[k] == 1:
+                    pos = starts[k]
+                    pi = pos // ps
+                    if len(table) <= pi:
+                        raise ValueError("a request's block table does not cover its new tokens")
+                    page = int(table[pi])
+                    if page < 0:
+                        raise ValueError("a new token would be written to a page that was given back")
+                    sm[t] = page * ps + (pos - pi * ps)
+                    t += 1
+                    continue
                 pos = np.arange(starts[k], ends[k])
                 page = pos // ps
                 if len(table) <= int(page[-1]):
@@ -312,6 +332,8 @@ class ModelRunner:
             ev.record()
         self.last_h2d_bytes = total * 4
         self.last_num_wanted = S_real
+        if not fill_ctx:
+            return None, order
 
         ctx.positions = dev[o_pos:o_pos + T]
         ctx.token_req = dev[o_req:o_req + T]
@@ -384,7 +406,8 @@ class ModelRunner:
             g = self._graphs[(bucket, ctx_bucket)] = _DecodeGraph(self, bucket)
             n = 16 * bucket + 64 + sum(4 * bucket + bucket * width + 8 for _ in self.groups)
             g.meta_dev = torch.zeros(n + 64, dtype=torch.int32, device=self.device)
-        token_ids, _ = self.build_batch(items, g.ctx, pad_reqs=bucket, table_width=width, dev=g.meta_dev)
+        token_ids, _ = self.build_batch(items, g.ctx, pad_reqs=bucket, table_width=width, dev=g.meta_dev,
+                                        fill_ctx=g.graph is None)
         if g.graph is None:
             # Once eagerly (allocates the work buffers), then captured; both runs do the step's real work.
             g.ctx.frozen = False
