@@ -57,6 +57,7 @@ class StepContext:
         self.device = runner.device
         self.error_flag: torch.Tensor = runner.error_flag
         self._arena: dict[str, torch.Tensor] = {} if arena is None else arena
+        self._views: dict = {}
         self.frozen = False            # a captured graph's buffers must not be reallocated
         # Filled per step:
         self.positions: torch.Tensor = None
@@ -78,6 +79,10 @@ class StepContext:
     def buffer(self, name: str, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A work buffer by name: the same storage every step, grown when a step needs more.
         ``zero``: the storage is zeroed when it is made (for counters that kernels leave at zero)."""
+        key = (name, tuple(shape), dtype)
+        hit = self._views.get(key)
+        if hit is not None and hit[0] is self._arena.get(name):
+            return hit[1]
         n = 1
         for s in shape:
             n *= int(s)
@@ -88,7 +93,9 @@ class StepContext:
                 raise RuntimeError(f"work buffer {name!r} would move under a captured graph")
             flat = (torch.zeros if zero else torch.empty)(nbytes + (-nbytes) % 256, dtype=torch.uint8, device=self.device)
             self._arena[name] = flat
-        return flat[:n * dtype.itemsize].view(dtype).view(*shape)
+        view = flat[:n * dtype.itemsize].view(dtype).view(*shape)
+        self._views[key] = (flat, view)              # the same tensor object until the storage is replaced
+        return view
 
     def kv_cache(self, cache_slot: int) -> KVView:
         g, idx = self.runner.slot_location[cache_slot]

@@ -85,17 +85,28 @@ def library_file() -> str:
     return _lib._name
 
 
+_fns: dict = {}
+
+
 def _call(name: str, *args) -> None:
     global launches
-    lib = _lib or require_extension()
-    rc = getattr(lib, name)(*args)
-    if rc != 0:
-        raise KernelError(lib.me_last_error().decode())
+    fn = _fns.get(name)
+    if fn is None:
+        fn = _fns[name] = getattr(_lib or require_extension(), name)
+    if fn(*args) != 0:
+        raise KernelError(_lib.me_last_error().decode())
     launches += 1
 
 
+_device_index: Optional[int] = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The current stream's handle (a launch a few microseconds apart cannot afford torch's Stream object)."""
+    global _device_index
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return torch._C._cuda_getCurrentRawStream(_device_index)
 
 
 def _dt(t: torch.Tensor) -> int:
