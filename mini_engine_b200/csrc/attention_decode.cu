@@ -677,6 +677,14 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   const int L = context_lens[b];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
   const int n_g = min(16, G - g0);
+  // The page of this lane's piece of the partition is asked for together with the context length (which page it
+  // is depends on the partition alone; whether it holds keys of the request is decided afterwards): one
+  // round trip to memory before the loads can be issued, not two.
+  int page_ahead = -1;
+  if (warp == 0 && lane < DEC_PART / page_size) {
+    const int pi = (z * DEC_PART) / page_size + lane;
+    if (pi < bt_stride) page_ahead = block_tables[(int64_t)b * bt_stride + pi];
+  }
   const int lo_w = window > 0 ? max(0, L - window) : 0;
   const int part_lo = z * DEC_PART, part_hi = min(L, part_lo + DEC_PART);
   const int64_t slot0 = ((int64_t)b * nh + kvh * G + g0) * max_parts + z;
@@ -695,7 +703,6 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   bf16* ks = reinterpret_cast<bf16*>(aligned);
   bf16* vs = ks + DEC_PART * HD;
   bf16* qs = vs + DEC_PART * HD;
-  const int* bt = block_tables + (int64_t)b * bt_stride;
   const int64_t tok = cu_seqlens[b];
   // Only the partition that holds the request's newest key depends on the kernel before this one (which
   // wrote that key); the others fetch their keys and values while that kernel is still running.  A block
@@ -722,8 +729,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     int first_row = -1;                                // row of the pool's 2-D view where this lane's page keeps K
     if (lane < n_pages) {
       const int j0 = part_lo + lane * page_size;
-      int page = -1;
-      if (j0 < part_hi && j0 + page_size > lo_w) page = bt[j0 / page_size];
+      const int page = (j0 < part_hi && j0 + page_size > lo_w) ? page_ahead : -1;
       if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size;
     }
     const unsigned present = __ballot_sync(0xffffffffu, first_row >= 0);

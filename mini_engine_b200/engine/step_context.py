@@ -39,6 +39,7 @@ class AttnMeta:
     max_context_len: int               # host upper bound of context_lens (sizes split-K scratch)
     workspace: Any                     # callable (name, shape, dtype) -> tensor
     error_flag: Any = None             # int32[4] on the device: kernels report bad input or a timed-out wait here
+    scratch_context_len: int = 0       # if larger than max_context_len: size split-K scratch for this many keys (so it never has to grow)
 
 
 @dataclass
@@ -59,6 +60,7 @@ class StepContext:
         self._arena: dict[str, torch.Tensor] = {} if arena is None else arena
         self._views: dict = {}
         self.frozen = False            # a captured graph's buffers must not be reallocated
+        self.on_replace = None         # called with a buffer's name before a larger one takes its place
         # Filled per step:
         self.positions: torch.Tensor = None
         self.token_req: torch.Tensor = None
@@ -91,6 +93,8 @@ class StepContext:
         if flat is None or flat.numel() < nbytes:
             if self.frozen:
                 raise RuntimeError(f"work buffer {name!r} would move under a captured graph")
+            if flat is not None and self.on_replace is not None:
+                self.on_replace(name)               # others that recorded the old storage must forget it
             flat = (torch.zeros if zero else torch.empty)(nbytes + (-nbytes) % 256, dtype=torch.uint8, device=self.device)
             self._arena[name] = flat
         view = flat[:n * dtype.itemsize].view(dtype).view(*shape)

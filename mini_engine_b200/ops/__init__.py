@@ -476,8 +476,9 @@ def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_siz
     of them by name (tests run each)."""
     D = meta.num_decodes
     parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
-    tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * parts * head_dim,), torch.float32)
-    tmp_ml = meta.workspace("decode_tmp_ml", (2, D * num_heads * parts), torch.float32)
+    room = max(parts, (getattr(meta, "scratch_context_len", 0) + DECODE_PARTITION - 1) // DECODE_PARTITION)
+    tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * room * head_dim,), torch.float32)
+    tmp_ml = meta.workspace("decode_tmp_ml", (2, D * num_heads * room), torch.float32)
     tm = kv_tensor_map(pool, page_size) if kind in ("auto", "tensor_cores_tma") else None
     _call("me_attn_decode", qkv.data_ptr(), _dt(qkv), qkv.stride(0), out.data_ptr(), out.stride(0),
           pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
@@ -506,8 +507,9 @@ def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, pa
     Other arguments as for that function and ``attention_decode``."""
     D = meta.num_decodes
     parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
-    tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * parts * head_dim,), torch.float32)
-    tmp_ml = meta.workspace("decode_tmp_ml", (2, D * num_heads * parts), torch.float32)
+    room = max(parts, (getattr(meta, "scratch_context_len", 0) + DECODE_PARTITION - 1) // DECODE_PARTITION)
+    tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * room * head_dim,), torch.float32)
+    tmp_ml = meta.workspace("decode_tmp_ml", (2, D * num_heads * room), torch.float32)
     tm = kv_tensor_map(pool, page_size)
     _need(tm is not None and tuple(pool.shape[1:]) == (2, num_kv_heads, page_size, head_dim) and pool.is_contiguous(),
           "attention_decode_fused: cache slot")
