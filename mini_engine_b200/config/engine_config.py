@@ -29,6 +29,7 @@ class EngineConfig:
     enable_prefix_caching: bool = True
     seed: int = 0
     use_cuda_graphs: bool = True
+    overlap_steps: bool = True          # launch the likely next decode step before reading the current one's tokens
 
     def __post_init__(self):
         self.model = os.path.expanduser(self.model)

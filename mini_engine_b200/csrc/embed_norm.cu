@@ -5,13 +5,17 @@
 // is normalised), layers/activation.py:4-7 (silu(gate) * up).
 #include "common.cuh"
 
+// A negative id ~j stands for ``feedback[j]``: the token that the step before drew for row j, still on the
+// device.  That lets the host launch a decode step before it has read the step before it.
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
-                             float* __restrict__ out, int H, int V, int* __restrict__ err) {
+                             float* __restrict__ out, int H, int V, int* __restrict__ err,
+                             const int* __restrict__ feedback, int n_feedback) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
-  const int id = ids[t];
+  int id = ids[t];
+  if (id < 0 && feedback != nullptr && ~id < n_feedback) id = feedback[~id];
   const bool ok = id >= 0 && id < V;
   if (!ok && threadIdx.x == 0) atomicOr(err, 1);
   const TW* row = table + (int64_t)(ok ? id : 0) * H;
@@ -20,12 +24,13 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
 }
 
 ME_API int me_embed(const int* ids, const void* table, int table_dtype, float* out, int T, int H,
-                    int V, int* err, cudaStream_t stream) {
+                    int V, int* err, const int* feedback, int n_feedback, cudaStream_t stream) {
   if (T == 0) return 0;
   ME_REQUIRE(T > 0 && H > 0 && V > 0, "me_embed: bad sizes T=%d H=%d V=%d", T, H, V);
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   ME_DISPATCH_DTYPE(table_dtype, TW,
-                    me_launch(embed_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, (const TW*)table, out, H, V, err));
+                    me_launch(embed_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, (const TW*)table, out, H, V, err,
+                              feedback, n_feedback));
   ME_LAUNCH_CHECK("me_embed");
   return 0;
 }

@@ -45,8 +45,12 @@ class LLMEngine:
             config.eos = self.tokenizer.eos_token_id        # engine/llm_engine.py:19
         self.cache = self.model_runner.make_cache_manager(config.enable_prefix_caching)
         self.scheduler = Scheduler(config, self.cache)
-        self._tokens_dev = torch.empty(config.max_num_seqs + 4, dtype=torch.int32, device=self.model_runner.device)
-        self._tokens_pin = torch.empty(config.max_num_seqs + 4, dtype=torch.int32, pin_memory=True)
+        self._result_pins = [torch.empty(config.max_num_seqs + 4, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+        self._result_events = [torch.cuda.Event() for _ in range(3)]
+        self._turn = 0
+        self._ahead = None                 # (requests, handle) of a step that is already running on the device
+        self.steps_ahead_used = 0          # steps launched ahead of the host whose results were kept ...
+        self.steps_ahead_dropped = 0       # ... and those the scheduler decided otherwise about
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -67,34 +71,98 @@ class LLMEngine:
         return int(s) & 0x7FFFFFFF
 
     # ---- one step --------------------------------------------------------------------
-    def step(self):
-        seqs = self.scheduler.schedule()
-        num_decode = sum(1 for s in seqs if s.num_scheduled_tokens == 1)
-        num_prefill = sum(s.num_scheduled_tokens for s in seqs if s.num_scheduled_tokens > 1)
-        items, samplers = [], []
-        for s in seqs:
-            a, n = s.num_computed_tokens, s.num_scheduled_tokens
-            wants = s.samples_this_step
-            items.append(StepItem(s, s.scheduled_tokens(), a, [n - 1] if wants else [],
-                                  (s.sampling_params.temperature, self._seed_of(s)) if wants else None))
-            if wants:
-                samplers.append(s)
-        # One copy to the device (the step's metadata, sampling options included), the step with the
-        # draw on the device, one copy back (the drawn ids and the kernels' error flags).
+    # One copy to the device (the step's metadata, sampling options included), the step with the draw on the
+    # device, one copy back (the kernels' error flags and the drawn ids).  The copy back is asynchronous: while
+    # the device runs a decode step, the host launches the step that will most likely follow it (the same
+    # requests, one token further, each continuing from the token the device is about to draw: a token id ~j in
+    # the metadata means row j of the step before) and only then waits for the first step's tokens.  If the
+    # scheduler then decides on exactly that step, its results are kept; if not (a request ended on its
+    # end-of-sequence token, a new request arrived, pages ran out) they are dropped, which costs a millisecond
+    # of device time and changes nothing: the dropped step wrote the keys and values that the real one writes
+    # again, and draws depend on (seed, position) only.
+    def _launch(self, seqs, items=None) -> dict:
+        if items is None:
+            items = []
+            for s in seqs:
+                a, n = s.num_computed_tokens, s.num_scheduled_tokens
+                wants = s.samples_this_step
+                items.append(StepItem(s, s.scheduled_tokens(), a, [n - 1] if wants else [],
+                                      (s.sampling_params.temperature, self._seed_of(s)) if wants else None))
+        rows = [i for i, it in enumerate(items) if it.want]
         result = self.model_runner.step(items, sample=True)
         self.h2d_bytes += self.model_runner.last_h2d_bytes
-        sampled = {}
-        if samplers:
-            S = len(samplers)
-            self._tokens_dev[:S].copy_(result.tokens)
-            self._tokens_dev[S:S + 4].copy_(self.model_runner.error_flag)
-            self._tokens_pin[:S + 4].copy_(self._tokens_dev[:S + 4])
-            self.d2h_bytes += (S + 4) * 4
-            got = self._tokens_pin[:S + 4].tolist()
-            if any(got[S:]):
-                self.model_runner.check_device_errors()
-            sampled = {s.seq_id: t for s, t in zip(samplers, got[:S])}
-        emitted = self.scheduler.postprocess(seqs, [sampled.get(s.seq_id) for s in seqs])
+        k = self._turn = (self._turn + 1) % 3
+        S = len(rows)
+        dev = self.model_runner.result_dev
+        dev[:4].copy_(self.model_runner.error_flag)
+        if S:
+            dev[4:4 + S].copy_(result.tokens)
+        self._result_pins[k][:4 + S].copy_(dev[:4 + S], non_blocking=True)
+        self._result_events[k].record()
+        self.d2h_bytes += (4 + S) * 4
+        return {"turn": k, "rows": rows, "take": list(range(S))}
+
+    def _collect(self, seqs, handle) -> list:
+        """The tokens of a launched step, one per request (None where the request drew none)."""
+        k = handle["turn"]
+        self._result_events[k].synchronize()
+        got = self._result_pins[k][:4 + len(handle["rows"])].tolist()
+        if any(got[:4]):
+            self.model_runner.check_device_errors()
+        tokens = [None] * len(seqs)
+        for i, r in zip(handle["for"] if "for" in handle else handle["rows"], handle["take"]):
+            tokens[i] = got[4 + r]
+        return tokens
+
+    def _launch_ahead(self, seqs):
+        """The step that follows a decode step of ``seqs`` if nothing unforeseen happens; None if it is not worth
+        or not possible to guess."""
+        if not self.config.overlap_steps or self.scheduler.waiting:
+            return None
+        if any(s.num_scheduled_tokens != 1 or not s.samples_this_step for s in seqs):
+            return None
+        ahead, items = [], []
+        for j, s in enumerate(seqs):
+            if s.num_completion_tokens + 1 >= s.sampling_params.max_tokens or len(s) + 1 >= self.config.max_model_len:
+                continue                             # this step is the request's last
+            if not self.cache.allocate(s, 2):        # room for the token after the one being drawn; nobody is evicted for a guess
+                return None
+            ahead.append(s)
+            items.append(StepItem(s, [~j], len(s), [0], (s.sampling_params.temperature, self._seed_of(s))))
+        if not ahead:
+            return None
+        return ahead, self._launch(ahead, items)
+
+    def step(self):
+        if self._ahead is not None:
+            seqs, handle = self._ahead               # launched during the call before this one
+            self._ahead = None
+        else:
+            seqs = self.scheduler.schedule()
+            handle = self._launch(seqs)
+        num_decode = sum(1 for s in seqs if s.num_scheduled_tokens == 1)
+        num_prefill = sum(s.num_scheduled_tokens for s in seqs if s.num_scheduled_tokens > 1)
+        guess = self._launch_ahead(seqs)
+        tokens = self._collect(seqs, handle)
+        emitted = self.scheduler.postprocess(seqs, tokens)
+        if guess is not None:
+            ahead, ahead_handle = guess
+            if self.scheduler.is_finished():
+                self.steps_ahead_dropped += 1
+            else:
+                nxt = self.scheduler.schedule()
+                expect = [s for s in ahead if not s.is_finished]
+                same = (len(nxt) == len(expect) and all(a is b for a, b in zip(nxt, expect))
+                        and all(s.num_scheduled_tokens == 1 and s.samples_this_step for s in nxt))
+                if same:
+                    where = {id(s): r for r, s in enumerate(ahead)}
+                    ahead_handle["for"] = list(range(len(nxt)))
+                    ahead_handle["take"] = [where[id(s)] for s in nxt]
+                    self._ahead = (nxt, ahead_handle)
+                    self.steps_ahead_used += 1
+                else:
+                    self.steps_ahead_dropped += 1
+                    self._ahead = (nxt, self._launch(nxt))
         outputs = [(s.seq_id, s.completion_token_ids) for s in emitted if s.is_finished]
         return outputs, num_prefill, num_decode, [s.seq_id for s in emitted]
 

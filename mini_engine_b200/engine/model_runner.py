@@ -109,6 +109,10 @@ class ModelRunner:
         self.state_storage = {slot: torch.zeros(self.num_state_slots, *need.shape, dtype=torch.float32,
                                                 device=self.device)
                               for slot, need in self.state_needs.items()}
+        # Four error flags and the tokens drawn by the last step whose results were staged here: one copy to the host,
+        # and the place where a step launched ahead of the host finds the tokens it continues from (a token id ~j).
+        self.result_dev = torch.zeros(4 + max_num_seqs, dtype=torch.int32, device=self.device)
+        self.token_feedback = self.result_dev[4:]
         self.ctx = StepContext(self)
         self._pins: list[Optional[torch.Tensor]] = [None, None]     # pinned host int32, used in turn
         self._pin_events: list[Any] = [None, None]

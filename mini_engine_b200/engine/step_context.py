@@ -61,6 +61,7 @@ class StepContext:
         self._views: dict = {}
         self.frozen = False            # a captured graph's buffers must not be reallocated
         self.on_replace = None         # called with a buffer's name before a larger one takes its place
+        self.token_feedback = getattr(runner, "token_feedback", None)   # int32 on the device: a token id ~j in a step means entry j of it
         # Filled per step:
         self.positions: torch.Tensor = None
         self.token_req: torch.Tensor = None

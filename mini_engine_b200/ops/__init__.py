@@ -21,7 +21,7 @@ MAX_HEAD_DIM = 256
 
 _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 _PROTOS = {
-    "me_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+    "me_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P, _I, _P],
     "me_add_rmsnorm": [_P, _P, _I, _P, _F, _P, _I, _P, _I, _I, _I, _L, _P],
     "me_gemm_skinny": [_P, _L, _P, _P, _I, _L, _P, _I, _I, _I, _I, _P],
     "me_silu_mul": [_P, _P, _I, _I, _I, _P],
@@ -135,12 +135,17 @@ def check_attention_sizes(head_dim: int, num_heads: int, num_kv_heads: int) -> N
 
 
 # ---- element-wise and normalisation ----------------------------------------------------
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor,
+          feedback: Optional[torch.Tensor] = None) -> None:
+    """Rows of ``table`` into the float32 ``out``.  An id ~j (negative) stands for ``feedback[j]`` (int32 on the
+    device: the tokens the step before drew); ids outside the vocabulary set flag 0 of ``err``."""
     _need(ids.dtype == torch.int32 and ids.is_contiguous(), "embed: token ids must be contiguous int32")
+    _need(feedback is None or (feedback.dtype == torch.int32 and feedback.is_contiguous()), "embed: feedback must be int32")
     _need(out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous(), "embed: bad tensors")
     T, (V, H) = ids.shape[0], table.shape
     _need(tuple(out.shape) == (T, H), "embed: output shape")
-    _call("me_embed", ids.data_ptr(), table.data_ptr(), _dt(table), out.data_ptr(), T, H, V, err.data_ptr(), _stream())
+    _call("me_embed", ids.data_ptr(), table.data_ptr(), _dt(table), out.data_ptr(), T, H, V, err.data_ptr(), _ptr(feedback),
+          feedback.numel() if feedback is not None else 0, _stream())
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,

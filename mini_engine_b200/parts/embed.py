@@ -25,7 +25,7 @@ class TokenEmbedding(Part):
 
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
         out = ctx.buffer("residual", (token_ids.shape[0], self.hidden_size), torch.float32)
-        ops.embed(token_ids, self.p("weight"), out, ctx.error_flag)
+        ops.embed(token_ids, self.p("weight"), out, ctx.error_flag, feedback=getattr(ctx, "token_feedback", None))
         return out
 
 

@@ -113,3 +113,51 @@ def test_add_request_and_step_surface():
     assert finished[0][0] == b and len(finished[0][1]) == 3
     with pytest.raises(ValueError, match="tokenizer"):
         llm.add_request("some text", SamplingParams())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_of_the_host_change_nothing(dtype):
+    """The engine launches the likely next decode step before it has read the current one's tokens.  With and
+    without that, the same requests give the same tokens: with different lengths (requests drop out of the
+    guessed batch), with an end-of-sequence token that ends requests unforeseen (their rows of the guessed step
+    are ignored), and with a request that arrives while others decode (the guessed step is dropped)."""
+    from mini_engine_b200 import SamplingParams
+    name = "B"
+    vocab = ALL[name][0]["vocab_size"]
+    prompts = helpers.random_requests(vocab, (3, 40, 17, 29, 9), seed=5)
+    lens = [12, 5, 20, 9, 16]
+
+    def run(overlap, eos=None, late=None):
+        llm = _llm(name, dtype, overlap_steps=overlap)
+        if eos is not None:
+            llm.scheduler.eos = eos
+        sps = [SamplingParams(temperature=0.8, max_tokens=n, seed=7 + i, ignore_eos=eos is None) for i, n in enumerate(lens)]
+        ids = [llm.add_request(p, sp) for p, sp in zip(prompts, sps)]
+        done, steps = {}, 0
+        while not llm.is_finished():
+            out, _, _, _ = llm.step()
+            steps += 1
+            if late is not None and steps == late:
+                ids.append(llm.add_request(prompts[0][::-1], SamplingParams(temperature=0, max_tokens=7)))
+            done.update(dict(out))
+        llm.cache.check([])
+        return [done[i] for i in ids], llm
+
+    plain, llm0 = run(False)
+    ahead, llm1 = run(True)
+    assert ahead == plain
+    assert llm0.steps_ahead_used == 0 and llm1.steps_ahead_used > 5
+    # an end-of-sequence token taken from the middle of a completion: requests now end where the host cannot foresee it
+    eos = plain[2][6]
+    plain_eos, _ = run(False, eos=eos)
+    ahead_eos, llm2 = run(True, eos=eos)
+    assert ahead_eos == plain_eos and any(len(a) < n for a, n in zip(plain_eos, lens))
+    # a request that arrives in the middle: the scheduler then wants a different step than the one guessed
+    plain_late, _ = run(False, late=6)
+    ahead_late, _ = run(True, late=6)
+    assert ahead_late == plain_late and len(ahead_late) == 6
+    # a request alone that ends on its end-of-sequence token: the step guessed behind its last one is dropped
+    llm = _llm(name, dtype)
+    llm.scheduler.eos = eos
+    out = llm.generate([prompts[2]], SamplingParams(temperature=0.8, max_tokens=lens[2], seed=9), use_tqdm=False)
+    assert out[0]["token_ids"] == plain_eos[2] and llm.steps_ahead_dropped == 1
