@@ -87,8 +87,9 @@ def test_parts_alone(name, dtype):
 # ---- a toy architecture defined here -------------------------------------------------------------
 def _register_toy():
     from mini_engine_b200.config import Architecture, ModelConfig, register_architecture
-    from mini_engine_b200.parts import (BlockSpec, LayerCall, Linear, Mixer, ModelPlan, PartSpec, SharedRef, StateNeed,
-                                        register_mixer)
+    from mini_engine_b200.parts import (BlockSpec, FeedForward, LayerCall, Linear, Mixer, ModelPlan, PartSpec, PositionEncoding,
+                                        SharedRef, StateNeed, register_feed_forward, register_mixer,
+                                        register_position_encoding)
 
     class RunningMean(Mixer):
         """out[t] = mean over the request's tokens 0..t of proj(x): its state (a sum and a count) has a
@@ -121,6 +122,49 @@ def _register_toy():
                 t += n
             return out.to(ctx.act_dtype)
 
+    class SoftExperts(FeedForward):
+        """A feed-forward with routing: a router (float32 logits, softmax) weighs the outputs of small experts,
+        ``sum_e p_e * down_e(silu(up_e(x)))``.  All experts run and the weights are soft, so the result is a
+        continuous function of the input and can be compared with a plain implementation at a tolerance."""
+        capturable = True
+
+        def __init__(self, hidden_size, expert_size, num_experts):
+            super().__init__()
+            self.h, self.e = hidden_size, num_experts
+            self.router = Linear(hidden_size, [("router.weight", num_experts)], name="router.weight")
+            self.ups = [Linear(hidden_size, [(f"experts.{i}.up.weight", expert_size)], name=f"experts.{i}.up.weight")
+                        for i in range(num_experts)]
+            self.downs = [Linear(expert_size, [(f"experts.{i}.down.weight", hidden_size)], name=f"experts.{i}.down.weight")
+                          for i in range(num_experts)]
+
+        def sub_parts(self):
+            return [("", self.router)] + [("", p) for p in self.ups + self.downs]
+
+        def forward(self, x, ctx):
+            logits = self.router.forward(x, ctx, "toy_router", out_dtype=torch.float32)
+            probs = torch.softmax(logits.float(), dim=-1)
+            out = torch.zeros(x.shape[0], self.h, dtype=torch.float32, device=x.device)
+            for i in range(self.e):
+                hid = self.ups[i].forward(x, ctx, f"toy_up{i}")
+                act = torch.nn.functional.silu(hid.float()).to(ctx.act_dtype)
+                out += probs[:, i:i + 1] * self.downs[i].forward(act, ctx, f"toy_down{i}").float()
+            return out.to(ctx.act_dtype)
+
+    class InterpolatedRotary(PositionEncoding):
+        """Another position encoding: rotary angles of position / factor (the table is all the attention mixer asks for)."""
+        capturable = True
+
+        def __init__(self, rotary_dim, max_position, theta, factor):
+            super().__init__()
+            self.rotary_dim, self.max_position, self.theta, self.factor = rotary_dim, max_position, float(theta), float(factor)
+            self.cos_sin = None
+
+        def finalize(self, dtype, device):
+            d = self.rotary_dim
+            inv_freq = 1.0 / (self.theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+            ang = torch.outer(torch.arange(self.max_position, dtype=torch.float32) / self.factor, inv_freq)
+            self.cos_sin = torch.cat((ang.cos(), ang.sin()), dim=-1).contiguous().to(device)
+
     @dataclass
     class ToyConfig(ModelConfig):
         num_attention_heads: int = 0
@@ -147,16 +191,23 @@ def _register_toy():
         toy = PartSpec("toy_running_mean", {"hidden_size": cfg.hidden_size})
         blocks = [BlockSpec(mixer=toy if i % 2 else attn, feed_forward=ffn, norm=norm)
                   for i in range(cfg.num_hidden_layers)]
-        if cfg.pattern == "state":           # attention, running mean, attention, running mean
+        rope = PartSpec("rope", {"rotary_dim": cfg.head_dim, "max_position": cfg.max_position_embeddings, "theta": cfg.rope_theta})
+        if cfg.pattern == "routed":          # attention everywhere with the other position encoding; every second feed-forward routed
+            experts = PartSpec("toy_soft_experts", {"hidden_size": cfg.hidden_size, "expert_size": 24, "num_experts": 3})
+            blocks = [BlockSpec(mixer=attn, feed_forward=experts if i % 2 else ffn, norm=norm) for i in range(cfg.num_hidden_layers)]
+            rope = PartSpec("toy_interpolated_rope", dict(rope.args, factor=2.5))
+            schedule = [LayerCall(i, i) for i in range(cfg.num_hidden_layers)]
+        elif cfg.pattern == "state":         # attention, running mean, attention, running mean
             schedule = [LayerCall(i, i) for i in range(cfg.num_hidden_layers)]
         else:                                # "twice": layer 0, layer 2, layer 0 again (own cache), layer 2 reading call 1's cache
             schedule = [LayerCall(0, 0), LayerCall(2, 1), LayerCall(0, 2), LayerCall(2, 1, writes_cache=False)]
         return ModelPlan(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, blocks=blocks, schedule=schedule,
                          final_norm=norm, tie_word_embeddings=False, max_position=cfg.max_position_embeddings,
-                         shared={"rope": PartSpec("rope", {"rotary_dim": cfg.head_dim, "max_position": cfg.max_position_embeddings,
-                                                           "theta": cfg.rope_theta})})
+                         shared={"rope": rope})
 
     register_mixer("toy_running_mean", RunningMean, replace=True)
+    register_feed_forward("toy_soft_experts", SoftExperts, replace=True)
+    register_position_encoding("toy_interpolated_rope", InterpolatedRotary, replace=True)
     register_architecture(Architecture("ToyStateLM", ToyConfig.from_dict, plan), replace=True)
 
 
@@ -170,6 +221,10 @@ def _toy_plain(cfg, w, ids):
     ids = torch.as_tensor(ids)
     T = len(ids)
     cos, sin = plain_model.rope_tables(cfg["head_dim"], T, cfg["rope_theta"], torch.float64)
+    if cfg["pattern"] == "routed":
+        inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, cfg["head_dim"], 2, dtype=torch.float64) / cfg["head_dim"]))
+        ang = torch.outer(torch.arange(T, dtype=torch.float64) / 2.5, inv)
+        cos, sin = torch.cat((ang.cos(), ang.cos()), -1), torch.cat((ang.sin(), ang.sin()), -1)
     r = w["model.embed_tokens.weight"][ids]
     eps = cfg["rms_norm_eps"]
 
@@ -188,7 +243,12 @@ def _toy_plain(cfg, w, ids):
         y = x @ w[p + "proj.weight"].T
         return torch.cumsum(y, 0) / torch.arange(1, T + 1)[:, None]
 
-    if cfg["pattern"] == "state":
+    def soft_experts(x, p):
+        probs = torch.softmax(x @ w[p + "router.weight"].T, dim=-1)
+        return sum(probs[:, i:i + 1] * (torch.nn.functional.silu(x @ w[p + f"experts.{i}.up.weight"].T) @ w[p + f"experts.{i}.down.weight"].T)
+                   for i in range(3))
+
+    if cfg["pattern"] in ("state", "routed"):
         calls = [(i, None) for i in range(cfg["num_hidden_layers"])]
     else:
         calls = [(0, None), (2, "write"), (0, None), (2, "read")]
@@ -196,7 +256,7 @@ def _toy_plain(cfg, w, ids):
     for layer, mode in calls:
         p = f"model.layers.{layer}."
         x = plain_model.rms_norm(r, w[p + "input_layernorm.weight"], eps)
-        if layer % 2:
+        if layer % 2 and cfg["pattern"] != "routed":
             m = mean_mixer(x, p + "self_attn.")
         else:
             m, kv = attn(x, p + "self_attn.", saved if mode == "read" else None)
@@ -204,13 +264,16 @@ def _toy_plain(cfg, w, ids):
                 saved = kv
         r = r + m
         x = plain_model.rms_norm(r, w[p + "post_attention_layernorm.weight"], eps)
-        r = r + plain_model.swiglu(x, w, p + "mlp.")
+        r = r + (soft_experts(x, p + "mlp.") if cfg["pattern"] == "routed" and layer % 2 else plain_model.swiglu(x, w, p + "mlp."))
     return (plain_model.rms_norm(r, w["model.norm.weight"], eps) @ w["lm_head.weight"].T).numpy()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("pattern", ["state", "twice"])
+@pytest.mark.parametrize("pattern", ["state", "twice", "routed"])
 def test_toy_architecture_is_registered_built_and_stepped(pattern, dtype):
+    """Parts defined here, in the test (a mixer with state of its own, a feed-forward with routing, another position
+    encoding) and orders of layers that name a layer twice or share a cache are registered, built from a model
+    folder and stepped through the engine's replay without a change to the package."""
     _register_toy()
     from mini_engine_b200.engine.replay import TraceReplayer
     from mini_engine_b200.weights import write_random_model
@@ -223,8 +286,10 @@ def test_toy_architecture_is_registered_built_and_stepped(pattern, dtype):
     rp = TraceReplayer(folder, dtype, helpers.max_live_tokens(steps), page_size=16)
     if pattern == "state":
         assert rp.runner.state_needs and rp.cache.state_slots.num_slots > 0 and not rp.cache.prefix_caching
-    else:
+    elif pattern == "twice":
         assert len(rp.runner.model.slot_needs) == 3           # three cache slots for four calls
+    else:
+        assert rp.runner.use_cuda_graphs == (rp.runner.device.type == "cuda")     # these toy parts may be captured
     got = helpers.collect(steps, [rp.run_step(st) for st in steps])
     rp.cache.check([])
     tol = helpers.TOL[dtype]
