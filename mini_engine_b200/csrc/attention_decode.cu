@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "mma_prims.cuh"
 #include "tma.cuh"
+#include "tcgen05.cuh"
 
 constexpr int DEC_PART = 128, DEC_THREADS = 128, DEC_LANES = 8, DEC_GROUPS = DEC_THREADS / DEC_LANES;
 
@@ -658,7 +659,12 @@ struct DecodePrep {
   bf16* pool;                 // the cache slot, [page][k|v][kv_head][offset][HD]
 };
 
-template <int HD, bool FUSED>
+// TC5: the two products run on the 5th-generation tensor cores.  The partition's 128 keys are the M side:
+// S^T [keys][16 heads] = K Q^T (eight tcgen05.mma of K 16, operands straight from the tiles the copy engine
+// wrote, accumulator in tensor memory); a thread then owns a key (tcgen05.ld), the softmax runs across threads,
+// P^T goes to shared memory as a K-major operand, and O^T [head_dim][16 heads] = V^T P^T takes V as an MN-major
+// operand, so that a thread ends up owning an output column.  Without TC5: mma.sync m16n8k16 with ldmatrix.
+template <int HD, bool FUSED, bool TC5>
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ qkv,
                                 int64_t q_row_stride, const int* __restrict__ block_tables, int bt_stride,
@@ -669,7 +675,8 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   using namespace mma_prims;
   extern __shared__ unsigned char dec_smem_raw[];
   __shared__ float w_m[4][16], w_l[4][16];
-  __shared__ __align__(8) unsigned long long bar_k, bar_v;
+  __shared__ __align__(8) unsigned long long bar_k, bar_v, bar_s, bar_o;
+  __shared__ uint32_t tmem_slot;
   constexpr int PIECES = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, HALVES = HD / 64;
   const int G = nh / nkv, head_tiles = (G + 15) / 16;
   const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * 16;
@@ -703,6 +710,11 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   bf16* ks = reinterpret_cast<bf16*>(aligned);
   bf16* vs = ks + DEC_PART * HD;
   bf16* qs = vs + DEC_PART * HD;
+  // Element i of row ``row`` of the Q tile: for mma.sync a [16][HD] tile with XOR-swizzled pieces, for tcgen05 a
+  // K-major operand as the copy engine would have written it (blocks of [16 rows][64], 128-byte swizzle).
+  auto q_at = [&](int row, int i) -> bf16* {
+    return TC5 ? tma::swz128(qs + (i >> 6) * 16 * 64, row, (i & 63) >> 3) + (i & 7) : tile_ptr<HD>(qs, row, i >> 3) + (i & 7);
+  };
   const int64_t tok = cu_seqlens[b];
   // Only the partition that holds the request's newest key depends on the kernel before this one (which
   // wrote that key); the others fetch their keys and values while that kernel is still running.  A block
@@ -718,8 +730,13 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   if (tid == 0) {
     tma::mbar_init(&bar_k, 1);
     tma::mbar_init(&bar_v, 1);
+    if (TC5) {
+      tma::mbar_init(&bar_s, 1);
+      tma::mbar_init(&bar_o, 1);
+    }
     tma::mbar_fence_init();
   }
+  if (TC5 && warp == 1) tc5::tmem_alloc(&tmem_slot, 32);          // S^T in columns 0..15, O^T in 16..31
   if (warp == 0) {
     // A tensor-map copy is issued per thread, so the lanes of one warp issue the partition's boxes together:
     // lane i looks up page i, lane 0 announces the bytes, then box x = ((k|v) * HALVES + half) * pages + page
@@ -784,8 +801,8 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       const int i0 = lane * VEC;
 #pragma unroll
       for (int j = 0; j < VEC; ++j) {
-        tile_ptr<HD>(qs, row, (i0 + j) >> 3)[(i0 + j) & 7] = ra[j];
-        tile_ptr<HD>(qs, row, (HD / 2 + i0 + j) >> 3)[(HD / 2 + i0 + j) & 7] = rb[j];
+        *q_at(row, i0 + j) = ra[j];
+        *q_at(row, HD / 2 + i0 + j) = rb[j];
       }
     }
     if (makes_new) {
@@ -805,13 +822,18 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     for (int c = tid; c < 16 * PIECES; c += DEC_THREADS) {     // q is written by the kernel before this one
       const int row = c / PIECES, piece = c % PIECES;
       const bool ok = row < n_g;
-      cp_async16(tile_ptr<HD>(qs, row, piece),
+      cp_async16(q_at(row, piece * 8),
                  ok ? qkv + tok * q_row_stride + (int64_t)(kvh * G + g0 + row) * HD + piece * 8 : qkv, ok);
     }
     cp_async_commit();
     cp_async_wait<0>();
   }
-  __syncthreads();                                   // barriers initialised, Q in place
+  if (TC5) {
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // Q, written by threads, is read by the tensor core
+    tc5::fence_before_sync();
+  }
+  __syncthreads();                                   // barriers initialised, Q in place, tensor memory allocated
+  if (TC5) tc5::fence_after_sync();
   bool landed = tma::mbar_wait(&bar_k, 0);
   // The newest key and value go to their row of the tiles (over whatever the slot held) and to the cache.
   auto put_new = [&](bf16* tile, int kv) {
@@ -834,10 +856,93 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     }
   };
   if (makes_new) {
-    if (warp == 0) put_new(ks, 0);
+    if (warp == 0) {
+      put_new(ks, 0);
+      if (TC5) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
     __syncthreads();                                 // the row is in place before any warp reads K
   }
   const float sl2 = scale * 1.4426950408889634f;
+  if (TC5) {
+    const uint32_t tmem = tmem_slot;
+    // ---- S^T = K Q^T: one thread issues, the accumulator's lanes are the keys
+    if (tid == 0) {
+      constexpr uint32_t idesc = tc5::instr_desc_bf16(DEC_PART, 16);
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const uint64_t a = tc5::smem_desc_k_major_sw128(ks + (kk >> 2) * DEC_PART * 64) + 2 * (kk & 3);
+        const uint64_t bq = tc5::smem_desc_k_major_sw128(qs + (kk >> 2) * 16 * 64) + 2 * (kk & 3);
+        tc5::mma_f16(tmem, a, bq, idesc, kk > 0);
+      }
+      tc5::commit(&bar_s);
+    }
+    landed = tma::mbar_wait(&bar_s, 0) && landed;
+    tc5::fence_after_sync();
+    float sc[16];
+    tc5::ld_16cols(tmem + ((uint32_t)(warp * 32) << 16), sc);
+    tc5::wait_ld();
+    const int j = part_lo + tid;                     // this thread's key
+    const bool live = j < part_hi && j >= lo_w;
+    // the maximum of every head over the 128 keys: lanes, then warps
+#pragma unroll
+    for (int h = 0; h < 16; ++h) {
+      if (h >= n_g) break;
+      const float mx = warp_max(live ? sc[h] : -INFINITY);
+      if (lane == 0) w_m[warp][h] = mx;
+    }
+    __syncthreads();                                 // (every thread has read its scores: Q may be overwritten by P)
+    bf16* ps = qs;                                   // P^T [16 heads][128 keys] as a K-major operand: two blocks of [16][64]
+#pragma unroll
+    for (int h = 0; h < 16; ++h) {
+      if (h >= n_g) break;
+      const float M = fmaxf(fmaxf(w_m[0][h], w_m[1][h]), fmaxf(w_m[2][h], w_m[3][h]));
+      const float p = live ? exp2f((sc[h] - (M == -INFINITY ? 0.f : M)) * sl2) : 0.f;
+      const float sum = warp_sum(p);
+      if (lane == 0) w_l[warp][h] = sum;
+      *(tma::swz128(ps + (tid >> 6) * 16 * 64, h, (tid & 63) >> 3) + (tid & 7)) = __float2bfloat16_rn(p);
+    }
+    landed = tma::mbar_wait(&bar_v, 0) && landed;
+    if (makes_new && warp == 1) put_new(vs, 1);
+    if (!live)                                       // rows of V that are no keys of this request: zero (0 * NaN is NaN)
+      for (int p = 0; p < PIECES; ++p)
+        *reinterpret_cast<uint4*>(tma::swz128(vs + (p >> 3) * DEC_PART * 64, tid, p & 7)) = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P and the touched rows of V, for the tensor core
+    tc5::fence_before_sync();
+    __syncthreads();
+    tc5::fence_after_sync();
+    // ---- O^T = V^T P^T: V is the MN-major operand (head_dim is M), the accumulator's lanes are output columns
+    if (tid == 0) {
+      static_assert(!TC5 || HD == 128, "the tcgen05 form needs head_dim 128 (an accumulator of 128 lanes)");
+      constexpr uint32_t idesc = tc5::instr_desc_bf16(128, 16, false, true);
+#pragma unroll
+      for (int kk = 0; kk < DEC_PART / 16; ++kk) {
+        const uint64_t a = tc5::smem_desc_mn_major_sw128(reinterpret_cast<unsigned char*>(vs) + kk * 2048, DEC_PART * 64 * 2);
+        const uint64_t bp = tc5::smem_desc_k_major_sw128(ps + (kk >> 2) * 16 * 64) + 2 * (kk & 3);
+        tc5::mma_f16(tmem + 16, a, bp, idesc, kk > 0);
+      }
+      tc5::commit(&bar_o);
+    }
+    landed = tma::mbar_wait(&bar_o, 0) && landed;
+    tc5::fence_after_sync();
+    {
+      float oc[16];
+      tc5::ld_16cols(tmem + 16 + ((uint32_t)(warp * 32) << 16), oc);
+      tc5::wait_ld();
+#pragma unroll
+      for (int h = 0; h < 16; ++h)
+        if (h < n_g) tmp_out[(slot0 + (int64_t)h * max_parts) * HD + tid] = oc[h];
+    }
+    if (tid < n_g) {
+      const float M = fmaxf(fmaxf(w_m[0][tid], w_m[1][tid]), fmaxf(w_m[2][tid], w_m[3][tid]));
+      tmp_m[slot0 + (int64_t)tid * max_parts] = M == -INFINITY ? -INFINITY : M * scale;
+      tmp_l[slot0 + (int64_t)tid * max_parts] = ((w_l[0][tid] + w_l[1][tid]) + w_l[2][tid]) + w_l[3][tid];
+    }
+    if (!landed && tid == 0) atomicOr(err + 1, 1);
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tc5::tmem_dealloc(tmem, 32);
+    return;
+  }
   const int mi = lane >> 3;
   float s[4][4];
 #pragma unroll
@@ -947,7 +1052,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   }
 }
 
-template <int HD, bool FUSED>
+template <int HD, bool FUSED, bool TC5>
 static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_parts, cudaStream_t stream, const void* qkv,
                                     int64_t q_row_stride, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
                                     int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int* err,
@@ -955,13 +1060,13 @@ static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_pa
   const size_t smem = (size_t)(16 + 2 * DEC_PART) * HD * sizeof(bf16) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, TC5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   const int G = nh / nkv;
   dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
-  me_launch(decode_partition_tma_mma_kernel<HD, FUSED>, grid, dim3(DEC_THREADS), smem, stream,
+  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, TC5>, grid, dim3(DEC_THREADS), smem, stream,
       *reinterpret_cast<const CUtensorMap*>(kv_map), (const bf16*)qkv, q_row_stride, bt, bt_stride, cu, cl, nh, nkv, page_size,
       scale, window, to, tm, tl, max_parts, err, prep);
   return 0;
@@ -1082,9 +1187,9 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   const bool tma = kind == 2;
   if (tma_mma) {
     const DecodePrep none = {};
-    int rc = hd == 64 ? launch_partition_tma_mma<64, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+    int rc = hd == 64 ? launch_partition_tma_mma<64, false, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none)
-                      : launch_partition_tma_mma<128, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                      : launch_partition_tma_mma<128, false, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                              cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none);
     if (rc) return rc;
   }
@@ -1136,13 +1241,14 @@ ME_API int me_attn_decode_fused_takes(int hd, int page_size) {
 // whole step) happen inside the partition kernel, for requests [0, num_reqs) that bring one token each
 // (token row = cu_seqlens[request], position = context_lens[request] - 1).  q_weight/k_weight (both or neither), cos_sin and slot_mapping may be
 // null; with a null slot_mapping the newest key and value are expected in the cache already.  The q rows of
-// ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.
+// ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.  tcgen05: 1 runs the two products
+// of a partition on the 5th-generation tensor cores (head_dim 128), 0 on mma.sync.
 ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out, int64_t out_row_stride, void* pool,
                                 const void* kv_map, const int* block_tables, int bt_stride, const int* cu_seqlens,
                                 const int* context_lens, int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
                                 int window, const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
-                                const int* slot_mapping, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts, int* err,
-                                cudaStream_t stream) {
+                                const int* slot_mapping, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts, int tcgen05,
+                                int* err, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   ME_REQUIRE(me_attn_decode_fused_takes(hd, page_size), "me_attn_decode_fused: head_dim %d with pages of %d is not taken", hd, page_size);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "me_attn_decode_fused: %d heads, %d kv heads", nh, nkv);
@@ -1153,10 +1259,16 @@ ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out
   const int G = nh / nkv;
   ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode_fused: too many heads");
   DecodePrep prep = {q_weight, k_weight, eps, cos_sin, slot_mapping, (bf16*)pool};
-  int rc = hd == 64 ? launch_partition_tma_mma<64, true>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
-                                                         cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, prep)
-                    : launch_partition_tma_mma<128, true>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
-                                                          cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, prep);
+  ME_REQUIRE(!tcgen05 || hd == 128, "me_attn_decode_fused: the tcgen05 form takes head_dim 128");
+  int rc = 1;
+#define ME_FUSED(HD_, TC_)                                                                                               \
+  rc = launch_partition_tma_mma<HD_, true, TC_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride, \
+                                                cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, \
+                                                err, prep)
+  if (hd == 64) ME_FUSED(64, false);
+  else if (tcgen05) ME_FUSED(128, true);
+  else ME_FUSED(128, false);
+#undef ME_FUSED
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_attn_decode_fused (partitions)");
   dim3 mgrid(num_reqs, nh);

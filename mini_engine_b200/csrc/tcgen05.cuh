@@ -52,11 +52,12 @@ __device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(const void* tile, u
   d |= (uint64_t)2 << 61;
   return d;
 }
-// Instruction descriptor of kind::f16: bfloat16 A and B, float32 D, M x N, A K-major; B K-major or MN-major.
-__host__ __device__ constexpr uint32_t instr_desc_bf16(int M, int N, bool b_mn_major = false) {
+// Instruction descriptor of kind::f16: bfloat16 A and B, float32 D, M x N; A and B each K-major or MN-major.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int M, int N, bool b_mn_major = false, bool a_mn_major = false) {
   return (1u << 4)                      // D format: float32
          | (1u << 7)                    // A format: bfloat16
          | (1u << 10)                   // B format: bfloat16
+         | ((a_mn_major ? 1u : 0u) << 15)
          | ((b_mn_major ? 1u : 0u) << 16)
          | ((uint32_t)(N >> 3) << 17)   // N / 8
          | ((uint32_t)(M >> 4) << 24);  // M / 16
@@ -83,6 +84,16 @@ __device__ __forceinline__ void ld_32cols(uint32_t taddr, float (&v)[32]) {
         "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
         "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// 16 consecutive float32 columns of this thread's lane.
+__device__ __forceinline__ void ld_16cols(uint32_t taddr, float (&v)[16]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
