@@ -664,7 +664,10 @@ struct DecodePrep {
 // wrote, accumulator in tensor memory); a thread then owns a key (tcgen05.ld), the softmax runs across threads,
 // P^T goes to shared memory as a K-major operand, and O^T [head_dim][16 heads] = V^T P^T takes V as an MN-major
 // operand, so that a thread ends up owning an output column.  Without TC5: mma.sync m16n8k16 with ldmatrix.
-template <int HD, bool FUSED, bool TC5>
+// ONE (mma.sync form only): K and V pass through the same tile, V requested once every warp has its scores: half the
+// shared memory a block, so that five blocks share an SM instead of three.  A block then lives one load longer, but
+// more of them are loading at any time, and a batch of 8 at 1,000 tokens fits the GPU in one wave.
+template <int HD, bool FUSED, bool TC5, bool ONE>
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ qkv,
                                 int64_t q_row_stride, const int* __restrict__ block_tables, int bt_stride,
@@ -708,7 +711,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   // Shared memory from a 1024-byte boundary: K halves [HALVES][128][64], V halves, then Q [16][HD].
   unsigned char* aligned = dec_smem_raw + ((1024u - (tma::smem_addr(dec_smem_raw) & 1023u)) & 1023u);
   bf16* ks = reinterpret_cast<bf16*>(aligned);
-  bf16* vs = ks + DEC_PART * HD;
+  bf16* vs = ONE ? ks : ks + DEC_PART * HD;
   bf16* qs = vs + DEC_PART * HD;
   // Element i of row ``row`` of the Q tile: for mma.sync a [16][HD] tile with XOR-swizzled pieces, for tcgen05 a
   // K-major operand as the copy engine would have written it (blocks of [16 rows][64], 128-byte swizzle).
@@ -737,23 +740,23 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     tma::mbar_fence_init();
   }
   if (TC5 && warp == 1) tc5::tmem_alloc(&tmem_slot, 32);          // S^T in columns 0..15, O^T in 16..31
-  if (warp == 0) {
-    // A tensor-map copy is issued per thread, so the lanes of one warp issue the partition's boxes together:
-    // lane i looks up page i, lane 0 announces the bytes, then box x = ((k|v) * HALVES + half) * pages + page
-    // goes out from lane x % 32.
-    const int n_pages = DEC_PART / page_size;
+  // A tensor-map copy is issued per thread, so the lanes of one warp issue the partition's boxes together: lane i
+  // looks up page i, lane 0 announces the bytes, then box x = ((k|v) * HALVES + half) * pages + page goes out from
+  // lane x % 32.
+  int first_row = -1;                                  // warp 0: row of the pool's 2-D view where this lane's page keeps K
+  const int n_pages = DEC_PART / page_size;
+  if (warp == 0 && lane < n_pages) {
+    const int j0 = part_lo + lane * page_size;
+    const int page = (j0 < part_hi && j0 + page_size > lo_w) ? page_ahead : -1;
+    if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size;
+  }
+  auto request = [&](bool want_k, bool want_v) {       // warp 0
     const unsigned box_bytes = (unsigned)page_size * 64 * sizeof(bf16);
-    int first_row = -1;                                // row of the pool's 2-D view where this lane's page keeps K
-    if (lane < n_pages) {
-      const int j0 = part_lo + lane * page_size;
-      const int page = (j0 < part_hi && j0 + page_size > lo_w) ? page_ahead : -1;
-      if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size;
-    }
     const unsigned present = __ballot_sync(0xffffffffu, first_row >= 0);
     if (lane == 0) {
       const unsigned bytes = (unsigned)__popc(present) * HALVES * box_bytes;
-      tma::mbar_expect_tx(&bar_k, bytes);
-      tma::mbar_expect_tx(&bar_v, bytes);
+      if (want_k) tma::mbar_expect_tx(&bar_k, bytes);
+      if (want_v) tma::mbar_expect_tx(&bar_v, bytes);
     }
     __syncwarp();
     const int v_rows = nkv * page_size;
@@ -761,11 +764,12 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       const int x = x0 + lane;
       const int i = x % n_pages, h = (x / n_pages) % HALVES, v = x / (n_pages * HALVES);
       const int row = __shfl_sync(0xffffffffu, first_row, i);
-      if (x < 2 * HALVES * n_pages && row >= 0)
+      if (x < 2 * HALVES * n_pages && row >= 0 && (v ? want_v : want_k))
         tma::load_2d((v ? vs : ks) + h * DEC_PART * 64 + i * page_size * 64, &kv_map, h * 64, row + v * v_rows,
                      v ? &bar_v : &bar_k);
     }
-  }
+  };
+  if (warp == 0) request(true, !ONE);
   constexpr int VEC = HD / 64;
   // what the preparation of q and of the newest key needs besides the rows themselves is no kernel's output:
   // read it while the kernel before this one is still running
@@ -960,6 +964,13 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       mma_bf16(s[2 * np + 1], qf, bfr[2], bfr[3]);
     }
   }
+  if (ONE) {
+    __syncthreads();                                 // every warp has its scores: the tile is free for V
+    if (warp == 0) {
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // (the newest key's row was written by threads)
+      request(false, true);
+    }
+  }
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -1014,6 +1025,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       mma_bf16(o[2 * np + 1], pf[kk], bfr[2], bfr[3]);
     }
   }
+  if (ONE) __syncthreads();                          // every warp is done reading V: the tile now takes the warps' results
   float* po = reinterpret_cast<float*>(ks);          // [4][16][HD] float32, over the K tile
   if (t4 == 0) {
     w_m[warp][g] = mx0;
@@ -1052,21 +1064,21 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   }
 }
 
-template <int HD, bool FUSED, bool TC5>
+template <int HD, bool FUSED, bool TC5, bool ONE>
 static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_parts, cudaStream_t stream, const void* qkv,
                                     int64_t q_row_stride, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
                                     int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int* err,
                                     const DecodePrep& prep) {
-  const size_t smem = (size_t)(16 + 2 * DEC_PART) * HD * sizeof(bf16) + 1024;
+  const size_t smem = (size_t)(16 + (ONE ? 1 : 2) * DEC_PART) * HD * sizeof(bf16) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, TC5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, TC5, ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   const int G = nh / nkv;
   dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
-  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, TC5>, grid, dim3(DEC_THREADS), smem, stream,
+  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, TC5, ONE>, grid, dim3(DEC_THREADS), smem, stream,
       *reinterpret_cast<const CUtensorMap*>(kv_map), (const bf16*)qkv, q_row_stride, bt, bt_stride, cu, cl, nh, nkv, page_size,
       scale, window, to, tm, tl, max_parts, err, prep);
   return 0;
@@ -1187,9 +1199,9 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   const bool tma = kind == 2;
   if (tma_mma) {
     const DecodePrep none = {};
-    int rc = hd == 64 ? launch_partition_tma_mma<64, false, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+    int rc = hd == 64 ? launch_partition_tma_mma<64, false, false, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none)
-                      : launch_partition_tma_mma<128, false, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                      : launch_partition_tma_mma<128, false, false, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                              cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none);
     if (rc) return rc;
   }
@@ -1241,8 +1253,8 @@ ME_API int me_attn_decode_fused_takes(int hd, int page_size) {
 // whole step) happen inside the partition kernel, for requests [0, num_reqs) that bring one token each
 // (token row = cu_seqlens[request], position = context_lens[request] - 1).  q_weight/k_weight (both or neither), cos_sin and slot_mapping may be
 // null; with a null slot_mapping the newest key and value are expected in the cache already.  The q rows of
-// ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.  tcgen05: 1 runs the two products
-// of a partition on the 5th-generation tensor cores (head_dim 128), 0 on mma.sync.
+// ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.  tcgen05 (the form of the partition
+// kernel): 0 mma.sync with K and V through one tile, 1 tcgen05 (head_dim 128), 2 mma.sync with a tile each.
 ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out, int64_t out_row_stride, void* pool,
                                 const void* kv_map, const int* block_tables, int bt_stride, const int* cu_seqlens,
                                 const int* context_lens, int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
@@ -1259,15 +1271,17 @@ ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out
   const int G = nh / nkv;
   ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode_fused: too many heads");
   DecodePrep prep = {q_weight, k_weight, eps, cos_sin, slot_mapping, (bf16*)pool};
-  ME_REQUIRE(!tcgen05 || hd == 128, "me_attn_decode_fused: the tcgen05 form takes head_dim 128");
+  ME_REQUIRE(tcgen05 != 1 || hd == 128, "me_attn_decode_fused: the tcgen05 form takes head_dim 128");
   int rc = 1;
-#define ME_FUSED(HD_, TC_)                                                                                               \
-  rc = launch_partition_tma_mma<HD_, true, TC_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride, \
+#define ME_FUSED(HD_, TC_, ONE_)                                                                                         \
+  rc = launch_partition_tma_mma<HD_, true, TC_, ONE_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride, \
                                                 cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, \
                                                 err, prep)
-  if (hd == 64) ME_FUSED(64, false);
-  else if (tcgen05) ME_FUSED(128, true);
-  else ME_FUSED(128, false);
+  if (tcgen05 == 1) ME_FUSED(128, true, false);
+  else if (hd == 64 && tcgen05 == 2) ME_FUSED(64, false, false);
+  else if (hd == 64) ME_FUSED(64, false, true);
+  else if (tcgen05 == 2) ME_FUSED(128, false, false);
+  else ME_FUSED(128, false, true);
 #undef ME_FUSED
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_attn_decode_fused (partitions)");

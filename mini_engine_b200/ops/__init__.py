@@ -503,22 +503,29 @@ def decode_fused_takes(qkv: torch.Tensor, head_dim: int, pool: torch.Tensor, pag
             and kv_tensor_map(pool, page_size) is not None)
 
 
-# The decode partitions' two products on tcgen05 instead of mma.sync.  Off: measured slower (batch 8: 1.02 against
-# 0.97 ms a step, batch 256: 9.8 against 8.9): an accumulator in tensor memory costs a partition two round trips
-# through commit, mbarrier and tcgen05.ld for 16 instructions' worth of arithmetic.  Kept as a tested alternative.
-use_tcgen05_decode = False
+# The form of the decode partition kernel: "one_tile" (mma.sync; K and V pass through the same shared-memory tile,
+# five blocks an SM), "two_tiles" (mma.sync; a tile each, three blocks an SM) or "tcgen05" (the two products on the
+# 5th-generation tensor cores, head size 128 only; measured slower than mma.sync: an accumulator in tensor memory
+# costs a partition two round trips through commit, mbarrier and tcgen05.ld for 16 instructions' worth of arithmetic).
+DECODE_FORMS = {"one_tile": 0, "tcgen05": 1, "two_tiles": 2}
+decode_form = "auto"          # two tiles while all partitions are resident at once (the loads of K and V overlap: batch 1,
+                              # 0.78 against 0.80 ms), one tile beyond (batch 64: 2.65 against 2.87 ms, batch 256: 7.8 against 8.7)
+DECODE_RESIDENT_TWO_TILES = 3 * 148
 
 
 def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window,
-                           q_weight, k_weight, eps, cos_sin, slot_mapping, tcgen05: Optional[bool] = None) -> None:
+                           q_weight, k_weight, eps, cos_sin, slot_mapping, form: Optional[str] = None) -> None:
     """Decode attention over requests [0, meta.num_decodes) straight from the q|k|v product's rows: the kernel
     applies the q/k norm and the rotary embedding to q and to the newest key itself and writes that key and the
     newest value into the cache (``slot_mapping``; None if another layer wrote them), so the step needs no
     ``qk_norm_rope_kv_write`` for these rows.  The token's position is its request's context length minus one.
-    Other arguments as for that function and ``attention_decode``.  ``tcgen05``: the partitions' two products on
-    the 5th-generation tensor cores (head size 128 only; default ``use_tcgen05_decode``) or on mma.sync."""
-    if tcgen05 is None:
-        tcgen05 = use_tcgen05_decode and head_dim == 128
+    Other arguments as for that function and ``attention_decode``.  ``form``: one of ``DECODE_FORMS`` (default
+    ``decode_form``)."""
+    form = form or decode_form
+    if form == "auto":
+        blocks = meta.num_decodes * num_kv_heads * ((num_heads // num_kv_heads + 15) // 16) \
+            * ((meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
+        form = "two_tiles" if blocks <= DECODE_RESIDENT_TWO_TILES else "one_tile"
     D = meta.num_decodes
     parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
     room = max(parts, (getattr(meta, "scratch_context_len", 0) + DECODE_PARTITION - 1) // DECODE_PARTITION)
@@ -536,7 +543,7 @@ def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, pa
           block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), D,
           num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), _ptr(q_weight), _ptr(k_weight),
           float(eps), _ptr(cos_sin), _ptr(slot_mapping), tmp_out.data_ptr(), tmp_ml[0].data_ptr(),
-          tmp_ml[1].data_ptr(), parts, 1 if tcgen05 else 0, meta.error_flag.data_ptr(), _stream())
+          tmp_ml[1].data_ptr(), parts, DECODE_FORMS[form], meta.error_flag.data_ptr(), _stream())
     global launches
     launches += 1          # partition kernel + merge kernel
 

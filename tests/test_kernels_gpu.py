@@ -422,9 +422,9 @@ def test_attention_decode_kernels_by_name(ops, kind, nh, nkv, hd, page, window):
                                                   (40, 2, 64, 16), (16, 8, 128, 128)])
 @pytest.mark.parametrize("window", [None, 200])
 @pytest.mark.parametrize("norm, rope, writes", [(True, True, True), (False, True, True), (True, False, True), (True, True, False)])
-@pytest.mark.parametrize("tcgen05", [False, True])
-def test_attention_decode_that_prepares_q_and_the_newest_key_itself(ops, nh, nkv, hd, page, window, norm, rope, writes, tcgen05):
-    if tcgen05 and hd != 128:
+@pytest.mark.parametrize("form", ["one_tile", "two_tiles", "tcgen05"])
+def test_attention_decode_that_prepares_q_and_the_newest_key_itself(ops, nh, nkv, hd, page, window, norm, rope, writes, form):
+    if form == "tcgen05" and hd != 128:
         pytest.skip("the tcgen05 form takes head_dim 128")
     # the same batch through (norm, rotation, cache write) as a pass of its own followed by plain attention, and
     # through the decode kernel that does all of it; the newest slots of its cache start as NaN
@@ -457,7 +457,7 @@ def test_attention_decode_that_prepares_q_and_the_newest_key_itself(ops, nh, nkv
     out = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
     assert ops.decode_fused_takes(qkv, hd, pool, page, b.meta)
     ops.attention_decode_fused(qkv, out, *args, pool, page, b.bt, b.meta, hd ** -0.5, window, qw, kw, 1e-5, cs,
-                               slots if writes else None, tcgen05=tcgen05)
+                               slots if writes else None, form=form)
     assert not out.isnan().any() and b.meta.error_flag.tolist() == [0, 0, 0, 0]
     close(out, ref, torch.bfloat16)
     assert torch.equal(qkv, b.qkv)                   # the rows of the product are left alone
