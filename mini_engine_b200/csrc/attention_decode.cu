@@ -667,8 +667,10 @@ struct DecodePrep {
 // ONE (mma.sync form only): K and V pass through the same tile, V requested once every warp has its scores: half the
 // shared memory a block, so that five blocks share an SM instead of three.  A block then lives one load longer, but
 // more of them are loading at any time, and a batch of 8 at 1,000 tokens fits the GPU in one wave.
-template <int HD, bool FUSED, bool TC5, bool ONE>
-__global__ void __launch_bounds__(DEC_THREADS)
+// With ONE and at most 8 query heads a group the Q tile keeps 8 rows (the upper half of the m16 strip reads one
+// chunk of zeros) and the registers are held to what lets six blocks share an SM.
+template <int HD, bool FUSED, bool TC5, bool ONE, int QROWS>
+__global__ void __launch_bounds__(DEC_THREADS, (ONE && QROWS == 8) ? 6 : 1)
 decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ qkv,
                                 int64_t q_row_stride, const int* __restrict__ block_tables, int bt_stride,
                                 const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
@@ -680,6 +682,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   __shared__ float w_m[4][16], w_l[4][16];
   __shared__ __align__(8) unsigned long long bar_k, bar_v, bar_s, bar_o;
   __shared__ uint32_t tmem_slot;
+  __shared__ __align__(16) bf16 zero_chunk[8];
   constexpr int PIECES = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, HALVES = HD / 64;
   const int G = nh / nkv, head_tiles = (G + 15) / 16;
   const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * 16;
@@ -730,6 +733,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     pdl_wait();
     pdl_launch_dependents();
   }
+  if (tid < 8) zero_chunk[tid] = __float2bfloat16_rn(0.f);
   if (tid == 0) {
     tma::mbar_init(&bar_k, 1);
     tma::mbar_init(&bar_v, 1);
@@ -795,7 +799,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   bf16 new_a[VEC], new_b[VEC];                       // warp 0: the newest key; warp 1: the newest value (makes_new)
   if (FUSED) {
     // q as the product before left it: norm and rotation here, one warp per head, into the swizzled tile
-    for (int row = warp; row < 16; row += 4) {
+    for (int row = warp; row < QROWS; row += 4) {
       bf16 ra[VEC], rb[VEC];
 #pragma unroll
       for (int j = 0; j < VEC; ++j) ra[j] = rb[j] = __float2bfloat16_rn(0.f);
@@ -823,7 +827,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       }
     }
   } else {
-    for (int c = tid; c < 16 * PIECES; c += DEC_THREADS) {     // q is written by the kernel before this one
+    for (int c = tid; c < QROWS * PIECES; c += DEC_THREADS) {  // q is written by the kernel before this one
       const int row = c / PIECES, piece = c % PIECES;
       const bool ok = row < n_g;
       cp_async16(q_at(row, piece * 8),
@@ -954,7 +958,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
 #pragma unroll
   for (int kk = 0; kk < KSTEPS; ++kk) {
     uint32_t qf[4];
-    ldmatrix_x4(qf, tile_ptr<HD>(qs, (mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
+    ldmatrix_x4(qf, (QROWS == 8 && (mi & 1)) ? zero_chunk : tile_ptr<HD>(qs, (mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
 #pragma unroll
     for (int np = 0; np < 2; ++np) {
       uint32_t bfr[4];
@@ -1064,21 +1068,21 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   }
 }
 
-template <int HD, bool FUSED, bool TC5, bool ONE>
+template <int HD, bool FUSED, bool TC5, bool ONE, int QROWS>
 static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_parts, cudaStream_t stream, const void* qkv,
                                     int64_t q_row_stride, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
                                     int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int* err,
                                     const DecodePrep& prep) {
-  const size_t smem = (size_t)(16 + (ONE ? 1 : 2) * DEC_PART) * HD * sizeof(bf16) + 1024;
+  const size_t smem = (size_t)(QROWS + (ONE ? 1 : 2) * DEC_PART) * HD * sizeof(bf16) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, TC5, ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, TC5, ONE, QROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   const int G = nh / nkv;
   dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
-  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, TC5, ONE>, grid, dim3(DEC_THREADS), smem, stream,
+  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, TC5, ONE, QROWS>, grid, dim3(DEC_THREADS), smem, stream,
       *reinterpret_cast<const CUtensorMap*>(kv_map), (const bf16*)qkv, q_row_stride, bt, bt_stride, cu, cl, nh, nkv, page_size,
       scale, window, to, tm, tl, max_parts, err, prep);
   return 0;
@@ -1199,9 +1203,9 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   const bool tma = kind == 2;
   if (tma_mma) {
     const DecodePrep none = {};
-    int rc = hd == 64 ? launch_partition_tma_mma<64, false, false, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+    int rc = hd == 64 ? launch_partition_tma_mma<64, false, false, false, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none)
-                      : launch_partition_tma_mma<128, false, false, false>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                      : launch_partition_tma_mma<128, false, false, false, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                              cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none);
     if (rc) return rc;
   }
@@ -1273,15 +1277,18 @@ ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out
   DecodePrep prep = {q_weight, k_weight, eps, cos_sin, slot_mapping, (bf16*)pool};
   ME_REQUIRE(tcgen05 != 1 || hd == 128, "me_attn_decode_fused: the tcgen05 form takes head_dim 128");
   int rc = 1;
-#define ME_FUSED(HD_, TC_, ONE_)                                                                                         \
-  rc = launch_partition_tma_mma<HD_, true, TC_, ONE_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride, \
+#define ME_FUSED(HD_, TC_, ONE_, Q_)                                                                                     \
+  rc = launch_partition_tma_mma<HD_, true, TC_, ONE_, Q_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride, \
                                                 cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, \
                                                 err, prep)
-  if (tcgen05 == 1) ME_FUSED(128, true, false);
-  else if (hd == 64 && tcgen05 == 2) ME_FUSED(64, false, false);
-  else if (hd == 64) ME_FUSED(64, false, true);
-  else if (tcgen05 == 2) ME_FUSED(128, false, false);
-  else ME_FUSED(128, false, true);
+  const bool few_heads = G <= 8;                     // a group's query heads fit the lower half of the m16 strip
+  if (tcgen05 == 1) ME_FUSED(128, true, false, 16);
+  else if (hd == 64 && tcgen05 == 2) ME_FUSED(64, false, false, 16);
+  else if (hd == 64 && few_heads) ME_FUSED(64, false, true, 8);
+  else if (hd == 64) ME_FUSED(64, false, true, 16);
+  else if (tcgen05 == 2) ME_FUSED(128, false, false, 16);
+  else if (few_heads) ME_FUSED(128, false, true, 8);
+  else ME_FUSED(128, false, true, 16);
 #undef ME_FUSED
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_attn_decode_fused (partitions)");
