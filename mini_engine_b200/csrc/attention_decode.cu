@@ -664,13 +664,15 @@ struct DecodePrep {
 // wrote, accumulator in tensor memory); a thread then owns a key (tcgen05.ld), the softmax runs across threads,
 // P^T goes to shared memory as a K-major operand, and O^T [head_dim][16 heads] = V^T P^T takes V as an MN-major
 // operand, so that a thread ends up owning an output column.  Without TC5: mma.sync m16n8k16 with ldmatrix.
-// ONE (mma.sync form only): K and V pass through the same tile, V requested once every warp has its scores: half the
-// shared memory a block, so that five blocks share an SM instead of three.  A block then lives one load longer, but
-// more of them are loading at any time, and a batch of 8 at 1,000 tokens fits the GPU in one wave.
-// With ONE and at most 8 query heads a group the Q tile keeps 8 rows (the upper half of the m16 strip reads one
-// chunk of zeros) and the registers are held to what lets six blocks share an SM.
-template <int HD, bool FUSED, bool TC5, bool ONE, int QROWS>
-__global__ void __launch_bounds__(DEC_THREADS, (ONE && QROWS == 8) ? 6 : 1)
+// VBUF (mma.sync form only) says how much shared memory V has of its own: 2 a whole tile (three blocks an SM); 0
+// none: V passes through K's tile, requested once every warp has its scores (six blocks an SM with an 8-row Q tile:
+// a block lives one load longer, but more of them are loading at any time: large batches); 1 half a tile: the
+// first 64 keys' values come with K, the other 64 pass through K's tile (four blocks an SM: a batch of 8 at 1,000
+// tokens then fits the GPU in one wave with most of its loads in flight before the dependency resolves).
+// With at most 8 query heads a group the Q tile keeps 8 rows (the upper half of the m16 strip reads one chunk of
+// zeros), and with VBUF 0 the registers are held to what lets six blocks share an SM.
+template <int HD, bool FUSED, bool TC5, int VBUF, int QROWS>
+__global__ void __launch_bounds__(DEC_THREADS, (VBUF == 0 && QROWS == 8) ? 6 : 1)
 decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ qkv,
                                 int64_t q_row_stride, const int* __restrict__ block_tables, int bt_stride,
                                 const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
@@ -680,7 +682,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   using namespace mma_prims;
   extern __shared__ unsigned char dec_smem_raw[];
   __shared__ float w_m[4][16], w_l[4][16];
-  __shared__ __align__(8) unsigned long long bar_k, bar_v, bar_s, bar_o;
+  __shared__ __align__(8) unsigned long long bar_k, bar_v, bar_v2, bar_s, bar_o;
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(16) bf16 zero_chunk[8];
   constexpr int PIECES = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, HALVES = HD / 64;
@@ -714,8 +716,17 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   // Shared memory from a 1024-byte boundary: K halves [HALVES][128][64], V halves, then Q [16][HD].
   unsigned char* aligned = dec_smem_raw + ((1024u - (tma::smem_addr(dec_smem_raw) & 1023u)) & 1023u);
   bf16* ks = reinterpret_cast<bf16*>(aligned);
-  bf16* vs = ONE ? ks : ks + DEC_PART * HD;
-  bf16* qs = vs + DEC_PART * HD;
+  constexpr int HALF = DEC_PART / 2;
+  bf16* vs = VBUF == 0 ? ks : ks + DEC_PART * HD;      // VBUF 1: the values of keys 0..63; those of 64..127 go to ks
+  bf16* qs = vs + (VBUF == 2 ? DEC_PART : (VBUF == 1 ? HALF : 0)) * HD + (VBUF == 0 ? DEC_PART * HD : 0);
+  // Row ``row`` (a key of the partition), 16-byte piece ``piece`` of the V tile(s)
+  auto v_at = [&](int row, int piece) -> bf16* {
+    if (VBUF == 1) {
+      const int hi_half = row >= HALF;
+      return tma::swz128((hi_half ? ks : vs) + (piece >> 3) * HALF * 64, row - hi_half * HALF, piece & 7);
+    }
+    return tma::swz128(vs + (piece >> 3) * DEC_PART * 64, row, piece & 7);
+  };
   // Element i of row ``row`` of the Q tile: for mma.sync a [16][HD] tile with XOR-swizzled pieces, for tcgen05 a
   // K-major operand as the copy engine would have written it (blocks of [16 rows][64], 128-byte swizzle).
   auto q_at = [&](int row, int i) -> bf16* {
@@ -737,6 +748,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   if (tid == 0) {
     tma::mbar_init(&bar_k, 1);
     tma::mbar_init(&bar_v, 1);
+    tma::mbar_init(&bar_v2, 1);
     if (TC5) {
       tma::mbar_init(&bar_s, 1);
       tma::mbar_init(&bar_o, 1);
@@ -754,13 +766,19 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     const int page = (j0 < part_hi && j0 + page_size > lo_w) ? page_ahead : -1;
     if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size;
   }
-  auto request = [&](bool want_k, bool want_v) {       // warp 0
+  // what: bit 0 K, bit 1 the values of the partition's first half of pages, bit 2 those of the second half
+  auto request = [&](int what) {                       // warp 0
     const unsigned box_bytes = (unsigned)page_size * 64 * sizeof(bf16);
     const unsigned present = __ballot_sync(0xffffffffu, first_row >= 0);
+    const unsigned lo_pages = (1u << (n_pages / 2)) - 1u;
     if (lane == 0) {
-      const unsigned bytes = (unsigned)__popc(present) * HALVES * box_bytes;
-      if (want_k) tma::mbar_expect_tx(&bar_k, bytes);
-      if (want_v) tma::mbar_expect_tx(&bar_v, bytes);
+      if (what & 1) tma::mbar_expect_tx(&bar_k, (unsigned)__popc(present) * HALVES * box_bytes);
+      if (VBUF == 1) {
+        if (what & 2) tma::mbar_expect_tx(&bar_v, (unsigned)__popc(present & lo_pages) * HALVES * box_bytes);
+        if (what & 4) tma::mbar_expect_tx(&bar_v2, (unsigned)__popc(present & ~lo_pages) * HALVES * box_bytes);
+      } else if (what & 6) {
+        tma::mbar_expect_tx(&bar_v, (unsigned)__popc(present) * HALVES * box_bytes);
+      }
     }
     __syncwarp();
     const int v_rows = nkv * page_size;
@@ -768,12 +786,20 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       const int x = x0 + lane;
       const int i = x % n_pages, h = (x / n_pages) % HALVES, v = x / (n_pages * HALVES);
       const int row = __shfl_sync(0xffffffffu, first_row, i);
-      if (x < 2 * HALVES * n_pages && row >= 0 && (v ? want_v : want_k))
-        tma::load_2d((v ? vs : ks) + h * DEC_PART * 64 + i * page_size * 64, &kv_map, h * 64, row + v * v_rows,
-                     v ? &bar_v : &bar_k);
+      if (x >= 2 * HALVES * n_pages || row < 0) continue;
+      if (!v) {
+        if (what & 1) tma::load_2d(ks + h * DEC_PART * 64 + i * page_size * 64, &kv_map, h * 64, row, &bar_k);
+      } else if (VBUF == 1) {
+        const bool second = i >= n_pages / 2;
+        if (what & (second ? 4 : 2))
+          tma::load_2d((second ? ks : vs) + h * HALF * 64 + (i - (second ? n_pages / 2 : 0)) * page_size * 64, &kv_map, h * 64,
+                       row + v_rows, second ? &bar_v2 : &bar_v);
+      } else if (what & 6) {
+        tma::load_2d(vs + h * DEC_PART * 64 + i * page_size * 64, &kv_map, h * 64, row + v_rows, &bar_v);
+      }
     }
   };
-  if (warp == 0) request(true, !ONE);
+  if (warp == 0) request(VBUF == 2 ? 7 : (VBUF == 1 ? 3 : 1));
   constexpr int VEC = HD / 64;
   // what the preparation of q and of the newest key needs besides the rows themselves is no kernel's output:
   // read it while the kernel before this one is still running
@@ -855,8 +881,8 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       const int ia = i0 + j, ib = HD / 2 + i0 + j;
-      tma::swz128(tile + (ia >> 6) * DEC_PART * 64, row, (ia & 63) >> 3)[ia & 7] = new_a[j];
-      tma::swz128(tile + (ib >> 6) * DEC_PART * 64, row, (ib & 63) >> 3)[ib & 7] = new_b[j];
+      (kv ? v_at(row, ia >> 3) : tma::swz128(tile + (ia >> 6) * DEC_PART * 64, row, (ia & 63) >> 3))[ia & 7] = new_a[j];
+      (kv ? v_at(row, ib >> 3) : tma::swz128(tile + (ib >> 6) * DEC_PART * 64, row, (ib & 63) >> 3))[ib & 7] = new_b[j];
       if (dst) {
         dst[ia] = new_a[j];
         dst[ib] = new_b[j];
@@ -968,11 +994,11 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       mma_bf16(s[2 * np + 1], qf, bfr[2], bfr[3]);
     }
   }
-  if (ONE) {
-    __syncthreads();                                 // every warp has its scores: the tile is free for V
+  if (VBUF < 2) {
+    __syncthreads();                                 // every warp has its scores: K's tile is free for V
     if (warp == 0) {
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // (the newest key's row was written by threads)
-      request(false, true);
+      request(VBUF == 1 ? 4 : 6);
     }
   }
   float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -1007,12 +1033,12 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   landed = tma::mbar_wait(&bar_v, 0) && landed;
+  if (VBUF == 1) landed = tma::mbar_wait(&bar_v2, 0) && landed;
   if (makes_new && warp == 1) put_new(vs, 1);
   {                                                  // rows of V that are no keys of this request: zero
     const int j = part_lo + tid;                     // 128 threads, 128 rows
     if (j >= part_hi || j < lo_w)
-      for (int p = 0; p < PIECES; ++p)
-        *reinterpret_cast<uint4*>(tma::swz128(vs + (p >> 3) * DEC_PART * 64, tid, p & 7)) = make_uint4(0, 0, 0, 0);
+      for (int p = 0; p < PIECES; ++p) *reinterpret_cast<uint4*>(v_at(tid, p)) = make_uint4(0, 0, 0, 0);
   }
   __syncthreads();                                   // V complete and cleaned; every warp is done reading K
   float o[NT_O][4];
@@ -1024,12 +1050,12 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     for (int np = 0; np < NT_O / 2; ++np) {
       uint32_t bfr[4];
       const int piece = np * 2 + (mi >> 1);
-      ldmatrix_x4_trans(bfr, tma::swz128(vs + (piece >> 3) * DEC_PART * 64, warp * 32 + kk * 16 + (mi & 1) * 8 + (lane & 7), piece & 7));
+      ldmatrix_x4_trans(bfr, v_at(warp * 32 + kk * 16 + (mi & 1) * 8 + (lane & 7), piece));
       mma_bf16(o[2 * np], pf[kk], bfr[0], bfr[1]);
       mma_bf16(o[2 * np + 1], pf[kk], bfr[2], bfr[3]);
     }
   }
-  if (ONE) __syncthreads();                          // every warp is done reading V: the tile now takes the warps' results
+  if (VBUF < 2) __syncthreads();                     // every warp is done reading V: K's tile now takes the warps' results
   float* po = reinterpret_cast<float*>(ks);          // [4][16][HD] float32, over the K tile
   if (t4 == 0) {
     w_m[warp][g] = mx0;
@@ -1068,21 +1094,21 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   }
 }
 
-template <int HD, bool FUSED, bool TC5, bool ONE, int QROWS>
+template <int HD, bool FUSED, bool TC5, int VBUF, int QROWS>
 static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_parts, cudaStream_t stream, const void* qkv,
                                     int64_t q_row_stride, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
                                     int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int* err,
                                     const DecodePrep& prep) {
-  const size_t smem = (size_t)(QROWS + (ONE ? 1 : 2) * DEC_PART) * HD * sizeof(bf16) + 1024;
+  const size_t smem = (size_t)(QROWS + DEC_PART + VBUF * DEC_PART / 2) * HD * sizeof(bf16) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, TC5, ONE, QROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, TC5, VBUF, QROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   const int G = nh / nkv;
   dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
-  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, TC5, ONE, QROWS>, grid, dim3(DEC_THREADS), smem, stream,
+  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, TC5, VBUF, QROWS>, grid, dim3(DEC_THREADS), smem, stream,
       *reinterpret_cast<const CUtensorMap*>(kv_map), (const bf16*)qkv, q_row_stride, bt, bt_stride, cu, cl, nh, nkv, page_size,
       scale, window, to, tm, tl, max_parts, err, prep);
   return 0;
@@ -1203,9 +1229,9 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   const bool tma = kind == 2;
   if (tma_mma) {
     const DecodePrep none = {};
-    int rc = hd == 64 ? launch_partition_tma_mma<64, false, false, false, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+    int rc = hd == 64 ? launch_partition_tma_mma<64, false, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none)
-                      : launch_partition_tma_mma<128, false, false, false, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                      : launch_partition_tma_mma<128, false, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                              cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none);
     if (rc) return rc;
   }
@@ -1257,13 +1283,14 @@ ME_API int me_attn_decode_fused_takes(int hd, int page_size) {
 // whole step) happen inside the partition kernel, for requests [0, num_reqs) that bring one token each
 // (token row = cu_seqlens[request], position = context_lens[request] - 1).  q_weight/k_weight (both or neither), cos_sin and slot_mapping may be
 // null; with a null slot_mapping the newest key and value are expected in the cache already.  The q rows of
-// ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.  tcgen05 (the form of the partition
-// kernel): 0 mma.sync with K and V through one tile, 1 tcgen05 (head_dim 128), 2 mma.sync with a tile each.
+// ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.  form (of the partition kernel):
+// 0 mma.sync with K and V through one tile, 1 tcgen05 (head_dim 128), 2 mma.sync with a tile each, 3 mma.sync with
+// half a tile for V beside K's.
 ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out, int64_t out_row_stride, void* pool,
                                 const void* kv_map, const int* block_tables, int bt_stride, const int* cu_seqlens,
                                 const int* context_lens, int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
                                 int window, const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
-                                const int* slot_mapping, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts, int tcgen05,
+                                const int* slot_mapping, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts, int form,
                                 int* err, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   ME_REQUIRE(me_attn_decode_fused_takes(hd, page_size), "me_attn_decode_fused: head_dim %d with pages of %d is not taken", hd, page_size);
@@ -1275,20 +1302,24 @@ ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out
   const int G = nh / nkv;
   ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode_fused: too many heads");
   DecodePrep prep = {q_weight, k_weight, eps, cos_sin, slot_mapping, (bf16*)pool};
-  ME_REQUIRE(tcgen05 != 1 || hd == 128, "me_attn_decode_fused: the tcgen05 form takes head_dim 128");
+  ME_REQUIRE(form >= 0 && form <= 3 && (form != 1 || hd == 128), "me_attn_decode_fused: form %d (the tcgen05 form takes head_dim 128)", form);
   int rc = 1;
-#define ME_FUSED(HD_, TC_, ONE_, Q_)                                                                                     \
-  rc = launch_partition_tma_mma<HD_, true, TC_, ONE_, Q_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride, \
-                                                cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, \
-                                                err, prep)
+#define ME_FUSED(HD_, TC_, VBUF_, Q_)                                                                                    \
+  rc = launch_partition_tma_mma<HD_, true, TC_, VBUF_, Q_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, \
+                                                           bt_stride, cu_seqlens, context_lens, nh, nkv, page_size, scale, window, \
+                                                           tmp_out, tmp_m, tmp_l, err, prep)
   const bool few_heads = G <= 8;                     // a group's query heads fit the lower half of the m16 strip
-  if (tcgen05 == 1) ME_FUSED(128, true, false, 16);
-  else if (hd == 64 && tcgen05 == 2) ME_FUSED(64, false, false, 16);
-  else if (hd == 64 && few_heads) ME_FUSED(64, false, true, 8);
-  else if (hd == 64) ME_FUSED(64, false, true, 16);
-  else if (tcgen05 == 2) ME_FUSED(128, false, false, 16);
-  else if (few_heads) ME_FUSED(128, false, true, 8);
-  else ME_FUSED(128, false, true, 16);
+  ME_REQUIRE(form != 3 || (DEC_PART / 2) % page_size == 0, "me_attn_decode_fused: pages of %d do not fit half a partition", page_size);
+#define ME_FUSED_Q(HD_, VBUF_)                                                                                           \
+  do { if (few_heads) ME_FUSED(HD_, false, VBUF_, 8); else ME_FUSED(HD_, false, VBUF_, 16); } while (0)
+  if (form == 1) ME_FUSED(128, true, 2, 16);
+  else if (hd == 64 && form == 2) ME_FUSED(64, false, 2, 16);
+  else if (hd == 64 && form == 3) ME_FUSED_Q(64, 1);
+  else if (hd == 64) ME_FUSED_Q(64, 0);
+  else if (form == 2) ME_FUSED(128, false, 2, 16);
+  else if (form == 3) ME_FUSED_Q(128, 1);
+  else ME_FUSED_Q(128, 0);
+#undef ME_FUSED_Q
 #undef ME_FUSED
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_attn_decode_fused (partitions)");

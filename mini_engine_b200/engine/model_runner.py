@@ -184,7 +184,7 @@ class ModelRunner:
 
     def build_batch(self, items: Sequence[StepItem], ctx: StepContext, *, pad_reqs: int = 0,
                     table_width: int = 0, dev: Optional[torch.Tensor] = None,
-                    fill_ctx: bool = True) -> tuple[Optional[torch.Tensor], list[int]]:
+                    fill_ctx: bool = True, typical_context: int = 0) -> tuple[Optional[torch.Tensor], list[int]]:
         """Lay the step's metadata out in pinned memory, copy it once, fill ``ctx``.
 
         Requests that bring one token come first (as in engine/model_runner.py:88-89).
@@ -358,7 +358,8 @@ class ModelRunner:
             num_tiles=n_tiles,
             max_context_len=max(ends + [1]) if not table_width else table_width * ps,
             workspace=ctx.buffer, error_flag=self.error_flag,
-            scratch_context_len=self.max_model_len if table_width else 0)
+            scratch_context_len=self.max_model_len if table_width else 0,
+            typical_context_len=typical_context)
         ctx.host = HostMeta(starts=starts, lengths=lens,
                             state_slots=[items[i].holder.state_slot for i in order],
                             holders=[items[i].holder for i in order])
@@ -424,8 +425,10 @@ class ModelRunner:
                 self._graphs.pop(k) for k in list(self._graphs) if k[0] == b and k != keep]
             n = 16 * bucket + 64 + sum(4 * bucket + bucket * width + 8 for _ in self.groups)
             g.meta_dev = torch.zeros(n + 64, dtype=torch.int32, device=self.device)
+        # the graph serves contexts from the bucket below up to this one: its kernels are chosen for the middle
         token_ids, _ = self.build_batch(items, g.ctx, pad_reqs=bucket, table_width=width, dev=g.meta_dev,
-                                        fill_ctx=g.graph is None)
+                                        fill_ctx=g.graph is None,
+                                        typical_context=ctx_bucket * 3 // 4 if bucket < 32 else max(ctx_bucket - 128, 1))
         if g.graph is None:
             # Once eagerly (allocates the work buffers), then captured; both runs do the step's real work.
             g.ctx.frozen = False

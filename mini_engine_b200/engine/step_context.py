@@ -40,6 +40,7 @@ class AttnMeta:
     workspace: Any                     # callable (name, shape, dtype) -> tensor
     error_flag: Any = None             # int32[4] on the device: kernels report bad input or a timed-out wait here
     scratch_context_len: int = 0       # if larger than max_context_len: size split-K scratch for this many keys (so it never has to grow)
+    typical_context_len: int = 0       # what contexts a captured step will mostly see (0: max_context_len); picks kernel variants
 
 
 @dataclass

@@ -507,9 +507,12 @@ def decode_fused_takes(qkv: torch.Tensor, head_dim: int, pool: torch.Tensor, pag
 # five blocks an SM), "two_tiles" (mma.sync; a tile each, three blocks an SM) or "tcgen05" (the two products on the
 # 5th-generation tensor cores, head size 128 only; measured slower than mma.sync: an accumulator in tensor memory
 # costs a partition two round trips through commit, mbarrier and tcgen05.ld for 16 instructions' worth of arithmetic).
-DECODE_FORMS = {"one_tile": 0, "tcgen05": 1, "two_tiles": 2}
-decode_form = "auto"          # two tiles while all partitions are resident at once (the loads of K and V overlap: batch 1,
-                              # 0.78 against 0.80 ms), one tile beyond (batch 64: 2.65 against 2.87 ms, batch 256: 7.8 against 8.7)
+DECODE_FORMS = {"one_tile": 0, "tcgen05": 1, "two_tiles": 2, "tile_and_half": 3}
+# "auto": by the number of partitions with keys.  Up to what three blocks an SM hold at once, two tiles (all loads
+# in flight together: batch 1, 0.78 ms a step against 0.80 with one tile); up to about four times that, a tile and a
+# half (batch 8: 0.92 against 0.97, batch 16: 1.23 against 1.27); beyond, one tile (batch 64: 2.60 against 2.90 and
+# 2.98; batch 256: 7.6 against 9.1 and 8.7).
+decode_form = "auto"
 DECODE_RESIDENT_TWO_TILES = 3 * 148
 
 
@@ -523,9 +526,15 @@ def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, pa
     ``decode_form``)."""
     form = form or decode_form
     if form == "auto":
+        typical = getattr(meta, "typical_context_len", 0) or meta.max_context_len
         blocks = meta.num_decodes * num_kv_heads * ((num_heads // num_kv_heads + 15) // 16) \
-            * ((meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
-        form = "two_tiles" if blocks <= DECODE_RESIDENT_TWO_TILES else "one_tile"
+            * ((typical + DECODE_PARTITION - 1) // DECODE_PARTITION)
+        if blocks <= DECODE_RESIDENT_TWO_TILES:
+            form = "two_tiles"
+        elif blocks <= 4 * DECODE_RESIDENT_TWO_TILES and (DECODE_PARTITION // 2) % page_size == 0:
+            form = "tile_and_half"
+        else:
+            form = "one_tile"
     D = meta.num_decodes
     parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
     room = max(parts, (getattr(meta, "scratch_context_len", 0) + DECODE_PARTITION - 1) // DECODE_PARTITION)
