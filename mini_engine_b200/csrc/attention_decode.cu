@@ -818,6 +818,8 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       rs[j] = rope ? cs[HD / 2 + i] : 0.f;
     }
   }
+  // (the slot of the newest key and value is the host's data as well)
+  const int new_slot = makes_new ? prep.slot_mapping[tok] : -1;
   if (!wait_first) {
     pdl_wait();
     pdl_launch_dependents();
@@ -872,7 +874,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   // The newest key and value go to their row of the tiles (over whatever the slot held) and to the cache.
   auto put_new = [&](bf16* tile, int kv) {
     const int row = L - 1 - part_lo, i0 = lane * VEC;
-    const int slot = prep.slot_mapping[tok];
+    const int slot = new_slot;
     bf16* dst = nullptr;
     if (slot >= 0 && g0 == 0) {
       const int page = slot / page_size, off = slot - page * page_size;
@@ -1133,6 +1135,30 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
   const int P = max(1, min(max_parts, (L + DEC_PART - 1) / DEC_PART));
   const int64_t row0 = ((int64_t)b * nh + h) * max_parts;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = (blockDim.x + 31) >> 5;
+  if (P <= 16 && hd <= (int)blockDim.x) {
+    // The usual case in one round trip to memory: every thread asks for all maxima and sums (the same few words
+    // for all threads) and for its column of every partition at once, then needs no other thread.
+    float mv[16], lv[16], ov[16];
+#pragma unroll
+    for (int p = 0; p < 16; ++p) {
+      mv[p] = p < P ? tmp_m[row0 + p] : -INFINITY;
+      lv[p] = p < P ? tmp_l[row0 + p] : 0.f;
+      ov[p] = (p < P && tid < hd) ? tmp_out[(row0 + p) * hd + tid] : 0.f;     // (never written where mv is -inf: not used then)
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int p = 0; p < 16; ++p) M = fmaxf(M, mv[p]);
+    float lt = 0.f, acc = 0.f;
+#pragma unroll
+    for (int p = 0; p < 16; ++p) {                   // partitions in index order
+      if (mv[p] == -INFINITY) continue;
+      const float f = expf(mv[p] - M);
+      lt += f * lv[p];
+      acc += f * ov[p];
+    }
+    if (tid < hd) out[tok * out_row_stride + (int64_t)h * hd + tid] = from_f<T>(lt > 0.f ? acc / lt : 0.f);
+    return;
+  }
   // the largest maximum: a partition per thread, then lanes, then warps
   float mx = -INFINITY;
   for (int p = tid; p < P; p += blockDim.x) mx = fmaxf(mx, tmp_m[row0 + p]);
