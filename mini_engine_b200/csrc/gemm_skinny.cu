@@ -20,15 +20,20 @@ __device__ __forceinline__ bf16* sk_ptr(bf16* base, int row, int piece) {
   return base + row * SK_KW + ((piece ^ (row & 7)) << 3);
 }
 
-template <int EPI, typename TO>
+// XR: rows of the X tile, 16, or 8 for up to 8 rows of X (the upper n8 tile then reads one chunk of zeros): a
+// block needs 48 KB instead of 64 KB, four share an SM instead of three, and a product with thousands of strips
+// (the vocabulary) has a third more weights in flight.
+template <int EPI, typename TO, int XR>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ X, int64_t ldx, const bf16* __restrict__ W, TO* __restrict__ Y,
                    int64_t ldy, float* __restrict__ partial, int M, int N, int K) {
   extern __shared__ __align__(128) unsigned char sk_smem[];
   __shared__ float red[4][16][17];
+  __shared__ __align__(16) bf16 zero_chunk[8];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
-  bf16* ws = reinterpret_cast<bf16*>(sk_smem) + warp * 2 * 16 * SK_KW;   // this warp's W tile [16][256]
-  bf16* xs = ws + 16 * SK_KW;                                              // this warp's X tile [16][256]
+  if (tid < 8) zero_chunk[tid] = __float2bfloat16_rn(0.f);
+  bf16* ws = reinterpret_cast<bf16*>(sk_smem) + warp * (16 + XR) * SK_KW;  // this warp's W tile [16][256]
+  bf16* xs = ws + 16 * SK_KW;                                              // this warp's X tile [XR][256]
   const int strip = blockIdx.x;
   const int k0 = (blockIdx.y * 4 + warp) * SK_KW;
   // rows of W in this strip
@@ -47,7 +52,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int64_t ldx, const bf16* __restri
   }
   pdl_wait();
   pdl_launch_dependents();
-  for (int c = lane; c < 16 * SK_PIECES; c += 32) {
+  for (int c = lane; c < XR * SK_PIECES; c += 32) {
     const int row = c / SK_PIECES, piece = c % SK_PIECES;
     const int k = k0 + piece * 8;
     const bool okx = k < K && row < M;
@@ -55,6 +60,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int64_t ldx, const bf16* __restri
   }
   cp_async_commit();
   cp_async_wait<0>();
+  if (XR == 8) __syncthreads();                      // (the chunk of zeros is another warp's write)
   __syncwarp();
   float c[2][4] = {};
   const int mi = lane >> 3;
@@ -63,7 +69,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int64_t ldx, const bf16* __restri
     for (int kk = 0; kk < SK_KW / 16; ++kk) {
       uint32_t a[4], b[4];
       ldmatrix_x4(a, sk_ptr(ws, (mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
-      ldmatrix_x4(b, sk_ptr(xs, (mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)));
+      ldmatrix_x4(b, (XR == 8 && (mi >> 1)) ? zero_chunk : sk_ptr(xs, (mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)));
       mma_bf16(c[0], a, b[0], b[1]);
       mma_bf16(c[1], a, b[2], b[3]);
     }
@@ -99,17 +105,17 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int64_t ldx, const bf16* __restri
   }
 }
 
-template <int EPI, typename TO>
+template <int EPI, typename TO, int XR>
 int launch_skinny(const void* X, int64_t ldx, const void* W, void* Y, int64_t ldy, float* partial, int M, int N,
                   int K, int strips, int splits, cudaStream_t stream) {
-  const size_t smem = (size_t)4 * 2 * 16 * SK_KW * sizeof(bf16);      // 64 KB
+  const size_t smem = (size_t)4 * (16 + XR) * SK_KW * sizeof(bf16);    // 64 KB, or 48 KB with 8 rows of X
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<EPI, TO, XR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_gemm_skinny: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  me_launch(gemm_skinny_kernel<EPI, TO>, dim3(strips, splits), dim3(SK_THREADS), smem, stream,
+  me_launch(gemm_skinny_kernel<EPI, TO, XR>, dim3(strips, splits), dim3(SK_THREADS), smem, stream,
       (const bf16*)X, ldx, (const bf16*)W, (TO*)Y, ldy, partial, M, N, K);
   return 0;
 }
@@ -133,11 +139,14 @@ ME_API int me_gemm_skinny(const void* X, int64_t ldx, const void* W, void* Y, in
   int rc;
   if (epi == 1) {
     ME_REQUIRE(y_dtype == ME_BF16, "me_gemm_skinny: the SiLU epilogue writes bfloat16");
-    rc = launch_skinny<1, bf16>(X, ldx, W, Y, ldy, partial, M, N, K, strips, splits, stream);
+    rc = M <= 8 ? launch_skinny<1, bf16, 8>(X, ldx, W, Y, ldy, partial, M, N, K, strips, splits, stream)
+                : launch_skinny<1, bf16, 16>(X, ldx, W, Y, ldy, partial, M, N, K, strips, splits, stream);
   } else if (y_dtype == ME_BF16) {
-    rc = launch_skinny<0, bf16>(X, ldx, W, Y, ldy, partial, M, N, K, strips, splits, stream);
+    rc = M <= 8 ? launch_skinny<0, bf16, 8>(X, ldx, W, Y, ldy, partial, M, N, K, strips, splits, stream)
+                : launch_skinny<0, bf16, 16>(X, ldx, W, Y, ldy, partial, M, N, K, strips, splits, stream);
   } else {
-    rc = launch_skinny<0, float>(X, ldx, W, Y, ldy, partial, M, N, K, strips, splits, stream);
+    rc = M <= 8 ? launch_skinny<0, float, 8>(X, ldx, W, Y, ldy, partial, M, N, K, strips, splits, stream)
+                : launch_skinny<0, float, 16>(X, ldx, W, Y, ldy, partial, M, N, K, strips, splits, stream);
   }
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_gemm_skinny");
