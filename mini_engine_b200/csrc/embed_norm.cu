@@ -166,6 +166,87 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ res, const TD* __res
   }
 }
 
+// Eight consecutive elements with 16-byte (bfloat16) or 2 x 16-byte (float32) accesses.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(h[k]);
+    v[2 * k] = f.x;
+    v[2 * k + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// Many rows (a portion of a prompt): a warp per row, every load of the row issued before the first is used, no
+// block-wide barrier.  H a multiple of 8 up to 256 * CH; the lane's chunks are elements 8 (lane + 32 i) .. + 7.
+template <typename TD, typename TO, int CH>
+__global__ void __launch_bounds__(128)
+add_rmsnorm_rows_kernel(float* __restrict__ res, const TD* __restrict__ delta, const float* __restrict__ w, float eps,
+                        TO* __restrict__ out, int n_rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  float ww[CH][8];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int h = 8 * (lane + 32 * i);
+    if (h < H) load8(w + h, ww[i]);
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  if (r >= n_rows) return;
+  float* rr = res + r * H;
+  float v[CH][8], d[CH][8];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int h = 8 * (lane + 32 * i);
+    if (h < H) {
+      load8(rr + h, v[i]);
+      if (delta) load8(delta + r * H + h, d[i]);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int h = 8 * (lane + 32 * i);
+    if (h < H) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (delta) v[i][e] += d[i][e];
+        ss += v[i][e] * v[i][e];
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int h = 8 * (lane + 32 * i);
+    if (h < H) {
+      if (delta) store8(rr + h, v[i]);
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = (v[i][e] * inv) * ww[i][e];
+      store8(out + r * H + h, o);
+    }
+  }
+}
+
 ME_API int me_add_rmsnorm(float* res, const void* delta, int delta_dtype, const float* w, float eps,
                           void* out, int out_dtype, const int* rows, int n_rows, int H, int splits,
                           int64_t split_stride, cudaStream_t stream) {
@@ -173,6 +254,19 @@ ME_API int me_add_rmsnorm(float* res, const void* delta, int delta_dtype, const 
   ME_REQUIRE(n_rows > 0 && H > 0 && splits >= 1, "me_add_rmsnorm: bad sizes rows=%d H=%d splits=%d", n_rows, H, splits);
   const int write_res = rows == nullptr;     // gathered rows leave the residual as it is
   constexpr int NV = 8;
+  // portions of prompts: a warp per row
+  const bool aligned16 = (((uintptr_t)res | (uintptr_t)w | (uintptr_t)delta | (uintptr_t)out) & 15) == 0;
+  if (n_rows >= 64 && rows == nullptr && splits == 1 && H % 8 == 0 && H <= 2048 && aligned16) {
+    const unsigned blocks = (unsigned)((n_rows + 3) / 4);
+#define ME_ROWS(CH_)                                                                                              \
+    ME_DISPATCH_DTYPE(delta_dtype, TD, ME_DISPATCH_DTYPE(out_dtype, TO,                                           \
+        (me_launch(add_rmsnorm_rows_kernel<TD, TO, CH_>, dim3(blocks), dim3(128), 0, stream, res, (const TD*)delta, w, eps, \
+                   (TO*)out, n_rows, H))))
+    if (H <= 256) ME_ROWS(1); else if (H <= 512) ME_ROWS(2); else if (H <= 1024) ME_ROWS(4); else ME_ROWS(8);
+#undef ME_ROWS
+    ME_LAUNCH_CHECK("me_add_rmsnorm");
+    return 0;
+  }
   if (H % 4 == 0 && H <= 8 * 1024 && ((uintptr_t)res & 15) == 0 && ((uintptr_t)w & 15) == 0) {
     int threads = ((H / 4 + 1) / 2 + 31) / 32 * 32;
     if (threads < 32) threads = 32;

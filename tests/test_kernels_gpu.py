@@ -46,10 +46,11 @@ def test_embed(ops, wd):
 
 
 # ---- residual add + RMSNorm --------------------------------------------------------------------
-@pytest.mark.parametrize("H", [64, 96, 1000, 1001, 4104, 8200, 9001])
+@pytest.mark.parametrize("H", [64, 96, 1000, 1001, 1024, 2048, 4104, 8200, 9001])
 @pytest.mark.parametrize("od", ["float32", "bfloat16"])
-def test_add_rmsnorm(ops, H, od):
-    T = 19
+@pytest.mark.parametrize("T", [19, 333])
+def test_add_rmsnorm(ops, H, od, T):
+    # (from 64 rows on and up to 2,048 columns a warp takes a row: another kernel than for a handful of rows)
     for delta_dt in (None, od, "float32"):
         res = rnd(T, H, seed=1)
         delta = None if delta_dt is None else rnd(T, H, dtype=DT[delta_dt], seed=2)
