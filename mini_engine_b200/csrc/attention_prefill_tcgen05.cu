@@ -7,8 +7,10 @@
 //
 // One block = 128 rows = (128 / GP query tokens) x (GP heads of one key/value head), row r being head
 // r / TQ, token r % TQ.  Key tiles of 128 keys at absolute multiples of 128.
-//   warp 0, one thread: TMA.  Q once (a box per head and 64-column half), then per key tile the pages
-//     of K and V (a box per page and half, 128-byte swizzle) into two buffers.
+//   warps 0 and 10: TMA.  Q once (a box per head and 64-column half), then per key tile the pages of K (warp 0)
+//     and of V (warp 10), a box per page and half with the 128-byte swizzle, each into a ring of two buffers of
+//     its own: a K buffer is handed back when Q K^T has read it, a V buffer when P V has, so the next K is on
+//     its way a tile's time before the next V.
 //   warp 1, one thread: tcgen05.mma.  S[128x128] = Q K^T into one of two S buffers in tensor memory
 //     (K-major operands), one tile ahead of the softmax; after the softmax warps have written P:
 //     O_tile[128 x head_dim] = P V, with V as an MN-major operand.
@@ -50,7 +52,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   constexpr int KB_BYTES = TA_KEYS * 128;               // one [TA_KEYS][64] bfloat16 block of K or V
   constexpr uint32_t TMEM_COLS = TA_KEYS == 128 ? 512 : 256;   // two S buffers of TA_KEYS columns, then the O tile
   extern __shared__ unsigned char ta_smem_raw[];
-  __shared__ __align__(8) unsigned long long q_bar, kv_full[2], kv_empty[2], s_ready[2], p_ready, p_free[2], o_ready;
+  __shared__ __align__(8) unsigned long long q_bar, k_full[2], k_empty[2], v_full[2], v_empty[2], s_ready[2], p_ready, p_free[2], o_ready;
   __shared__ uint32_t tmem_slot;
   __shared__ float l_other[TA_ROWS];
   __shared__ float m_half[2][TA_ROWS];                  // the two threads of a row tell each other their half's maximum
@@ -80,8 +82,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   if (threadIdx.x == 0) {
     tma::mbar_init(&q_bar, 1);
     for (int s = 0; s < 2; ++s) {
-      tma::mbar_init(&kv_full[s], 2);                     // the K producer and the V producer each announce their bytes
-      tma::mbar_init(&kv_empty[s], 1);
+      tma::mbar_init(&k_full[s], 1);                      // K and V have rings of their own: a K buffer is free again as soon
+      tma::mbar_init(&k_empty[s], 1);                     // as Q K^T has read it, a V buffer only after P V, a tile's time later
+      tma::mbar_init(&v_full[s], 1);
+      tma::mbar_init(&v_empty[s], 1);
     }
     tma::mbar_init(&s_ready[0], 1);
     tma::mbar_init(&s_ready[1], 1);
@@ -118,9 +122,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int row_off = is_v ? nkv * page_size : 0;
     unsigned char* dst0 = is_v ? v_s : k_s;
     const int pg = lane / HALVES, hf = lane % HALVES;
+    unsigned long long* const full = is_v ? v_full : k_full;
+    unsigned long long* const empty = is_v ? v_empty : k_empty;
     for (int it = 0; it < n_tiles && ok; ++it) {
       const int s = it & 1, kt = lo + it * TA_KEYS;
-      ok = tma::mbar_wait(&kv_empty[s], ((it >> 1) & 1) ^ 1);
+      ok = tma::mbar_wait(&empty[s], ((it >> 1) & 1) ^ 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       int first_row = -1;
@@ -132,10 +138,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         }
       }
       const unsigned n_boxes = __popc(__ballot_sync(0xffffffffu, first_row >= 0));
-      if (lane == 0) tma::mbar_expect_tx(&kv_full[s], n_boxes * box_bytes);
+      if (lane == 0) tma::mbar_expect_tx(&full[s], n_boxes * box_bytes);
       __syncwarp();
       if (first_row >= 0)
-        tma::load_2d(dst0 + s * KV_BYTES + hf * KB_BYTES + pg * page_size * 128, &kv_map, hf * 64, first_row, &kv_full[s]);
+        tma::load_2d(dst0 + s * KV_BYTES + hf * KB_BYTES + pg * page_size * 128, &kv_map, hf * 64, first_row, &full[s]);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -146,7 +152,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       // arrived on p_ready(it - 2) before this thread issued P V (it - 2).
       auto issue_qk = [&](int it) -> bool {
         const int s = it & 1;
-        if (!tma::mbar_wait(&kv_full[s], (it >> 1) & 1)) return false;
+        if (!tma::mbar_wait(&k_full[s], (it >> 1) & 1)) return false;
         tc5::fence_after_sync();
 #pragma unroll
         for (int c = 0; c < HALVES; ++c) {
@@ -156,6 +162,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           for (int k = 0; k < 4; ++k) tc5::mma_f16(tmem_s + s * TA_KEYS, a_desc + 2 * k, b_desc + 2 * k, idesc_s, c > 0 || k > 0);
         }
         tc5::commit(&s_ready[s]);
+        tc5::commit(&k_empty[s]);                          // the K buffer may be refilled while the softmax and P V of the tile run
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -166,6 +173,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           if (!ok) break;
         }
         ok = tma::mbar_wait(&p_ready, it & 1);             // P(it) is in shared memory, O is rescaled if it had to be
+        if (ok) ok = tma::mbar_wait(&v_full[s], (it >> 1) & 1);
         if (!ok) break;
         tc5::fence_after_sync();
         // O += P V: A = P [128 rows][TA_KEYS] K-major (blocks of 64 keys); B = V [TA_KEYS][HD], MN-major:
@@ -178,7 +186,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         }
         tc5::commit(&o_ready);                             // P V (it) and everything before it are done
         tc5::commit(&p_free[s]);
-        tc5::commit(&kv_empty[s]);
+        tc5::commit(&v_empty[s]);
       }
     }
   } else {
@@ -202,12 +210,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       float sv[KH];
       float mx = neg_inf;
       const bool need_mask = kt + TA_KEYS - 1 > p_lo || (window > 0 && kt <= p_hi - window) || n_tok * gp < TA_ROWS;
-      if (ok) ok = tma::mbar_wait(&kv_full[s], (it >> 1) & 1);
-      if (ok && (kt + TA_KEYS > hi || kt < lo_seen)) {
+      if (kt + TA_KEYS > hi || kt < lo_seen) {
         // Rows of V that hold no key this tile may use must be zero (0 * anything-else would not be 0):
-        // thread (r, half) clears its 64-column half of key row r.
+        // thread (r, half) clears its 64-column half of key row r, once the tile's pages have landed.
+        if (ok) ok = tma::mbar_wait(&v_full[s], (it >> 1) & 1);
         const int j = kt + r;
-        if (r < TA_KEYS && (j >= hi || j < lo_seen) && half < HALVES) {
+        if (ok && r < TA_KEYS && (j >= hi || j < lo_seen) && half < HALVES) {
           uint4* row = reinterpret_cast<uint4*>(v_s + s * KV_BYTES + half * KB_BYTES + r * 128);
 #pragma unroll
           for (int q = 0; q < 8; ++q) row[q] = make_uint4(0, 0, 0, 0);
