@@ -86,16 +86,45 @@ def library_file() -> str:
 
 
 _fns: dict = {}
+_last_call = None         # (entry point, arguments) of the launch before
 
 
 def _call(name: str, *args) -> None:
-    global launches
+    global launches, _last_call
     fn = _fns.get(name)
     if fn is None:
         fn = _fns[name] = getattr(_lib or require_extension(), name)
     if fn(*args) != 0:
         raise KernelError(_lib.me_last_error().decode())
     launches += 1
+    _last_call = (fn, args)
+
+
+# The same product or norm comes back step after step with the same tensors (the work buffers of a step are the
+# same storage every time): a wrapper that finds its key here, with the same addresses, shapes and strides as when
+# it was made, launches at once with the arguments of that time (and the stream of now) instead of checking and
+# deciding everything again.  An eager step spends more host time on that than on the launches themselves.
+_repeats: dict = {}
+remember_launches = True  # False: every wrapper runs in full every time (a switch for comparisons)
+
+
+def _repeat(key, sig) -> bool:
+    global launches
+    hit = _repeats.get(key) if remember_launches else None
+    if hit is None or hit[0] != sig:
+        return False
+    if hit[1](*hit[2], _stream()) != 0:
+        raise KernelError(_lib.me_last_error().decode())
+    launches += 1
+    return True
+
+
+def _remember(key, sig, launches_before: int) -> None:
+    """After a wrapper has run in full: keep its launch if it was exactly one, with the stream as last argument."""
+    if launches == launches_before + 1 and _last_call is not None and _last_call[1][-1] == _stream():
+        if len(_repeats) > 16384:
+            _repeats.clear()
+        _repeats[key] = (sig, _last_call[0], _last_call[1][:-1])
 
 
 _device_index: Optional[int] = None
@@ -153,6 +182,13 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     """``residual += delta`` (float32, in place), ``out = rmsnorm(residual) * weight``; with ``rows``
     only those rows are read and ``residual`` is not written.  A 3-D ``delta`` [splits, T, H] holds the
     partial results of a split-K product; they are added in order."""
+    key = ("add_rmsnorm", id(residual), id(delta), id(weight), id(out), id(rows))
+    sig = (residual.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), _ptr(rows), residual.shape, residual.stride(),
+           residual.dtype, None if delta is None else (delta.shape, delta.stride(), delta.dtype), weight.shape, weight.dtype,
+           out.shape, out.stride(), out.dtype, None if rows is None else (rows.shape, rows.stride(), rows.dtype), eps)
+    if _repeat(key, sig):
+        return
+    before = launches
     H = residual.shape[1]
     _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_rmsnorm: residual must be float32")
     _need(weight.dtype == torch.float32 and weight.shape == (H,), "add_rmsnorm: weight must be float32 [H]")
@@ -169,6 +205,7 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
         _need(rows.dtype == torch.int32 and rows.is_contiguous(), "add_rmsnorm: rows must be int32")
     _call("me_add_rmsnorm", residual.data_ptr(), _ptr(delta), _dt(delta) if delta is not None else 0,
           weight.data_ptr(), float(eps), out.data_ptr(), _dt(out), _ptr(rows), n, H, splits, stride, _stream())
+    _remember(key, sig, before)
 
 
 def silu_mul(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -272,6 +309,7 @@ def matrix_tensor_map(t: torch.Tensor, box_rows: int) -> "TensorMap":
     if tm is None:
         if len(_tensor_maps) > 8192:
             _tensor_maps.clear()
+            _repeats.clear()          # remembered launches hold the addresses of the maps just dropped
         tm = TensorMap()
         lib = _lib or require_extension()
         if lib.me_tma_encode_2d(tm.ptr, t.data_ptr(), t.shape[0], t.shape[1], t.stride(0) * 2, box_rows, 64, 128) != 0:
@@ -328,6 +366,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
     (K no multiple of 8) go to cuBLAS, as all the reference's products do through ``F.linear``
     (layers/linear.py:26,45), with SiLU-and-multiply as a kernel of ours behind it."""
     global library_calls
+    err_word = err if err is not None else _gemm_error_word(x.device)
+    key = ("linear", id(x), id(weight), id(out), epilogue)
+    sig = (x.data_ptr(), weight.data_ptr(), out.data_ptr(), err_word.data_ptr(), x.shape, x.stride(), x.dtype, weight.shape,
+           weight.stride(), weight.dtype, out.shape, out.stride(), out.dtype, use_tcgen05_gemm)
+    if _repeat(key, sig):
+        return
+    before = launches
     M, K = x.shape
     _need(weight.dim() == 2 and weight.shape[1] == K and weight.is_contiguous(), "linear: weight shape")
     _need(x.stride(1) == 1 and out.stride(1) == 1, "linear: rows must be contiguous")
@@ -339,9 +384,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
     if skinny_splits(M, K, x, weight) == 1 and (epi == 0 or out.dtype == torch.bfloat16):
         _call("me_gemm_skinny", x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), _dt(out), out.stride(0),
               0, M, N, K, epi, _stream())
+        _remember(key, sig, before)
         return
     if use_tcgen05_gemm and tcgen05_takes(x, weight) and (epi == 0 or out.dtype == torch.bfloat16):
-        linear_tcgen05(x, weight, out, epilogue, err if err is not None else _gemm_error_word(x.device))
+        linear_tcgen05(x, weight, out, epilogue, err_word)
+        _remember(key, sig, before)
         return
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.is_cuda:
         if epi == 0 and out.dtype == torch.bfloat16:
