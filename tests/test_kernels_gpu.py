@@ -239,6 +239,46 @@ def test_linear_rows_do_not_depend_on_the_batch(ops):
     assert torch.equal(full[41:42], one)
 
 
+def test_remembered_launches_follow_their_tensors(ops):
+    # a product or norm called again with the same tensors launches with last time's arguments: the result must
+    # follow the tensors' contents, and tensors of other shapes, kinds or places must not be taken for them
+    bf = torch.bfloat16
+    w = rnd(96, 64, dtype=bf, seed=2, scale=0.125)
+    x, out, ref = rnd(130, 64, dtype=bf, seed=1), torch.empty(130, 96, dtype=bf, device=DEV), torch.empty(130, 96, dtype=bf, device=DEV)
+    for seed in (1, 5, 9):                                   # same tensors, new contents: twice remembered
+        x.copy_(rnd(130, 64, dtype=bf, seed=seed))
+        ops.linear(x, w, out)
+        plain_ops.linear(x, w, ref)
+        close(out, ref, bf, scale=4)
+    before = ops.launches
+    ops.linear(x, w, out)
+    assert ops.launches == before + 1
+    for M, dt in ((130, torch.float32), (7, bf), (131, bf)):  # other kinds and sizes, some at the same addresses as before
+        del x, out, ref
+        x, w2 = rnd(M, 64, dtype=dt, seed=3), w.to(dt)
+        out, ref = torch.empty(M, 96, dtype=dt, device=DEV), torch.empty(M, 96, dtype=dt, device=DEV)
+        for _ in range(2):
+            out.fill_(float("nan"))
+            ops.linear(x, w2, out)
+            plain_ops.linear(x, w2, ref)
+            close(out, ref, dt, scale=4)
+    res, delta = rnd(70, 96, seed=4), rnd(70, 96, dtype=bf, seed=5)
+    nw, y, y_ref = 1 + 0.1 * rnd(96, seed=6), torch.empty(70, 96, dtype=bf, device=DEV), torch.empty(70, 96, dtype=bf, device=DEV)
+    res_ref = res.clone()
+    for _ in range(3):                                       # the residual grows each time: a stale launch would show
+        ops.add_rmsnorm(res, delta, nw, 1e-6, y)
+        plain_ops.add_rmsnorm(res_ref, delta, nw, 1e-6, y_ref)
+        close(res, res_ref, torch.float32, scale=8)
+        close(y, y_ref, bf, scale=4)
+    ops.remember_launches = False
+    try:
+        ops.add_rmsnorm(res, delta, nw, 1e-6, y)
+        plain_ops.add_rmsnorm(res_ref, delta, nw, 1e-6, y_ref)
+        close(y, y_ref, bf, scale=4)
+    finally:
+        ops.remember_launches = True
+
+
 # ---- q/k norm + rotary + cache write --------------------------------------------------------------
 @pytest.mark.parametrize("nh, nkv, hd", [(4, 2, 16), (8, 2, 32), (6, 3, 48), (16, 8, 128), (5, 5, 80), (2, 1, 256)])
 @pytest.mark.parametrize("dt", ["float32", "bfloat16"])
