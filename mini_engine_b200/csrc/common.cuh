@@ -79,6 +79,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
 bool me_pdl_enabled();
+int me_sm_count();          // SMs of the current device (asked once)
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t me_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

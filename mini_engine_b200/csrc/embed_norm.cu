@@ -195,10 +195,11 @@ __device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
 
 // Many rows (a portion of a prompt): a warp per row, every load of the row issued before the first is used, no
 // block-wide barrier.  H a multiple of 8 up to 256 * CH; the lane's chunks are elements 8 (lane + 32 i) .. + 7.
+// ``splits`` partial results ``split_stride`` elements apart are added in order.
 template <typename TD, typename TO, int CH>
 __global__ void __launch_bounds__(128)
 add_rmsnorm_rows_kernel(float* __restrict__ res, const TD* __restrict__ delta, const float* __restrict__ w, float eps,
-                        TO* __restrict__ out, int n_rows, int H) {
+                        TO* __restrict__ out, int n_rows, int H, int splits, int64_t split_stride) {
   const int lane = threadIdx.x & 31;
   const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   float ww[CH][8];
@@ -220,16 +221,33 @@ add_rmsnorm_rows_kernel(float* __restrict__ res, const TD* __restrict__ delta, c
       if (delta) load8(delta + r * H + h, d[i]);
     }
   }
+  if (delta) {
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      if (8 * (lane + 32 * i) < H) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += d[i][e];
+      }
+    }
+  }
+  for (int sp = 1; sp < splits; ++sp) {                 // the second and later partial results, in their order
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int h = 8 * (lane + 32 * i);
+      if (h < H) {
+        load8(delta + sp * split_stride + r * H + h, d[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += d[i][e];
+      }
+    }
+  }
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < CH; ++i) {
     const int h = 8 * (lane + 32 * i);
     if (h < H) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        if (delta) v[i][e] += d[i][e];
-        ss += v[i][e] * v[i][e];
-      }
+      for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
     }
   }
   ss = warp_sum(ss);
@@ -256,12 +274,13 @@ ME_API int me_add_rmsnorm(float* res, const void* delta, int delta_dtype, const 
   constexpr int NV = 8;
   // portions of prompts: a warp per row
   const bool aligned16 = (((uintptr_t)res | (uintptr_t)w | (uintptr_t)delta | (uintptr_t)out) & 15) == 0;
-  if (n_rows >= 64 && rows == nullptr && splits == 1 && H % 8 == 0 && H <= 2048 && aligned16) {
+  if (n_rows >= 64 && rows == nullptr && (splits == 1 || (delta != nullptr && split_stride % 4 == 0)) && H % 8 == 0 && H <= 2048 &&
+      aligned16) {
     const unsigned blocks = (unsigned)((n_rows + 3) / 4);
 #define ME_ROWS(CH_)                                                                                              \
     ME_DISPATCH_DTYPE(delta_dtype, TD, ME_DISPATCH_DTYPE(out_dtype, TO,                                           \
         (me_launch(add_rmsnorm_rows_kernel<TD, TO, CH_>, dim3(blocks), dim3(128), 0, stream, res, (const TD*)delta, w, eps, \
-                   (TO*)out, n_rows, H))))
+                   (TO*)out, n_rows, H, splits, split_stride))))
     if (H <= 256) ME_ROWS(1); else if (H <= 512) ME_ROWS(2); else if (H <= 1024) ME_ROWS(4); else ME_ROWS(8);
 #undef ME_ROWS
     ME_LAUNCH_CHECK("me_add_rmsnorm");

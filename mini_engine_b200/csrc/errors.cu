@@ -17,5 +17,13 @@ ME_API int me_abi_version() { return 1; }
 
 static bool g_pdl = true;
 bool me_pdl_enabled() { return g_pdl; }
+int me_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
 // Switch programmatic dependent launch on (default) or off for all later launches.
 ME_API void me_set_pdl(int on) { g_pdl = on != 0; }

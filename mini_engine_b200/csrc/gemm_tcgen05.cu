@@ -22,7 +22,9 @@ constexpr int TG_BM = 128, TG_BK = 64, TG_THREADS = 192;
 constexpr int TG_A_BYTES = TG_BM * TG_BK * 2;
 
 // Stages sized so that two blocks fit on an SM (about 96 KB each): one block's epilogue overlaps the other's main loop.
-template <int BN> constexpr int tg_stages() { return BN <= 64 ? 4 : (BN <= 128 ? 3 : 2); }
+// A grid of no more blocks than SMs has the SM to itself and takes twice the stages: what bounds these products
+// is the bytes a block has on their way from L2.
+template <int BN> constexpr int tg_stages(bool deep) { return (BN <= 64 ? 4 : (BN <= 128 ? 3 : 2)) * (deep ? 2 : 1); }
 
 // 32 consecutive results of one row: 16-byte stores where the row's place allows, else one by one.
 __device__ __forceinline__ void store_row32(bf16* dst, const float (&v)[32], int n_left, bool vec) {
@@ -53,11 +55,14 @@ __device__ __forceinline__ void store_row32(float* dst, const float (&v)[32], in
   }
 }
 
-template <int BN, int EPI, typename TO>
+// gridDim.z blocks share a tile: block z takes ``kb_per_split`` blocks of 64 along K from z * kb_per_split on and writes
+// its partial result ``split_stride`` elements after the one before (float32 results that the next kernel adds).
+template <int BN, int EPI, typename TO, bool DEEP>
 __global__ void __launch_bounds__(TG_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    TO* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err) {
-  constexpr int STAGES = tg_stages<BN>();
+                    TO* __restrict__ C, int64_t ldc, int M, int N, int K, int kb_per_split, int64_t split_stride,
+                    int* __restrict__ err) {
+  constexpr int STAGES = tg_stages<BN>(DEEP);
   constexpr int B_BYTES = BN * TG_BK * 2, STAGE_BYTES = TG_A_BYTES + B_BYTES;
   constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
   extern __shared__ unsigned char tg_smem_raw[];
@@ -66,7 +71,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   unsigned char* smem = tg_smem_raw + ((1024u - (tma::smem_addr(tg_smem_raw) & 1023u)) & 1023u);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * OUT_COLS;
-  const int num_kb = (K + TG_BK - 1) / TG_BK;
+  const int kb0 = blockIdx.z * kb_per_split;
+  const int num_kb = min(kb_per_split, (K + TG_BK - 1) / TG_BK - kb0);
+  C += blockIdx.z * split_stride;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -97,19 +104,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         unsigned char* b_dst = a_dst + TG_A_BYTES;
         tma::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
         if (EPI == 1) {
-          tma::load_2d(b_dst, &map_w, kb * TG_BK, n0, &full_bar[s]);
-          tma::load_2d(b_dst + B_BYTES / 2, &map_w, kb * TG_BK, N + n0, &full_bar[s]);
+          tma::load_2d(b_dst, &map_w, (kb0 + kb) * TG_BK, n0, &full_bar[s]);
+          tma::load_2d(b_dst + B_BYTES / 2, &map_w, (kb0 + kb) * TG_BK, N + n0, &full_bar[s]);
         } else {
-          tma::load_2d(b_dst, &map_w, kb * TG_BK, n0, &full_bar[s]);
+          tma::load_2d(b_dst, &map_w, (kb0 + kb) * TG_BK, n0, &full_bar[s]);
         }
         if (!waited && (kb == STAGES - 1 || kb == num_kb - 1)) {
           // first ring of weights requested: now wait for the predecessor and send the held-back A tiles
           pdl_wait();
           waited = true;
           for (int k2 = 0; k2 <= kb; ++k2)
-            tma::load_2d(smem + (k2 % STAGES) * STAGE_BYTES, &map_a, k2 * TG_BK, m0, &full_bar[k2 % STAGES]);
+            tma::load_2d(smem + (k2 % STAGES) * STAGE_BYTES, &map_a, (kb0 + k2) * TG_BK, m0, &full_bar[k2 % STAGES]);
         } else if (waited) {
-          tma::load_2d(a_dst, &map_a, kb * TG_BK, m0, &full_bar[s]);
+          tma::load_2d(a_dst, &map_a, (kb0 + kb) * TG_BK, m0, &full_bar[s]);
         }
       }
     }
@@ -169,48 +176,64 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 1) tc5::tmem_dealloc(tmem, BN < 32 ? 32 : BN);
 }
 
-template <int BN, int EPI, typename TO>
-int launch_tg(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, int* err, cudaStream_t stream) {
-  constexpr int STAGES = tg_stages<BN>();
+template <int BN, int EPI, typename TO, bool DEEP>
+int launch_tg(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, int splits, int64_t split_stride,
+              int* err, cudaStream_t stream) {
+  constexpr int STAGES = tg_stages<BN>(DEEP);
   const size_t smem = (size_t)STAGES * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, TO, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_gemm_tcgen05: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
-  dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (M + TG_BM - 1) / TG_BM);
-  me_launch(gemm_tcgen05_kernel<BN, EPI, TO>, grid, dim3(TG_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(map_a),
-            *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, err);
+  const int num_kb = (K + TG_BK - 1) / TG_BK, kb_per_split = (num_kb + splits - 1) / splits;
+  dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (M + TG_BM - 1) / TG_BM, (num_kb + kb_per_split - 1) / kb_per_split);
+  me_launch(gemm_tcgen05_kernel<BN, EPI, TO, DEEP>, grid, dim3(TG_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(map_a),
+            *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, kb_per_split, split_stride, err);
   return 0;
 }
 
 }  // namespace
+
+// How many partial results a product over K asked to be split ``splits`` ways writes (whole blocks of 64 along K each).
+ME_API int me_gemm_tcgen05_splits(int K, int splits) {
+  if (splits < 1) return 0;
+  const int num_kb = (K + TG_BK - 1) / TG_BK, per = (num_kb + splits - 1) / splits;
+  return (num_kb + per - 1) / per;
+}
 
 // Rows of W that one block's TMA box covers for a given tile width and epilogue (the caller encodes the map so).
 ME_API int me_gemm_tcgen05_w_box_rows(int bn, int epi) { return epi == 1 ? bn / 2 : bn; }
 
 // map_a: X as [M][K], boxes 128 x 64, 128-byte swizzle; map_w: W as [rows][K], boxes
 // me_gemm_tcgen05_w_box_rows(bn, epi) x 64.  N counts output columns (epi 1: W has 2N rows).
-// bn is the accumulator's width: 64, 128 or 256.
+// bn is the accumulator's width: 64, 128 or 256.  ``splits`` > 1: the K range is shared out over that many blocks a tile, whose
+// float32 partial results lie ``split_stride`` elements apart (me_gemm_tcgen05_splits says how many there will be).
 ME_API int me_gemm_tcgen05(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, int M, int N,
-                           int K, int epi, int bn, int* err, cudaStream_t stream) {
+                           int K, int epi, int bn, int splits, int64_t split_stride, int* err, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   ME_REQUIRE(M > 0 && N > 0 && K > 0 && K % 8 == 0, "me_gemm_tcgen05: bad sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
   ME_REQUIRE(map_a != nullptr && map_w != nullptr && err != nullptr, "me_gemm_tcgen05: tensor maps and the error word are required");
   ME_REQUIRE(epi == 0 || (epi == 1 && c_dtype == ME_BF16), "me_gemm_tcgen05: epilogue %d", epi);
   ME_REQUIRE((M + TG_BM - 1) / TG_BM <= 65535, "me_gemm_tcgen05: M=%d is too large", M);
+  ME_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (epi == 0 && c_dtype == ME_F32)),
+             "me_gemm_tcgen05: %d splits (they need float32 results and no epilogue)", splits);
+  ME_REQUIRE(bn == 64 || bn == 128 || bn == 256, "me_gemm_tcgen05: tile width %d is not 64, 128 or 256", bn);
+  const int out_cols = epi == 1 ? bn / 2 : bn;
+  const bool deep = (int64_t)((N + out_cols - 1) / out_cols) * ((M + TG_BM - 1) / TG_BM) * me_gemm_tcgen05_splits(K, splits) <= me_sm_count();
   int rc = 1;
 #define ME_TG_CASE(BN_)                                                                                              \
   if (bn == BN_) {                                                                                                   \
-    if (epi == 1) rc = launch_tg<BN_, 1, bf16>(map_a, map_w, C, ldc, M, N, K, err, stream);                          \
-    else if (c_dtype == ME_BF16) rc = launch_tg<BN_, 0, bf16>(map_a, map_w, C, ldc, M, N, K, err, stream);           \
-    else rc = launch_tg<BN_, 0, float>(map_a, map_w, C, ldc, M, N, K, err, stream);                                  \
+    if (epi == 1) rc = launch_tg<BN_, 1, bf16, false>(map_a, map_w, C, ldc, M, N, K, 1, 0, err, stream);             \
+    else if (c_dtype == ME_BF16) rc = deep ? launch_tg<BN_, 0, bf16, true>(map_a, map_w, C, ldc, M, N, K, 1, 0, err, stream)   \
+                                           : launch_tg<BN_, 0, bf16, false>(map_a, map_w, C, ldc, M, N, K, 1, 0, err, stream); \
+    else rc = deep ? launch_tg<BN_, 0, float, true>(map_a, map_w, C, ldc, M, N, K, splits, split_stride, err, stream)          \
+                   : launch_tg<BN_, 0, float, false>(map_a, map_w, C, ldc, M, N, K, splits, split_stride, err, stream);        \
   }
   ME_TG_CASE(64) ME_TG_CASE(128) ME_TG_CASE(256)
 #undef ME_TG_CASE
-  ME_REQUIRE(bn == 64 || bn == 128 || bn == 256, "me_gemm_tcgen05: tile width %d is not 64, 128 or 256", bn);
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_gemm_tcgen05");
   return 0;

@@ -61,6 +61,13 @@ def test_add_rmsnorm(ops, H, od, T):
         ops.add_rmsnorm(res, delta, w, 1e-5, out)
         assert torch.allclose(res, ref_res, atol=1e-6)
         close(out, ref_out, DT[od], scale=4)
+    # partial results of a product split along K: [splits, T, H] float32, added in order
+    res, parts = rnd(T, H, seed=6), rnd(3, T, H, seed=7)
+    ref_res = res.clone()
+    plain_ops.add_rmsnorm(ref_res, parts, w, 1e-5, ref_out)
+    ops.add_rmsnorm(res, parts, w, 1e-5, out)
+    assert torch.allclose(res, ref_res, atol=2e-6)
+    close(out, ref_out, DT[od], scale=4)
     # gathered rows: the residual is read, not written
     res, delta = rnd(T, H, seed=4), rnd(T, H, dtype=DT[od], seed=5)
     rows = torch.tensor([3, 0, 18, 3], dtype=torch.int32, device=DEV)
@@ -92,6 +99,30 @@ def test_linear(ops, M, N, K, kinds):
     ops.linear(x, w, out)
     plain_ops.linear(x, w, ref)
     close(out, ref, od, scale=4)
+
+
+@pytest.mark.parametrize("M, N, K", [(128, 1024, 2048), (300, 1000, 3072), (1024, 96, 1024), (520, 1024, 584)])
+def test_products_split_along_k(ops, M, N, K):
+    # the tcgen05 product with K shared out over several blocks a tile: float32 partial results that sum to the product
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5)
+    ref = torch.empty(M, N, device=DEV)
+    plain_ops.linear(x, w, ref)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    for bn in (64, 128, 256):
+        for want in (2, 3, 4):
+            n = ops.tcgen05_splits(K, want)
+            part = torch.full((n, M, N), float("nan"), device=DEV)
+            ops.linear_tcgen05(x, w, part, "none", err, tile_n=bn, splits=want if n == want else n)
+            close(part.sum(0), ref, torch.float32, scale=4)
+    assert err.tolist() == [0, 0, 0, 0]
+    # the engine's choice, through the call that a feed-forward or attention output makes
+    ws = {}
+    part = ops.linear_partials(x, w, lambda name, shape, dt: ws.setdefault(name, torch.full(shape, float("nan"), dtype=dt, device=DEV)), "p")
+    bn, parts = ops.tcgen05_split_plan(M, N, K)
+    assert (part is None) == (parts < 2)
+    if part is not None:
+        assert part.shape == (parts, M, N)
+        close(part.sum(0), ref, torch.float32, scale=4)
 
 
 @pytest.mark.parametrize("M, I, K", [(1, 128, 64), (37, 224, 96), (70, 200, 72), (8, 3072, 1024)])
