@@ -2,8 +2,9 @@
 //
 // Reference (layers/sampler.py:5-11): argmax where the temperature is 0, else
 // argmax(softmax(logits/T) / E), E ~ Exp(1), which picks the same token as
-// argmax(logits/T - log E).  E = -log(u), u in (0,1) from a counter-based hash of
-// (seed, position, vocabulary index), restated on the host in sampling/sampler.py.
+// argmax(logits/T - log E).  E = -log(u), u = (k + 0.5) / 2^23 with the 23-bit k from a counter-based hash of
+// (seed, position, vocabulary index), restated on the host in sampling/sampler.py.  (23 bits, not 24: k + 0.5 must
+// be exact in float32, or the largest k would round u to 1 and its entry would win with an infinite key.)
 // Ties go to the lower index.
 #include "common.cuh"
 
@@ -48,11 +49,30 @@ __device__ __forceinline__ void block_best(float& best, int& best_i) {
       }
 }
 
-// Pass 1: block (row, chunk) finds the best entry of its piece of the vocabulary.
+// The key of entry v at temperature T > 0: x / T - log(-log(u)), u from the hash of (p, v).
+__device__ __forceinline__ float noise_u(uint32_t p, int v) {
+  const uint32_t h = mix32((p ^ (uint32_t)v) + 0xC2B2AE35u);
+  return ((float)(h >> 9) + 0.5f) * (1.0f / 8388608.0f);      // 23 bits: k + 0.5 is exact in float32 and u stays inside (0, 1)
+}
+__device__ __forceinline__ float exact_key(float x, float T, uint32_t p, int v) { return x / T - logf(-logf(noise_u(p, v))); }
+// The same within 1e-4 (far less for keys of ordinary size) at a quarter of the instructions: the fast logarithm
+// (absolute error 2^-21.4 on [0.5, 2], 3 ulp elsewhere) would lose -log(u) for u near 1, where the winners are, so
+// there the series of -log(1 - d) stands in, d = 1 - u being exact.
+__device__ __forceinline__ float rough_key(float x, float inv_T, uint32_t p, int v) {
+  const float u = noise_u(p, v), d = 1.0f - u;
+  const float e = d < 0.03125f ? d * (1.0f + d * (0.5f + d * (0.33333334f + d * 0.25f))) : -__logf(u);
+  return fmaf(x, inv_T, -__logf(e));
+}
+
+// Pass 1: block (row, chunk) finds the best entry of its piece of the vocabulary.  With a temperature every thread
+// first takes the rough keys of its entries, then the exact keys of those within a margin of the best rough one
+// (one or two as a rule): the entry with the best exact key is always among them, so the draw is the one that exact
+// keys for all entries would give.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_partial_kernel(const float* __restrict__ logits, int64_t row_stride, const float* __restrict__ temperature,
                       const int* __restrict__ seeds, const int* __restrict__ positions,
                       float* __restrict__ part_key, int* __restrict__ part_idx, int V, int chunks) {
+  constexpr int PER_THREAD = SAMPLE_CHUNK / SAMPLE_THREADS;
   pdl_wait();
   pdl_launch_dependents();
   const int row = blockIdx.x, chunk = blockIdx.y;
@@ -62,17 +82,52 @@ sample_partial_kernel(const float* __restrict__ logits, int64_t row_stride, cons
   const uint32_t p = mix32((s ^ (uint32_t)positions[row]) + 0x85EBCA6Bu);
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  const int v_end = min(V, (chunk + 1) * SAMPLE_CHUNK);
-  for (int v = chunk * SAMPLE_CHUNK + threadIdx.x; v < v_end; v += SAMPLE_THREADS) {
-    float key = x[v];
-    if (T > 0.f) {
-      const uint32_t h = mix32((p ^ (uint32_t)v) + 0xC2B2AE35u);
-      const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
-      key = key / T - logf(-logf(u));
+  const int v0 = chunk * SAMPLE_CHUNK + threadIdx.x;
+  float xv[PER_THREAD];
+#pragma unroll
+  for (int i = 0; i < PER_THREAD; ++i) {
+    const int v = v0 + i * SAMPLE_THREADS;
+    xv[i] = v < V ? x[v] : -INFINITY;
+  }
+  if (T > 0.f) {
+    const float inv_T = 1.0f / T;
+    float rough[PER_THREAD], top = -INFINITY;
+    int i_top = -1;
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+      const int v = v0 + i * SAMPLE_THREADS;
+      rough[i] = v < V ? rough_key(xv[i], inv_T, p, v) : -INFINITY;
+      if (rough[i] > top) {
+        top = rough[i];
+        i_top = i;
+      }
     }
-    if (better(key, v, best, best_i)) {
-      best = key;
-      best_i = v;
+    // The exact key of the thread's best rough entry, all lanes at once (each for its own entry, read again: an index
+    // into registers that is not known at compile time would move them to memory); then, rarely, of the others near it.
+    if (i_top >= 0) {
+      best_i = v0 + i_top * SAMPLE_THREADS;
+      best = exact_key(x[best_i], T, p, best_i);
+    }
+    const float margin = 1e-3f + 2e-6f * fabsf(top);     // many times the rough keys' error, at any size of key
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+      const int v = v0 + i * SAMPLE_THREADS;
+      if (i != i_top && v < V && rough[i] >= top - margin) {
+        const float key = exact_key(xv[i], T, p, v);
+        if (better(key, v, best, best_i)) {
+          best = key;
+          best_i = v;
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+      const int v = v0 + i * SAMPLE_THREADS;
+      if (v < V && better(xv[i], v, best, best_i)) {
+        best = xv[i];
+        best_i = v;
+      }
     }
   }
   block_best(best, best_i);

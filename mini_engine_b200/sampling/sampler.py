@@ -33,7 +33,7 @@ def noise_uniform(seed: int, position: int, vocab_size: int) -> np.ndarray:
         s = _mix32(np.asarray([seed & 0xFFFFFFFF], dtype=np.uint32) + np.uint32(0x9E3779B9))
         p = _mix32((s ^ np.uint32(position & 0xFFFFFFFF)) + np.uint32(0x85EBCA6B))
         h = _mix32((p ^ v) + np.uint32(0xC2B2AE35))
-    return ((h >> np.uint32(8)).astype(np.float64) + 0.5) / 16777216.0
+    return ((h >> np.uint32(9)).astype(np.float64) + 0.5) / 8388608.0
 
 
 class Sampler:

@@ -155,7 +155,7 @@ def sample_keys(logits_row, temperature, seed, position):
         s = _mix32(np.asarray([seed & 0xFFFFFFFF], dtype=np.uint32) + np.uint32(0x9E3779B9))
         p = _mix32((s ^ np.uint32(position & 0xFFFFFFFF)) + np.uint32(0x85EBCA6B))
         h = _mix32((p ^ v) + np.uint32(0xC2B2AE35))
-    u = ((h >> np.uint32(8)).astype(np.float64) + 0.5) / 16777216.0
+    u = ((h >> np.uint32(9)).astype(np.float64) + 0.5) / 8388608.0
     return x / temperature - np.log(-np.log(u))
 
 

@@ -629,6 +629,19 @@ def test_sample(ops):
         assert keys[got[r]] >= keys.max() - 1e-4, f"row {r}"
         if float(temps[r]) == 0:
             assert got[r] == int(np.argmax(keys))
+    # a vocabulary of many pieces, keys of every size: the kernel takes exact keys only for the entries whose rough
+    # keys come near the best, which must never lose the winner; flat rows make thousands of near-ties
+    S2, V2 = 8, 151936
+    big = rnd(S2, V2, seed=11, scale=3.0)
+    big[6:] = 0.25
+    temps2 = torch.tensor([0.01, 0.05, 0.6, 1.0, 8.0, 100.0, 0.7, 1e-3], device=DEV)
+    seeds2 = torch.arange(21, 21 + S2, dtype=torch.int32, device=DEV)
+    pos2 = torch.arange(5, 5 + S2, dtype=torch.int32, device=DEV)
+    out_big = torch.empty(S2, dtype=torch.int32, device=DEV)
+    ops.sample(big, temps2, seeds2, pos2, out_big)
+    for r, g in enumerate(out_big.tolist()):
+        keys = plain_ops.sample_keys(big[r], float(temps2[r]), int(seeds2[r]), int(pos2[r]))
+        assert np.isfinite(keys).all() and keys[g] >= keys.max() - 1e-4 * max(1.0, abs(keys.max()) * 1e-3), f"row {r}"
     # the draw does not depend on the row's place in the batch
     out2 = torch.empty(1, dtype=torch.int32, device=DEV)
     ops.sample(logits[4:5], temps[4:5], seeds[4:5], pos[4:5], out2)

@@ -9,6 +9,10 @@ def test_noise_is_uniform_and_depends_on_every_key():
     u = noise_uniform(seed=1, position=7, vocab_size=50000)
     assert 0 < u.min() and u.max() < 1 and abs(u.mean() - 0.5) < 0.01
     assert abs(np.mean(u < 0.1) - 0.1) < 0.01
+    # 23 bits: every value is a float32 number as it stands (the kernel computes in float32), none of them 0 or 1
+    assert np.array_equal(u.astype(np.float32).astype(np.float64), u)
+    edge = (np.asarray([0, 2 ** 23 - 1], dtype=np.float64) + 0.5) / 8388608.0
+    assert 0 < np.float32(edge[0]) and np.float32(edge[1]) < 1 and np.array_equal(edge.astype(np.float32).astype(np.float64), edge)
     assert not np.array_equal(u, noise_uniform(2, 7, 50000))
     assert not np.array_equal(u, noise_uniform(1, 8, 50000))
     assert np.array_equal(u, noise_uniform(1, 7, 50000))
