@@ -46,9 +46,10 @@ class StepResult:
     tokens: Optional[torch.Tensor]     # [wanted] int32, drawn on the device when the step was asked to sample
 
 
-class _DecodeGraph:
-    """A captured decode step for a fixed number of requests and a bound on their contexts: its own context and
-    metadata; the work buffers are shared by the graphs of one batch bucket (they never run at the same time)."""
+class _StepGraph:
+    """A captured step of fixed shape: a decode step for a number of requests and a bound on their contexts, or one
+    request's portion of a prompt.  It has its own context and metadata; the work buffers are shared by the decode
+    graphs of one batch bucket (they never run at the same time), a prompt graph has its own."""
 
     def __init__(self, runner, bucket: int, arena: dict):
         self.bucket = bucket
@@ -121,9 +122,16 @@ class ModelRunner:
         # A decode step is replayed from a graph only if every part of the model allows it.
         self.use_cuda_graphs = (use_cuda_graphs and self.device.type == "cuda"
                                 and all(part.capturable for _, part in self.model.walk()))
-        self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
+        self._graphs: dict[tuple[int, int], _StepGraph] = {}
         self._graph_arenas: dict[int, dict] = {}
         self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256) if b <= max_num_seqs]
+        # A portion of one prompt, alone in its step, is replayed from a graph as well once its shape (tokens, wanted
+        # places) has come twice: the portions of a long prompt all have the step's token budget.  The host needs
+        # longer to launch such a step's kernels one by one than the device to run them, up to some 1,500 tokens.
+        self.prefill_graph_min_tokens = 128      # below, products go to the library and the step is short anyway
+        self.prefill_graph_max = 4               # graphs kept (each has work buffers of its own); the oldest goes first
+        self._prefill_graphs: dict[tuple, _StepGraph] = {}
+        self._prefill_seen: dict[tuple, int] = {}
         self.sample_tokens = torch.empty(max(max_num_seqs, 1), dtype=torch.int32, device=self.device)
         self.graph_launches = 0          # kernels replayed from graphs (they bypass ops.launches)
         self.last_h2d_bytes = 0
@@ -391,9 +399,63 @@ class ModelRunner:
             bucket = next((b for b in self.graph_buckets if b >= len(items)), None)
             if bucket is not None:
                 return self._step_graph(items, bucket, sample)
+        if self.use_cuda_graphs and len(items) == 1 and len(items[0].tokens) >= self.prefill_graph_min_tokens:
+            result = self._step_prefill_graph(items, sample)
+            if result is not None:
+                return result
         token_ids, _ = self.build_batch(items, self.ctx)
         logits, tokens = self._forward(token_ids, self.ctx, sample)
         return StepResult(logits, tokens)
+
+    def _capture(self, g: _StepGraph, token_ids: torch.Tensor, sample: bool) -> None:
+        """Run the step once eagerly (this allocates the graph's work buffers), then capture it; both runs do the
+        step's real work."""
+        g.ctx.frozen = False
+        self._forward(token_ids, g.ctx, sample)
+        torch.cuda.current_stream().synchronize()
+        g.ctx.frozen = True
+        before = ops.launches
+        graph = torch.cuda.CUDAGraph()
+        # Nothing may free device or pinned memory while the stream is capturing: Python's collector is
+        # paused, and calls that have nothing to do with the capture do not invalidate it.
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, capture_error_mode="relaxed"):
+                g.logits, g.tokens = self._forward(token_ids, g.ctx, sample)
+        finally:
+            gc.enable()
+        g.launches = ops.launches - before
+        g.graph = graph
+
+    def _step_prefill_graph(self, items: Sequence[StepItem], sample: bool) -> Optional[StepResult]:
+        """One request's portion of a prompt from a graph; None while the shape has not come twice.
+
+        Nothing that is launched for such a step depends on the request's context: the attention kernel's grid
+        follows from the number of query tiles, its loops from the lengths on the device.  So the key is the number
+        of tokens and of wanted places, and the block table has the width of the longest request there can be."""
+        item = items[0]
+        key = (len(item.tokens), len(item.want), bool(sample))
+        g = self._prefill_graphs.get(key)
+        if g is None:
+            seen = self._prefill_seen[key] = self._prefill_seen.get(key, 0) + 1
+            if seen < 2:
+                return None
+            while len(self._prefill_graphs) >= self.prefill_graph_max:
+                self._prefill_graphs.pop(next(iter(self._prefill_graphs)))
+            g = self._prefill_graphs[key] = _StepGraph(self, 0, {})
+        width = (self.max_model_len + self.page_size - 1) // self.page_size
+        if g.meta_dev is None:
+            T = len(item.tokens)
+            n = 8 * T + 64 + sum(T + width + 16 for _ in self.groups) + 8 * max(len(item.want), 1)
+            g.meta_dev = torch.zeros(n + 64, dtype=torch.int32, device=self.device)
+        token_ids, _ = self.build_batch(items, g.ctx, table_width=width, dev=g.meta_dev, fill_ctx=g.graph is None)
+        if g.graph is None:
+            self._capture(g, token_ids, sample)
+        g.graph.replay()
+        self.graph_launches += g.launches
+        if g.logits is None:
+            return StepResult(None, None)
+        return StepResult(g.logits, g.tokens if sample else None)
 
     def _step_graph(self, items: Sequence[StepItem], bucket: int, sample: bool) -> StepResult:
         """Decode-only steps replay a graph captured for the bucket: metadata goes to fixed device
@@ -419,7 +481,7 @@ class ModelRunner:
         g = self._graphs.get((bucket, ctx_bucket))
         if g is None:
             arena = self._graph_arenas.setdefault(bucket, {})
-            g = self._graphs[(bucket, ctx_bucket)] = _DecodeGraph(self, bucket, arena)
+            g = self._graphs[(bucket, ctx_bucket)] = _StepGraph(self, bucket, arena)
             # a buffer that has to grow (scratch sized by the context bucket) takes the bucket's other graphs with it
             g.ctx.on_replace = lambda name, b=bucket, keep=(bucket, ctx_bucket): [
                 self._graphs.pop(k) for k in list(self._graphs) if k[0] == b and k != keep]
@@ -430,23 +492,7 @@ class ModelRunner:
                                         fill_ctx=g.graph is None,
                                         typical_context=ctx_bucket * 3 // 4 if bucket < 32 else max(ctx_bucket - 128, 1))
         if g.graph is None:
-            # Once eagerly (allocates the work buffers), then captured; both runs do the step's real work.
-            g.ctx.frozen = False
-            self._forward(token_ids, g.ctx, True)
-            torch.cuda.current_stream().synchronize()
-            g.ctx.frozen = True
-            before = ops.launches
-            graph = torch.cuda.CUDAGraph()
-            # Nothing may free device or pinned memory while the stream is capturing: Python's collector is
-            # paused, and calls that have nothing to do with the capture do not invalidate it.
-            gc.disable()
-            try:
-                with torch.cuda.graph(graph, capture_error_mode="relaxed"):
-                    g.logits, g.tokens = self._forward(token_ids, g.ctx, True)
-            finally:
-                gc.enable()
-            g.launches = ops.launches - before
-            g.graph = graph
+            self._capture(g, token_ids, True)
         g.graph.replay()
         self.graph_launches += g.launches
         n = self.last_num_wanted

@@ -161,3 +161,40 @@ def test_steps_launched_ahead_of_the_host_change_nothing(dtype):
     llm.scheduler.eos = eos
     out = llm.generate([prompts[2]], SamplingParams(temperature=0.8, max_tokens=lens[2], seed=9), use_tqdm=False)
     assert out[0]["token_ids"] == plain_eos[2] and llm.steps_ahead_dropped == 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_prompt_portions_replayed_from_a_graph_change_nothing(name, dtype):
+    # one request's portions of equal size: the first runs eagerly, the second is captured, the others are replayed
+    # (at other contexts than the captured one, past a window, on other pages); a second request reuses the graph
+    from mini_engine_b200.cache.manager import CacheHolder
+    from mini_engine_b200.engine.model_runner import ModelRunner, StepItem
+    T, portions = 130, 3
+    rng = np.random.default_rng(5)
+    vocab = ALL[name][0]["vocab_size"]
+
+    def run(graphs, prompts):
+        runner = ModelRunner(helpers.model_folder(name), dtype=dtype, page_size=ALL[name][2], num_pages=64, max_num_seqs=4,
+                             max_num_batched_tokens=256, max_model_len=512, use_cuda_graphs=graphs)
+        cache = runner.make_cache_manager(False)
+        rows = []
+        for prompt in prompts:
+            h = CacheHolder()
+            assert cache.allocate(h, len(prompt))
+            for k in range(portions):
+                want = [T - 1] if k == portions - 1 else [0, T - 1]     # two shapes: each comes often enough to be captured
+                out = runner.step([StepItem(h, prompt[k * T:(k + 1) * T], k * T, want)])
+                rows.append(out.logits.float().cpu().numpy().copy())
+            cache.free(h)
+        runner.check_device_errors()
+        return runner, rows
+
+    prompts = [rng.integers(0, vocab, size=T * portions).tolist() for _ in range(3)]
+    runner, got = run(True, prompts)
+    assert runner.use_cuda_graphs and len(runner._prefill_graphs) == 2 and runner.graph_launches > 0
+    _, eager = run(False, prompts)
+    for a, b in zip(got, eager):
+        assert np.array_equal(a, b)                                     # the same kernels on the same numbers
+    ref = helpers.plain_logits(name, prompts[2])
+    assert np.abs(got[-1][0] - ref[T * portions - 1]).max() <= helpers.TOL[dtype]
