@@ -399,7 +399,8 @@ class ModelRunner:
             bucket = next((b for b in self.graph_buckets if b >= len(items)), None)
             if bucket is not None:
                 return self._step_graph(items, bucket, sample)
-        if self.use_cuda_graphs and len(items) == 1 and len(items[0].tokens) >= self.prefill_graph_min_tokens:
+        if (self.use_cuda_graphs and len(items) == 1 and len(items[0].tokens) >= self.prefill_graph_min_tokens
+                and len(items[0].want) <= 8):            # (a graph keeps its own logits: not for replays that want every place)
             result = self._step_prefill_graph(items, sample)
             if result is not None:
                 return result
