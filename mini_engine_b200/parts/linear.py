@@ -17,7 +17,6 @@ class Linear(Part):
 
     capturable = True
 
-
     def __init__(self, in_features: int, pieces: Sequence[tuple[str, int]], name: str = "weight"):
         super().__init__()
         self.in_features = in_features
