@@ -198,3 +198,34 @@ def test_prompt_portions_replayed_from_a_graph_change_nothing(name, dtype):
         assert np.array_equal(a, b)                                     # the same kernels on the same numbers
     ref = helpers.plain_logits(name, prompts[2])
     assert np.abs(got[-1][0] - ref[T * portions - 1]).max() <= helpers.TOL[dtype]
+
+
+def test_prompt_graphs_are_few_and_the_oldest_goes_first():
+    # more shapes than graphs are kept: the oldest is dropped, comes back by a new capture, and results stay the eager ones
+    from mini_engine_b200.cache.manager import CacheHolder
+    from mini_engine_b200.engine.model_runner import ModelRunner, StepItem
+    name, dtype = "D", "bfloat16"
+    vocab = ALL[name][0]["vocab_size"]
+    rng = np.random.default_rng(9)
+    sizes = [128, 129, 130, 131, 132, 133]
+    prompts = {T: rng.integers(0, vocab, size=T).tolist() for T in sizes}
+
+    def run(graphs):
+        runner = ModelRunner(helpers.model_folder(name), dtype=dtype, page_size=ALL[name][2], num_pages=64, max_num_seqs=4,
+                             max_num_batched_tokens=256, max_model_len=256, use_cuda_graphs=graphs)
+        cache = runner.make_cache_manager(False)
+        rows = []
+        for T in sizes + sizes + sizes[:2] + sizes[:2]:
+            h = CacheHolder()
+            assert cache.allocate(h, T)
+            rows.append(runner.step([StepItem(h, prompts[T], 0, [T - 1])]).logits.float().cpu().numpy().copy())
+            cache.free(h)
+        runner.check_device_errors()
+        return runner, rows
+
+    runner, got = run(True)
+    assert len(runner._prefill_graphs) == runner.prefill_graph_max == 4
+    assert list(runner._prefill_graphs)[-2:] == [(128, 1, False), (129, 1, False)]       # dropped, then captured anew
+    _, eager = run(False)
+    for a, b in zip(got, eager):
+        assert np.array_equal(a, b)
