@@ -28,12 +28,24 @@ def _load_tokenizer(folder: str):
     return AutoTokenizer.from_pretrained(folder, use_fast=True)
 
 
+class _NoEvent:
+    """Stands in for a CUDA event where the runner is not on a CUDA device (host-side tests with a fake runner)."""
+
+    def record(self):
+        pass
+
+    def synchronize(self):
+        pass
+
+
 class LLMEngine:
     def __init__(self, model: str, **kwargs):
         names = {f.name for f in fields(EngineConfig)}
         config = EngineConfig(model, **{k: v for k, v in kwargs.items() if k in names})
         self.config = config
-        self.model_runner = ModelRunner(
+        # ``model_runner=``: an object with ModelRunner's surface (step, result_dev, token_feedback, error_flag,
+        # make_cache_manager, ...) in place of the real one; host-side tests drive the engine's loop with a fake.
+        self.model_runner = kwargs.get("model_runner") or ModelRunner(
             config.model, dtype=config.dtype, page_size=config.kvcache_block_size,
             num_pages=config.num_kvcache_blocks, max_num_seqs=config.max_num_seqs,
             max_num_batched_tokens=config.max_num_batched_tokens, max_model_len=config.max_model_len,
@@ -45,8 +57,9 @@ class LLMEngine:
             config.eos = self.tokenizer.eos_token_id        # engine/llm_engine.py:19
         self.cache = self.model_runner.make_cache_manager(config.enable_prefix_caching)
         self.scheduler = Scheduler(config, self.cache)
-        self._result_pins = [torch.empty(config.max_num_seqs + 4, dtype=torch.int32, pin_memory=True) for _ in range(3)]
-        self._result_events = [torch.cuda.Event() for _ in range(3)]
+        on_gpu = self.model_runner.device.type == "cuda"
+        self._result_pins = [torch.empty(config.max_num_seqs + 4, dtype=torch.int32, pin_memory=on_gpu) for _ in range(3)]
+        self._result_events = [torch.cuda.Event() if on_gpu else _NoEvent() for _ in range(3)]
         self._turn = 0
         self._ahead = None                 # (requests, handle) of a step that is already running on the device
         self.steps_ahead_used = 0          # steps launched ahead of the host whose results were kept ...
@@ -114,13 +127,20 @@ class LLMEngine:
             tokens[i] = got[4 + r]
         return tokens
 
-    def _launch_ahead(self, seqs):
+    def _launch_ahead(self, seqs, handle):
         """The step that follows a decode step of ``seqs`` if nothing unforeseen happens; None if it is not worth
-        or not possible to guess."""
+        or not possible to guess.  ``handle`` is the launched step of ``seqs``: it knows in which row of the
+        device's result each request's token lies (the rows of a kept guess are those of the batch that was
+        guessed, which may hold requests that have ended since)."""
         if not self.config.overlap_steps or self.scheduler.waiting:
+            return None
+        if self.model_runner.state_needs:
+            # A dropped guess is harmless only because keys and values are written again by the real step; a mixer
+            # with state of its own would have advanced that state twice.
             return None
         if any(s.num_scheduled_tokens != 1 or not s.samples_this_step for s in seqs):
             return None
+        row_of = dict(zip(handle["for"] if "for" in handle else handle["rows"], handle["take"]))
         ahead, items = [], []
         for j, s in enumerate(seqs):
             if s.num_completion_tokens + 1 >= s.sampling_params.max_tokens or len(s) + 1 >= self.config.max_model_len:
@@ -128,7 +148,7 @@ class LLMEngine:
             if not self.cache.allocate(s, 2):        # room for the token after the one being drawn; nobody is evicted for a guess
                 return None
             ahead.append(s)
-            items.append(StepItem(s, [~j], len(s), [0], (s.sampling_params.temperature, self._seed_of(s))))
+            items.append(StepItem(s, [~row_of[j]], len(s), [0], (s.sampling_params.temperature, self._seed_of(s))))
         if not ahead:
             return None
         return ahead, self._launch(ahead, items)
@@ -142,7 +162,7 @@ class LLMEngine:
             handle = self._launch(seqs)
         num_decode = sum(1 for s in seqs if s.num_scheduled_tokens == 1)
         num_prefill = sum(s.num_scheduled_tokens for s in seqs if s.num_scheduled_tokens > 1)
-        guess = self._launch_ahead(seqs)
+        guess = self._launch_ahead(seqs, handle)
         tokens = self._collect(seqs, handle)
         emitted = self.scheduler.postprocess(seqs, tokens)
         if guess is not None:

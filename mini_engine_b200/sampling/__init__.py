@@ -1,2 +1,2 @@
 from .params import SamplingParams
-from .sampler import Sampler, noise_uniform
+from .sampler import noise_uniform

@@ -1,4 +1,4 @@
-"""Greedy and temperature sampling on the device.
+"""Greedy and temperature sampling on the device (the kernels of csrc/sampler.cu, called by the step function).
 
 Reference (layers/sampler.py:5-11): logits in float32; greedy = argmax where the
 temperature is 0; else ``argmax(softmax(logits / T) / E)`` with E ~ Exp(1) per entry (an
@@ -11,9 +11,6 @@ on how its prompt was cut; ``noise_uniform`` restates the hash on the host for t
 from __future__ import annotations
 
 import numpy as np
-import torch
-
-from .. import ops
 
 
 def _mix32(x: np.ndarray) -> np.ndarray:
@@ -34,13 +31,3 @@ def noise_uniform(seed: int, position: int, vocab_size: int) -> np.ndarray:
         p = _mix32((s ^ np.uint32(position & 0xFFFFFFFF)) + np.uint32(0x85EBCA6B))
         h = _mix32((p ^ v) + np.uint32(0xC2B2AE35))
     return ((h >> np.uint32(9)).astype(np.float64) + 0.5) / 8388608.0
-
-
-class Sampler:
-    def __call__(self, logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,
-                 positions: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """logits [S, V] float32; temperatures [S] float32; seeds, positions [S] int32 -> tokens [S] int32."""
-        if out is None:
-            out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        ops.sample(logits, temperatures, seeds, positions, out)
-        return out
