@@ -85,6 +85,7 @@ class CacheManager:
         self.state_slots = StateSlotPool(num_state_slots)
         self.prefix_caching = bool(enable_prefix_caching and not has_state and self.groups
                                    and all(g.window is None for g in self.groups))
+        self.num_prefix_hit_tokens = 0          # tokens that requests found in the cache instead of computing them
 
     # ---- sizes -----------------------------------------------------------------------
     @property
@@ -169,6 +170,7 @@ class CacheManager:
         if n_hit:
             holder.num_computed_tokens = computed
             holder.num_cached_tokens += n_hit * ps
+            self.num_prefix_hit_tokens += n_hit * ps
             holder.num_hashed_blocks += n_hit
         if need_slot:
             holder.state_slot = self.state_slots.acquire()

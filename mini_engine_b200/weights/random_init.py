@@ -48,12 +48,15 @@ def random_state_dict(model: DecoderModel, seed: int, dtype: torch.dtype = torch
 
 
 def write_random_model(folder: str, config: dict[str, Any], seed: int,
-                       dtype: torch.dtype = torch.bfloat16) -> str:
-    """Write ``config.json`` and ``model.safetensors`` into ``folder``; returns the folder."""
+                       dtype: torch.dtype = torch.bfloat16, matrix_std: float = 0.02, norm_std: float = 0.1) -> str:
+    """Write ``config.json`` and ``model.safetensors`` into ``folder``; returns the folder.
+
+    ``matrix_std``: with wider matrices (0.1, say) what the layers add to the residual stream outweighs the token's
+    own embedding, so the next token depends on the cache far more than on the token itself."""
     folder = os.path.expanduser(folder)
     os.makedirs(folder, exist_ok=True)
     _, model = build_model_from_config_dict(config)
-    tensors = random_state_dict(model, seed, dtype)
+    tensors = random_state_dict(model, seed, dtype, matrix_std, norm_std)
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(config, f, indent=1)
     save_file(tensors, os.path.join(folder, "model.safetensors"))

@@ -17,13 +17,25 @@ from mini_engine_b200.weights import write_random_model
 TOL = {"float32": 5e-5, "bfloat16": 3e-2}
 
 
+# "A" is the tiny configuration A with the usual random weights N(0, 0.02).  "A!" is the same configuration with
+# matrices N(0, 0.1): what the layers add to the residual stream then outweighs a token's own embedding and the
+# logits spread over several units, so a wrong input token, a stale page or a wrong key changes the next token.
+def _std_of(name: str) -> float:
+    return 0.1 if name.endswith("!") else 0.02
+
+
+def config_of(name: str):
+    from tiny_configs import ALL
+    return ALL[name.rstrip("!")]
+
+
 @functools.lru_cache(maxsize=None)
 def model_folder(name: str, dtype: str = "bfloat16") -> str:
     """A temporary model folder for a tiny configuration (made once per session, never committed)."""
-    from tiny_configs import ALL
-    cfg, seed, _ = ALL[name]
-    d = tempfile.mkdtemp(prefix=f"me_tiny_{name}_")
-    return write_random_model(d, cfg, seed, dtype={"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype])
+    cfg, seed, _ = config_of(name)
+    d = tempfile.mkdtemp(prefix=f"me_tiny_{name.rstrip('!')}_")
+    return write_random_model(d, cfg, seed, dtype={"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype],
+                              matrix_std=_std_of(name))
 
 
 @functools.lru_cache(maxsize=None)

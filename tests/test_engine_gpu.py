@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 def _llm(name, dtype, **kw):
     from mini_engine_b200 import LLM
-    args = dict(dtype=dtype, kvcache_block_size=ALL[name][2], num_kvcache_blocks=64, max_num_seqs=8,
+    args = dict(dtype=dtype, kvcache_block_size=helpers.config_of(name)[2], num_kvcache_blocks=64, max_num_seqs=8,
                 max_num_batched_tokens=64, max_model_len=256)
     args.update(kw)
     return LLM(helpers.model_folder(name), **args)
@@ -22,18 +22,19 @@ def _llm(name, dtype, **kw):
 def _check_greedy(name, dtype, prompt, tokens):
     """Every generated token is the plain implementation's argmax, or within the tolerance of it."""
     ref = helpers.plain_logits(name, list(prompt) + list(tokens))
+    tol = 2 * helpers.TOL[dtype] * max(1.0, float(np.abs(ref).max()))
     for k, t in enumerate(tokens):
         row = ref[len(prompt) + k - 1]
-        assert row[t] >= row.max() - 2 * helpers.TOL[dtype], f"token {k}: {t} is not the plain argmax {row.argmax()}"
+        assert row[t] >= row.max() - tol, f"token {k}: {t} is not the plain argmax {row.argmax()}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "B!", "D!"])
 def test_greedy_generation(name, dtype):
     from mini_engine_b200 import SamplingParams
     llm = _llm(name, dtype)
     lengths = (5, 17, 33, 9) if name == "A" else (3, 40, 21, 12)
-    prompts = helpers.random_requests(ALL[name][0]["vocab_size"], lengths, seed=2)
+    prompts = helpers.random_requests(helpers.config_of(name)[0]["vocab_size"], lengths, seed=2)
     out = llm.generate(prompts, SamplingParams(temperature=0, max_tokens=8), use_tqdm=False)
     assert [len(o["token_ids"]) for o in out] == [8] * len(prompts)
     for p, o in zip(prompts, out):
@@ -55,6 +56,7 @@ def test_temperature_sampling_with_shared_prefix_and_small_budget(dtype):
     prompts[4] = prompts[1][:16] + prompts[4]
     sps = [SamplingParams(temperature=0.7, max_tokens=6, seed=100 + i, ignore_eos=True) for i in range(6)]
     out = llm.generate(prompts, sps, use_tqdm=False)
+    assert llm.cache.num_prefix_hit_tokens >= 16                # the shared prefix was found, not computed again
     margin = 2 * helpers.TOL[dtype] / 0.7
     for i, (p, o) in enumerate(zip(prompts, out)):
         ref = helpers.plain_logits(name, list(p) + o["token_ids"])
@@ -69,16 +71,46 @@ def test_temperature_sampling_with_shared_prefix_and_small_budget(dtype):
         assert [o["token_ids"] for o in out2] == [o["token_ids"] for o in out]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_tokens_behind_a_shared_prefix(dtype):
+    """Weights under which the next token hangs on every key in the cache: requests that find their first pages in
+    the cache (while the request that wrote them lives, and after it has ended) draw the plain implementation's
+    tokens."""
+    from mini_engine_b200 import SamplingParams
+    name = "B!"
+    vocab = helpers.config_of(name)[0]["vocab_size"]
+    base, t1, t2, other = helpers.random_requests(vocab, (29, 7, 12, 40), seed=8)
+    # Budget 40, three at a time: the first step holds all of request 0 and four tokens of request 1; request 2 is
+    # admitted in the second step, while request 0 lives, and finds its three pages; request 3 comes when a request has
+    # ended and finds two pages that may have been freed.
+    prompts = [base + t1, other, base + t2, base[:17] + t1]
+    sp = SamplingParams(temperature=0, max_tokens=8, ignore_eos=True)
+    llm = _llm(name, dtype, max_num_batched_tokens=40, max_num_seqs=3)
+    out = llm.generate(prompts, sp, use_tqdm=False)
+    assert llm.cache.num_prefix_hit_tokens >= 24 + 16                       # 3 and 2 pages of 8 tokens
+    for p, o in zip(prompts, out):
+        _check_greedy(name, dtype, p, o["token_ids"])
+    if dtype == "float32":
+        cfg, w = helpers.plain_weights(name)
+        for p, o in zip(prompts, out):
+            assert o["token_ids"] == plain_model.greedy_generate(cfg, w, p, 8)
+    off = _llm(name, dtype, max_num_batched_tokens=40, max_num_seqs=3, enable_prefix_caching=False)
+    assert off.generate(prompts, sp, use_tqdm=False) == out or dtype == "bfloat16"
+    assert off.cache.num_prefix_hit_tokens == 0
+
+
 def test_running_out_of_pages_preempts_and_gives_the_same_tokens():
     from mini_engine_b200 import SamplingParams
-    name = "A"
-    prompts = helpers.random_requests(ALL[name][0]["vocab_size"], (40, 40, 25), seed=4)
+    name = "A!"
+    prompts = helpers.random_requests(helpers.config_of(name)[0]["vocab_size"], (40, 40, 25), seed=4)
     sp = SamplingParams(temperature=0, max_tokens=30, ignore_eos=True)
     roomy = _llm(name, "float32", num_kvcache_blocks=64).generate(prompts, sp, use_tqdm=False)
     tight = _llm(name, "float32", num_kvcache_blocks=7, max_num_batched_tokens=128)
     out = tight.generate(prompts, sp, use_tqdm=False)
     assert tight.scheduler.num_preemptions > 0
     assert [o["token_ids"] for o in out] == [o["token_ids"] for o in roomy]
+    cfg, w = helpers.plain_weights(name)
+    assert out[2]["token_ids"] == plain_model.greedy_generate(cfg, w, prompts[2], 30)
     tight.cache.check([])
     assert tight.cache.num_free_pages == [7]
 
@@ -122,8 +154,8 @@ def test_steps_launched_ahead_of_the_host_change_nothing(dtype):
     guessed batch), with an end-of-sequence token that ends requests unforeseen (their rows of the guessed step
     are ignored), and with a request that arrives while others decode (the guessed step is dropped)."""
     from mini_engine_b200 import SamplingParams
-    name = "B"
-    vocab = ALL[name][0]["vocab_size"]
+    name = "B!"                # the next token hangs on the token fed and on the cache: a neighbour's token shows
+    vocab = helpers.config_of(name)[0]["vocab_size"]
     prompts = helpers.random_requests(vocab, (3, 40, 17, 29, 9), seed=5)
     lens = [12, 5, 20, 9, 16]
 
@@ -131,7 +163,8 @@ def test_steps_launched_ahead_of_the_host_change_nothing(dtype):
         llm = _llm(name, dtype, overlap_steps=overlap)
         if eos is not None:
             llm.scheduler.eos = eos
-        sps = [SamplingParams(temperature=0.8, max_tokens=n, seed=7 + i, ignore_eos=eos is None) for i, n in enumerate(lens)]
+        sps = [SamplingParams(temperature=0.8 if i % 2 else 0.0, max_tokens=n, seed=7 + i, ignore_eos=eos is None)
+               for i, n in enumerate(lens)]
         ids = [llm.add_request(p, sp) for p, sp in zip(prompts, sps)]
         done, steps = {}, 0
         while not llm.is_finished():
@@ -146,12 +179,17 @@ def test_steps_launched_ahead_of_the_host_change_nothing(dtype):
     plain, llm0 = run(False)
     ahead, llm1 = run(True)
     assert ahead == plain
+    for i in (0, 2, 4):                                           # the greedy ones against the plain implementation
+        _check_greedy(name, dtype, prompts[i], ahead[i])
     assert llm0.steps_ahead_used == 0 and llm1.steps_ahead_used > 5
     # an end-of-sequence token taken from the middle of a completion: requests now end where the host cannot foresee it
-    eos = plain[2][6]
+    k = next(k for k in range(4, len(plain[2])) if plain[2][k] not in plain[2][:k])
+    eos = plain[2][k]
     plain_eos, _ = run(False, eos=eos)
     ahead_eos, llm2 = run(True, eos=eos)
-    assert ahead_eos == plain_eos and any(len(a) < n for a, n in zip(plain_eos, lens))
+    assert ahead_eos == plain_eos and len(plain_eos[2]) == k + 1
+    assert any(len(plain_eos[i]) > k + 3 for i in (3, 4))         # a request behind it in the batch goes on
+    _check_greedy(name, dtype, prompts[4], ahead_eos[4])
     # a request that arrives in the middle: the scheduler then wants a different step than the one guessed
     plain_late, _ = run(False, late=6)
     ahead_late, _ = run(True, late=6)
@@ -159,7 +197,7 @@ def test_steps_launched_ahead_of_the_host_change_nothing(dtype):
     # a request alone that ends on its end-of-sequence token: the step guessed behind its last one is dropped
     llm = _llm(name, dtype)
     llm.scheduler.eos = eos
-    out = llm.generate([prompts[2]], SamplingParams(temperature=0.8, max_tokens=lens[2], seed=9), use_tqdm=False)
+    out = llm.generate([prompts[2]], SamplingParams(temperature=0.0, max_tokens=lens[2], seed=9), use_tqdm=False)
     assert out[0]["token_ids"] == plain_eos[2] and llm.steps_ahead_dropped == 1
 
 
