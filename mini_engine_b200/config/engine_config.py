@@ -29,6 +29,7 @@ class EngineConfig:
     enable_prefix_caching: bool = True
     seed: int = 0
     use_cuda_graphs: bool = True
+    random_weights: bool = False        # the folder holds config.json only: weights are drawn on the device from ``seed``
     overlap_steps: bool = True          # launch the likely next decode step before reading the current one's tokens
 
     def __post_init__(self):

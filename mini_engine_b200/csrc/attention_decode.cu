@@ -14,7 +14,6 @@
 #include "common.cuh"
 #include "mma_prims.cuh"
 #include "tma.cuh"
-#include "tcgen05.cuh"
 
 constexpr int DEC_PART = 128, DEC_THREADS = 128, DEC_LANES = 8, DEC_GROUPS = DEC_THREADS / DEC_LANES;
 
@@ -172,232 +171,6 @@ decode_partition_kernel(const T* __restrict__ qkv, int64_t q_row_stride, const T
       tmp_l[slot] = lt;
     }
   }
-}
-
-// ---- the same partition step with the keys and values brought in by bulk copies ----------------
-// A page of one key/value head is one contiguous piece of memory ([page][k|v][kv_head][offset][head_dim]),
-// so one thread issues a cp.async.bulk per page for K and for V into shared memory, all of the
-// partition's copies at once (two stages of 64 keys, an mbarrier each), and the block computes from
-// shared memory as the stages land.  bfloat16, head_dim <= 128, page sizes 8, 16, 32, 64.
-constexpr int DEC_STAGE = 64, DEC_STAGES = DEC_PART / DEC_STAGE;
-constexpr unsigned DEC_WAIT_LIMIT = 1u << 22;      // polls of an mbarrier before the kernel gives up
-
-__device__ __forceinline__ uint32_t dec_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t phase) {
-  for (unsigned i = 0; i < DEC_WAIT_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(done) : "r"(bar), "r"(phase) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-template <int GT, int CH>
-__global__ void __launch_bounds__(DEC_THREADS)
-decode_partition_tma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, const bf16* __restrict__ pool,
-                            const int* __restrict__ block_tables, int bt_stride,
-                            const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
-                            int nh, int nkv, int hd, int page_size, float scale, int window,
-                            float* __restrict__ tmp_out, float* __restrict__ tmp_m,
-                            float* __restrict__ tmp_l, int max_parts, int* __restrict__ err) {
-  extern __shared__ __align__(128) unsigned char dec_smem[];
-  __shared__ __align__(8) unsigned long long bars[DEC_STAGES];
-  pdl_wait();
-  pdl_launch_dependents();
-  const int G = nh / nkv, head_tiles = (G + GT - 1) / GT;
-  const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * GT;
-  const int z = blockIdx.z;
-  const int L = context_lens[b];
-  const int tid = threadIdx.x, kg = tid / DEC_LANES, lg = tid % DEC_LANES;
-  const int n_g = min(GT, G - g0);
-  const int lo_w = window > 0 ? max(0, L - window) : 0;
-  const int part_lo = z * DEC_PART, part_hi = min(L, part_lo + DEC_PART);
-  const int64_t slot0 = ((int64_t)b * nh + kvh * G + g0) * max_parts + z;
-  if (part_hi <= part_lo || part_hi <= lo_w) {
-    if (part_lo < L || z == 0)
-      for (int g = tid; g < n_g; g += DEC_THREADS) {
-        tmp_m[slot0 + (int64_t)g * max_parts] = -INFINITY;
-        tmp_l[slot0 + (int64_t)g * max_parts] = 0.f;
-      }
-    return;
-  }
-  bf16* k_s = reinterpret_cast<bf16*>(dec_smem);                  // [DEC_PART][hd]
-  bf16* v_s = k_s + DEC_PART * hd;                                // [DEC_PART][hd]
-  float* q_s = reinterpret_cast<float*>(v_s + DEC_PART * hd);     // [GT][hd], scaled
-  float* s_m = q_s + GT * hd;
-  float* s_l = s_m + DEC_GROUPS * GT;
-  float* s_acc = s_l + DEC_GROUPS * GT;                           // [DEC_GROUPS][GT][hd]
-  const int* bt = block_tables + (int64_t)b * bt_stride;
-  if (tid == 0) {
-#pragma unroll
-    for (int s = 0; s < DEC_STAGES; ++s)
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(dec_smem_u32(&bars[s])));
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    const unsigned page_bytes = (unsigned)(page_size * hd * sizeof(bf16));
-    const int64_t v_off = (int64_t)nkv * page_size * hd;
-    const int pages_per_stage = DEC_STAGE / page_size;
-#pragma unroll
-    for (int s = 0; s < DEC_STAGES; ++s) {
-      const uint32_t bar = dec_smem_u32(&bars[s]);
-      const int key0 = part_lo + s * DEC_STAGE;
-      unsigned bytes = 0;
-      int pages[DEC_STAGE / 8];
-      for (int i = 0; i < pages_per_stage; ++i) {
-        const int j0 = key0 + i * page_size;                       // first key of the page
-        int page = -1;
-        if (j0 < part_hi && j0 + page_size > lo_w) page = bt[j0 / page_size];
-        pages[i] = page;
-        if (page >= 0) bytes += 2 * page_bytes;
-      }
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-      for (int i = 0; i < pages_per_stage; ++i) {
-        if (pages[i] < 0) continue;
-        const bf16* src = pool + (((int64_t)pages[i] * 2) * nkv + kvh) * page_size * hd;
-        const int row = s * DEC_STAGE + i * page_size;
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                     ::"r"(dec_smem_u32(k_s + row * hd)), "l"(src), "r"(page_bytes), "r"(bar) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                     ::"r"(dec_smem_u32(v_s + row * hd)), "l"(src + v_off), "r"(page_bytes), "r"(bar) : "memory");
-      }
-    }
-  }
-  const int64_t tok = cu_seqlens[b];
-  for (int idx = tid; idx < GT * hd; idx += DEC_THREADS) {
-    const int g = idx / hd, d = idx - g * hd;
-    q_s[idx] = g < n_g ? to_f<bf16>(qkv[tok * q_row_stride + (int64_t)(kvh * G + g0 + g) * hd + d]) * scale : 0.f;
-  }
-  __syncthreads();                                                 // barriers initialised, q in place
-
-  float m[GT], l[GT], acc[GT][CH][8];
-#pragma unroll
-  for (int g = 0; g < GT; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int u = 0; u < CH; ++u)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[g][u][e] = 0.f;
-  }
-  const unsigned gmask = 0xFFu << ((tid & 31) & ~7);
-  bool gave_up = false;
-#pragma unroll 1
-  for (int s = 0; s < DEC_STAGES; ++s) {
-    if (part_lo + s * DEC_STAGE >= part_hi) break;
-    if (!mbar_wait(dec_smem_u32(&bars[s]), 0)) {
-      gave_up = true;
-      break;
-    }
-#pragma unroll 2
-    for (int jj = s * DEC_STAGE + kg; jj < (s + 1) * DEC_STAGE; jj += DEC_GROUPS) {
-      const int j = part_lo + jj;
-      if (j >= part_hi || j < lo_w) continue;
-      if (bt[j / page_size] < 0) continue;
-      float kx[CH][8], vx[CH][8];
-#pragma unroll
-      for (int u = 0; u < CH; ++u) {
-        const int d0 = (lg + DEC_LANES * u) * 8;
-        if (d0 < hd) {
-          Vec8<bf16>::load(k_s + jj * hd + d0, kx[u]);
-          Vec8<bf16>::load(v_s + jj * hd + d0, vx[u]);
-        }
-      }
-#pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        float dot = 0.f;
-#pragma unroll
-        for (int u = 0; u < CH; ++u) {
-          const int d0 = (lg + DEC_LANES * u) * 8;
-          if (d0 < hd) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) dot = fmaf(q_s[g * hd + d0 + e], kx[u][e], dot);
-          }
-        }
-#pragma unroll
-        for (int o = 1; o < DEC_LANES; o <<= 1) dot += __shfl_xor_sync(gmask, dot, o);
-        const float m_new = fmaxf(m[g], dot);
-        const float alpha = expf(m[g] - m_new), p = expf(dot - m_new);
-        l[g] = l[g] * alpha + p;
-        m[g] = m_new;
-#pragma unroll
-        for (int u = 0; u < CH; ++u) {
-          const int d0 = (lg + DEC_LANES * u) * 8;
-          if (d0 < hd) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[g][u][e] = fmaf(p, vx[u][e], acc[g][u][e] * alpha);
-          }
-        }
-      }
-    }
-  }
-  if (gave_up) {
-    // A copy did not land within the limit: report it, wait (bounded) for what is still in flight so that
-    // no copy writes into memory the next block owns, and leave this partition empty.
-    if (tid == 0) atomicOr(err + 1, 1);
-    for (int s = 0; s < DEC_STAGES; ++s)
-      if (part_lo + s * DEC_STAGE < part_hi) mbar_wait(dec_smem_u32(&bars[s]), 0);
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      m[g] = -INFINITY;
-      l[g] = 0.f;
-    }
-  }
-#pragma unroll
-  for (int g = 0; g < GT; ++g) {
-    if (lg == 0) {
-      s_m[kg * GT + g] = m[g];
-      s_l[kg * GT + g] = l[g];
-    }
-#pragma unroll
-    for (int u = 0; u < CH; ++u) {
-      const int d0 = (lg + DEC_LANES * u) * 8;
-      if (d0 < hd) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) s_acc[((int64_t)kg * GT + g) * hd + d0 + e] = acc[g][u][e];
-      }
-    }
-  }
-  __syncthreads();
-  for (int idx = tid; idx < n_g * hd; idx += DEC_THREADS) {
-    const int g = idx / hd, d = idx - g * hd;
-    float M = -INFINITY;
-    for (int k = 0; k < DEC_GROUPS; ++k) M = fmaxf(M, s_m[k * GT + g]);
-    float lt = 0.f, o = 0.f;
-    if (M > -INFINITY) {
-      for (int k = 0; k < DEC_GROUPS; ++k) {
-        const float mk = s_m[k * GT + g];
-        const float f = mk == -INFINITY ? 0.f : expf(mk - M);
-        lt += f * s_l[k * GT + g];
-        o += f * s_acc[((int64_t)k * GT + g) * hd + d];
-      }
-    }
-    const int64_t slot = slot0 + (int64_t)g * max_parts;
-    tmp_out[slot * hd + d] = o;
-    if (d == 0) {
-      tmp_m[slot] = M;
-      tmp_l[slot] = lt;
-    }
-  }
-}
-
-template <int GT, int CH>
-static int launch_partition_tma(dim3 grid, cudaStream_t stream, const void* qkv, int64_t q_row_stride, const void* pool,
-                                const int* bt, int bt_stride, const int* cu, const int* cl, int nh, int nkv, int hd,
-                                int page_size, float scale, int window, float* to, float* tm, float* tl, int max_parts,
-                                int* err) {
-  const size_t smem = (size_t)2 * DEC_PART * hd * sizeof(bf16) +
-                      sizeof(float) * ((size_t)GT * hd + 2 * DEC_GROUPS * GT + (size_t)DEC_GROUPS * GT * hd);
-  static size_t attr = 0;
-  if (smem > attr) {
-    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_kernel<GT, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
-    attr = smem;
-  }
-  me_launch(decode_partition_tma_kernel<GT, CH>, grid, dim3(DEC_THREADS), smem, stream,
-      (const bf16*)qkv, q_row_stride, (const bf16*)pool, bt, bt_stride, cu, cl, nh, nkv, hd, page_size, scale, window,
-      to, tm, tl, max_parts, err);
-  return 0;
 }
 
 // ---- the partition step on the tensor cores -----------------------------------------------------
@@ -659,19 +432,15 @@ struct DecodePrep {
   bf16* pool;                 // the cache slot, [page][k|v][kv_head][offset][HD]
 };
 
-// TC5: the two products run on the 5th-generation tensor cores.  The partition's 128 keys are the M side:
-// S^T [keys][16 heads] = K Q^T (eight tcgen05.mma of K 16, operands straight from the tiles the copy engine
-// wrote, accumulator in tensor memory); a thread then owns a key (tcgen05.ld), the softmax runs across threads,
-// P^T goes to shared memory as a K-major operand, and O^T [head_dim][16 heads] = V^T P^T takes V as an MN-major
-// operand, so that a thread ends up owning an output column.  Without TC5: mma.sync m16n8k16 with ldmatrix.
-// VBUF (mma.sync form only) says how much shared memory V has of its own: 2 a whole tile (three blocks an SM); 0
+// The two products are mma.sync m16n8k16 with ldmatrix.
+// VBUF says how much shared memory V has of its own: 2 a whole tile (three blocks an SM); 0
 // none: V passes through K's tile, requested once every warp has its scores (six blocks an SM with an 8-row Q tile:
 // a block lives one load longer, but more of them are loading at any time: large batches); 1 half a tile: the
 // first 64 keys' values come with K, the other 64 pass through K's tile (four blocks an SM: a batch of 8 at 1,000
 // tokens then fits the GPU in one wave with most of its loads in flight before the dependency resolves).
 // With at most 8 query heads a group the Q tile keeps 8 rows (the upper half of the m16 strip reads one chunk of
 // zeros), and with VBUF 0 the registers are held to what lets six blocks share an SM.
-template <int HD, bool FUSED, bool TC5, int VBUF, int QROWS>
+template <int HD, bool FUSED, int VBUF, int QROWS>
 __global__ void __launch_bounds__(DEC_THREADS, (VBUF == 0 && QROWS == 8) ? 6 : 1)
 decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ qkv,
                                 int64_t q_row_stride, const int* __restrict__ block_tables, int bt_stride,
@@ -682,8 +451,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   using namespace mma_prims;
   extern __shared__ unsigned char dec_smem_raw[];
   __shared__ float w_m[4][16], w_l[4][16];
-  __shared__ __align__(8) unsigned long long bar_k, bar_v, bar_v2, bar_s, bar_o;
-  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) unsigned long long bar_k, bar_v, bar_v2;
   __shared__ __align__(16) bf16 zero_chunk[8];
   constexpr int PIECES = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, HALVES = HD / 64;
   const int G = nh / nkv, head_tiles = (G + 15) / 16;
@@ -727,11 +495,8 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     }
     return tma::swz128(vs + (piece >> 3) * DEC_PART * 64, row, piece & 7);
   };
-  // Element i of row ``row`` of the Q tile: for mma.sync a [16][HD] tile with XOR-swizzled pieces, for tcgen05 a
-  // K-major operand as the copy engine would have written it (blocks of [16 rows][64], 128-byte swizzle).
-  auto q_at = [&](int row, int i) -> bf16* {
-    return TC5 ? tma::swz128(qs + (i >> 6) * 16 * 64, row, (i & 63) >> 3) + (i & 7) : tile_ptr<HD>(qs, row, i >> 3) + (i & 7);
-  };
+  // Element i of row ``row`` of the Q tile: a [16][HD] tile with XOR-swizzled pieces.
+  auto q_at = [&](int row, int i) -> bf16* { return tile_ptr<HD>(qs, row, i >> 3) + (i & 7); };
   const int64_t tok = cu_seqlens[b];
   // Only the partition that holds the request's newest key depends on the kernel before this one (which
   // wrote that key); the others fetch their keys and values while that kernel is still running.  A block
@@ -749,13 +514,8 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     tma::mbar_init(&bar_k, 1);
     tma::mbar_init(&bar_v, 1);
     tma::mbar_init(&bar_v2, 1);
-    if (TC5) {
-      tma::mbar_init(&bar_s, 1);
-      tma::mbar_init(&bar_o, 1);
-    }
     tma::mbar_fence_init();
   }
-  if (TC5 && warp == 1) tc5::tmem_alloc(&tmem_slot, 32);          // S^T in columns 0..15, O^T in 16..31
   // A tensor-map copy is issued per thread, so the lanes of one warp issue the partition's boxes together: lane i
   // looks up page i, lane 0 announces the bytes, then box x = ((k|v) * HALVES + half) * pages + page goes out from
   // lane x % 32.
@@ -864,12 +624,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     cp_async_commit();
     cp_async_wait<0>();
   }
-  if (TC5) {
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // Q, written by threads, is read by the tensor core
-    tc5::fence_before_sync();
-  }
-  __syncthreads();                                   // barriers initialised, Q in place, tensor memory allocated
-  if (TC5) tc5::fence_after_sync();
+  __syncthreads();                                   // barriers initialised, Q in place
   bool landed = tma::mbar_wait(&bar_k, 0);
   // The newest key and value go to their row of the tiles (over whatever the slot held) and to the cache.
   auto put_new = [&](bf16* tile, int kv) {
@@ -894,91 +649,10 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   if (makes_new) {
     if (warp == 0) {
       put_new(ks, 0);
-      if (TC5) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     __syncthreads();                                 // the row is in place before any warp reads K
   }
   const float sl2 = scale * 1.4426950408889634f;
-  if (TC5) {
-    const uint32_t tmem = tmem_slot;
-    // ---- S^T = K Q^T: one thread issues, the accumulator's lanes are the keys
-    if (tid == 0) {
-      constexpr uint32_t idesc = tc5::instr_desc_bf16(DEC_PART, 16);
-#pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) {
-        const uint64_t a = tc5::smem_desc_k_major_sw128(ks + (kk >> 2) * DEC_PART * 64) + 2 * (kk & 3);
-        const uint64_t bq = tc5::smem_desc_k_major_sw128(qs + (kk >> 2) * 16 * 64) + 2 * (kk & 3);
-        tc5::mma_f16(tmem, a, bq, idesc, kk > 0);
-      }
-      tc5::commit(&bar_s);
-    }
-    landed = tma::mbar_wait(&bar_s, 0) && landed;
-    tc5::fence_after_sync();
-    float sc[16];
-    tc5::ld_16cols(tmem + ((uint32_t)(warp * 32) << 16), sc);
-    tc5::wait_ld();
-    const int j = part_lo + tid;                     // this thread's key
-    const bool live = j < part_hi && j >= lo_w;
-    // the maximum of every head over the 128 keys: lanes, then warps
-#pragma unroll
-    for (int h = 0; h < 16; ++h) {
-      if (h >= n_g) break;
-      const float mx = warp_max(live ? sc[h] : -INFINITY);
-      if (lane == 0) w_m[warp][h] = mx;
-    }
-    __syncthreads();                                 // (every thread has read its scores: Q may be overwritten by P)
-    bf16* ps = qs;                                   // P^T [16 heads][128 keys] as a K-major operand: two blocks of [16][64]
-#pragma unroll
-    for (int h = 0; h < 16; ++h) {
-      if (h >= n_g) break;
-      const float M = fmaxf(fmaxf(w_m[0][h], w_m[1][h]), fmaxf(w_m[2][h], w_m[3][h]));
-      const float p = live ? exp2f((sc[h] - (M == -INFINITY ? 0.f : M)) * sl2) : 0.f;
-      const float sum = warp_sum(p);
-      if (lane == 0) w_l[warp][h] = sum;
-      *(tma::swz128(ps + (tid >> 6) * 16 * 64, h, (tid & 63) >> 3) + (tid & 7)) = __float2bfloat16_rn(p);
-    }
-    landed = tma::mbar_wait(&bar_v, 0) && landed;
-    if (makes_new && warp == 1) put_new(vs, 1);
-    if (!live)                                       // rows of V that are no keys of this request: zero (0 * NaN is NaN)
-      for (int p = 0; p < PIECES; ++p)
-        *reinterpret_cast<uint4*>(tma::swz128(vs + (p >> 3) * DEC_PART * 64, tid, p & 7)) = make_uint4(0, 0, 0, 0);
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P and the touched rows of V, for the tensor core
-    tc5::fence_before_sync();
-    __syncthreads();
-    tc5::fence_after_sync();
-    // ---- O^T = V^T P^T: V is the MN-major operand (head_dim is M), the accumulator's lanes are output columns
-    if (tid == 0) {
-      static_assert(!TC5 || HD == 128, "the tcgen05 form needs head_dim 128 (an accumulator of 128 lanes)");
-      constexpr uint32_t idesc = tc5::instr_desc_bf16(128, 16, false, true);
-#pragma unroll
-      for (int kk = 0; kk < DEC_PART / 16; ++kk) {
-        const uint64_t a = tc5::smem_desc_mn_major_sw128(reinterpret_cast<unsigned char*>(vs) + kk * 2048, DEC_PART * 64 * 2);
-        const uint64_t bp = tc5::smem_desc_k_major_sw128(ps + (kk >> 2) * 16 * 64) + 2 * (kk & 3);
-        tc5::mma_f16(tmem + 16, a, bp, idesc, kk > 0);
-      }
-      tc5::commit(&bar_o);
-    }
-    landed = tma::mbar_wait(&bar_o, 0) && landed;
-    tc5::fence_after_sync();
-    {
-      float oc[16];
-      tc5::ld_16cols(tmem + 16 + ((uint32_t)(warp * 32) << 16), oc);
-      tc5::wait_ld();
-#pragma unroll
-      for (int h = 0; h < 16; ++h)
-        if (h < n_g) tmp_out[(slot0 + (int64_t)h * max_parts) * HD + tid] = oc[h];
-    }
-    if (tid < n_g) {
-      const float M = fmaxf(fmaxf(w_m[0][tid], w_m[1][tid]), fmaxf(w_m[2][tid], w_m[3][tid]));
-      tmp_m[slot0 + (int64_t)tid * max_parts] = M == -INFINITY ? -INFINITY : M * scale;
-      tmp_l[slot0 + (int64_t)tid * max_parts] = ((w_l[0][tid] + w_l[1][tid]) + w_l[2][tid]) + w_l[3][tid];
-    }
-    if (!landed && tid == 0) atomicOr(err + 1, 1);
-    tc5::fence_before_sync();
-    __syncthreads();
-    if (warp == 1) tc5::tmem_dealloc(tmem, 32);
-    return;
-  }
   const int mi = lane >> 3;
   float s[4][4];
 #pragma unroll
@@ -1096,7 +770,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   }
 }
 
-template <int HD, bool FUSED, bool TC5, int VBUF, int QROWS>
+template <int HD, bool FUSED, int VBUF, int QROWS>
 static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_parts, cudaStream_t stream, const void* qkv,
                                     int64_t q_row_stride, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
                                     int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int* err,
@@ -1104,13 +778,13 @@ static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_pa
   const size_t smem = (size_t)(QROWS + DEC_PART + VBUF * DEC_PART / 2) * HD * sizeof(bf16) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, TC5, VBUF, QROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, VBUF, QROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   const int G = nh / nkv;
   dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
-  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, TC5, VBUF, QROWS>, grid, dim3(DEC_THREADS), smem, stream,
+  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, VBUF, QROWS>, grid, dim3(DEC_THREADS), smem, stream,
       *reinterpret_cast<const CUtensorMap*>(kv_map), (const bf16*)qkv, q_row_stride, bt, bt_stride, cu, cl, nh, nkv, page_size,
       scale, window, to, tm, tl, max_parts, err, prep);
   return 0;
@@ -1241,23 +915,20 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   ME_REQUIRE((int64_t)nkv * head_tiles <= 65535, "me_attn_decode: too many heads");
   dim3 grid(num_reqs, nkv * head_tiles, max_parts);
   const size_t smem = sizeof(float) * ((size_t)GT * hd + 2 * DEC_GROUPS * GT + (size_t)DEC_GROUPS * GT * hd);
-  // kind: 0 = the fastest kernel that takes the shape, 1 = CUDA cores, 2 = CUDA cores fed by bulk copies,
+  // kind: 0 = the fastest kernel that takes the shape, 1 = CUDA cores,
   // 3 = tensor cores fed by cp.async, 4 = tensor cores fed by tensor-map loads (needs ``kv_map``, made by
   // me_tma_encode_2d over the cache slot: rows = pages * 2 * kv_heads * page_size, boxes page_size x 64).
   const bool mma_ok = dtype == ME_BF16 && (hd == 64 || hd == 128);
   const bool tma_mma_ok = mma_ok && kv_map != nullptr && err != nullptr && page_size >= 8 && DEC_PART % page_size == 0;
-  const bool bulk_ok = dtype == ME_BF16 && hd <= 128 && err != nullptr &&
-                       (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
-  ME_REQUIRE(kind >= 0 && kind <= 4 && (kind != 4 || tma_mma_ok) && (kind != 3 || mma_ok) && (kind != 2 || bulk_ok),
+  ME_REQUIRE(kind >= 0 && kind <= 4 && kind != 2 && (kind != 4 || tma_mma_ok) && (kind != 3 || mma_ok),
              "me_attn_decode: kernel kind %d does not take this shape", kind);
   const bool tma_mma = kind == 4 || (kind == 0 && tma_mma_ok);
   const bool mma = !tma_mma && (kind == 3 || (kind == 0 && mma_ok));
-  const bool tma = kind == 2;
   if (tma_mma) {
     const DecodePrep none = {};
-    int rc = hd == 64 ? launch_partition_tma_mma<64, false, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+    int rc = hd == 64 ? launch_partition_tma_mma<64, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none)
-                      : launch_partition_tma_mma<128, false, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
+                      : launch_partition_tma_mma<128, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                              cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none);
     if (rc) return rc;
   }
@@ -1270,18 +941,8 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
     if (rc) return rc;
   }
   const bool simt = !tma_mma && !mma;
-#define ME_DEC_TMA_CASE(GT_, CH_)                                                                   \
-  if (simt && tma && GT == GT_ && CH == CH_) {                                                              \
-    int rc = launch_partition_tma<GT_, CH_>(grid, stream, qkv, q_row_stride, pool, block_tables,    \
-        bt_stride, cu_seqlens, context_lens, nh, nkv, hd, page_size, scale, window, tmp_out, tmp_m, \
-        tmp_l, max_parts, err);                                                                     \
-    if (rc) return rc;                                                                              \
-  }
-  ME_DEC_TMA_CASE(1, 1) ME_DEC_TMA_CASE(2, 1) ME_DEC_TMA_CASE(4, 1)
-  ME_DEC_TMA_CASE(1, 2) ME_DEC_TMA_CASE(2, 2) ME_DEC_TMA_CASE(4, 2)
-#undef ME_DEC_TMA_CASE
 #define ME_DEC_CASE(GT_, CH_)                                                                       \
-  if (simt && !tma && GT == GT_ && CH == CH_) {                                                             \
+  if (simt && GT == GT_ && CH == CH_) {                                                             \
     ME_DISPATCH_DTYPE(dtype, T, (launch_partition<T, GT_, CH_>(grid, smem, stream, qkv, q_row_stride, \
         pool, block_tables, bt_stride, cu_seqlens, context_lens, nh, nkv, hd, page_size, scale,     \
         window, tmp_out, tmp_m, tmp_l, max_parts)));                                                \
@@ -1310,8 +971,7 @@ ME_API int me_attn_decode_fused_takes(int hd, int page_size) {
 // (token row = cu_seqlens[request], position = context_lens[request] - 1).  q_weight/k_weight (both or neither), cos_sin and slot_mapping may be
 // null; with a null slot_mapping the newest key and value are expected in the cache already.  The q rows of
 // ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.  form (of the partition kernel):
-// 0 mma.sync with K and V through one tile, 1 tcgen05 (head_dim 128), 2 mma.sync with a tile each, 3 mma.sync with
-// half a tile for V beside K's.
+// 0 K and V through one tile, 2 a tile each, 3 half a tile for V beside K's.
 ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out, int64_t out_row_stride, void* pool,
                                 const void* kv_map, const int* block_tables, int bt_stride, const int* cu_seqlens,
                                 const int* context_lens, int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
@@ -1328,21 +988,20 @@ ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out
   const int G = nh / nkv;
   ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode_fused: too many heads");
   DecodePrep prep = {q_weight, k_weight, eps, cos_sin, slot_mapping, (bf16*)pool};
-  ME_REQUIRE(form >= 0 && form <= 3 && (form != 1 || hd == 128), "me_attn_decode_fused: form %d (the tcgen05 form takes head_dim 128)", form);
+  ME_REQUIRE(form == 0 || form == 2 || form == 3, "me_attn_decode_fused: unknown form %d", form);
   int rc = 1;
-#define ME_FUSED(HD_, TC_, VBUF_, Q_)                                                                                    \
-  rc = launch_partition_tma_mma<HD_, true, TC_, VBUF_, Q_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, \
+#define ME_FUSED(HD_, VBUF_, Q_)                                                                                    \
+  rc = launch_partition_tma_mma<HD_, true, VBUF_, Q_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, \
                                                            bt_stride, cu_seqlens, context_lens, nh, nkv, page_size, scale, window, \
                                                            tmp_out, tmp_m, tmp_l, err, prep)
   const bool few_heads = G <= 8;                     // a group's query heads fit the lower half of the m16 strip
   ME_REQUIRE(form != 3 || (DEC_PART / 2) % page_size == 0, "me_attn_decode_fused: pages of %d do not fit half a partition", page_size);
 #define ME_FUSED_Q(HD_, VBUF_)                                                                                           \
-  do { if (few_heads) ME_FUSED(HD_, false, VBUF_, 8); else ME_FUSED(HD_, false, VBUF_, 16); } while (0)
-  if (form == 1) ME_FUSED(128, true, 2, 16);
-  else if (hd == 64 && form == 2) ME_FUSED(64, false, 2, 16);
+  do { if (few_heads) ME_FUSED(HD_, VBUF_, 8); else ME_FUSED(HD_, VBUF_, 16); } while (0)
+  if (hd == 64 && form == 2) ME_FUSED(64, 2, 16);
   else if (hd == 64 && form == 3) ME_FUSED_Q(64, 1);
   else if (hd == 64) ME_FUSED_Q(64, 0);
-  else if (form == 2) ME_FUSED(128, false, 2, 16);
+  else if (form == 2) ME_FUSED(128, 2, 16);
   else if (form == 3) ME_FUSED_Q(128, 1);
   else ME_FUSED_Q(128, 0);
 #undef ME_FUSED_Q

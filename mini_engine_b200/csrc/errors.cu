@@ -25,5 +25,6 @@ int me_sm_count() {
   }
   return n;
 }
+ME_API int me_device_sm_count() { return me_sm_count(); }
 // Switch programmatic dependent launch on (default) or off for all later launches.
 ME_API void me_set_pdl(int on) { g_pdl = on != 0; }

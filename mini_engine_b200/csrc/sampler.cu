@@ -190,7 +190,10 @@ static void* sample_static_scratch_of_current_device(int* device_out) {
   static void* ptrs[MAX_DEVICES] = {};
   static std::mutex lock;
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    me_set_error("me_sample_static: no usable CUDA device is current");
+    return nullptr;
+  }
   *device_out = dev;
   std::lock_guard<std::mutex> guard(lock);
   if (ptrs[dev] == nullptr) {
@@ -214,7 +217,6 @@ ME_API int me_sample_static(const float* logits, int64_t row_stride, const float
   ME_REQUIRE(V <= ME_SAMPLE_STATIC_MAX_VOCAB, "me_sample_static: vocabulary %d, the built-in work buffer holds %d; use me_sample()",
              V, ME_SAMPLE_STATIC_MAX_VOCAB);
   int dev = -1;
-  me_set_error("me_sample_static: no usable CUDA device is current");
   void* scratch = sample_static_scratch_of_current_device(&dev);
   if (scratch == nullptr) return 1;
   const int chunks = me_sample_chunks(V);

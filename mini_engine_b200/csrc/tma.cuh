@@ -26,9 +26,9 @@ __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t phase) {
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t phase, unsigned limit = WAIT_LIMIT) {
   const uint32_t a = smem_addr(bar);
-  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+  for (unsigned i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                  : "=r"(done) : "r"(a), "r"(phase) : "memory");

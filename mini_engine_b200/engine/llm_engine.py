@@ -50,7 +50,7 @@ class LLMEngine:
             num_pages=config.num_kvcache_blocks, max_num_seqs=config.max_num_seqs,
             max_num_batched_tokens=config.max_num_batched_tokens, max_model_len=config.max_model_len,
             gpu_memory_utilization=config.gpu_memory_utilization, use_cuda_graphs=config.use_cuda_graphs,
-            model_config=config.model_config)
+            model_config=config.model_config, random_weights_seed=config.seed if config.random_weights else None)
         config.num_kvcache_blocks = self.model_runner.num_pages
         self.tokenizer = _load_tokenizer(config.model)
         if self.tokenizer is not None and self.tokenizer.eos_token_id is not None:
@@ -66,6 +66,7 @@ class LLMEngine:
         self.steps_ahead_dropped = 0       # ... and those the scheduler decided otherwise about
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self.num_steps = 0                 # steps whose results were used (a dropped guess is not one)
 
     # ---- requests --------------------------------------------------------------------
     def add_request(self, prompt: str | Seq[int], sampling_params: SamplingParams, priority: int = 0) -> int:
@@ -154,6 +155,7 @@ class LLMEngine:
         return ahead, self._launch(ahead, items)
 
     def step(self):
+        self.num_steps += 1
         if self._ahead is not None:
             seqs, handle = self._ahead               # launched during the call before this one
             self._ahead = None

@@ -26,6 +26,7 @@ from ..config.registry import get_architecture, load_model_config
 from ..parts.base import KVCacheNeed, StateNeed
 from ..parts.model import DecoderModel
 from ..weights.loader import load_weights
+from ..weights.random_init import init_random_on_device
 from .step_context import AttnMeta, HostMeta, StepContext
 
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -85,7 +86,8 @@ class ModelRunner:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", page_size: int = 16,
                  num_pages: int = -1, max_num_seqs: int = 512, max_num_batched_tokens: int = 16384,
                  max_model_len: int = 4096, gpu_memory_utilization: float = 0.9,
-                 use_cuda_graphs: bool = True, device: str = "cuda:0", model_config=None):
+                 use_cuda_graphs: bool = True, device: str = "cuda:0", model_config=None,
+                 random_weights_seed: Optional[int] = None):
         ops.require_extension()                      # fails loudly when the kernels cannot be had
         self.device = torch.device(device)
         self.act_dtype = _TORCH_DTYPE[dtype]
@@ -96,7 +98,10 @@ class ModelRunner:
         self.max_model_len = min(max_model_len, self.model_config.max_position_embeddings)
         arch = get_architecture(self.model_config.architecture)
         self.model = DecoderModel(arch.plan(self.model_config))
-        load_weights(self.model, model_dir, self.act_dtype, self.device)
+        if random_weights_seed is None:
+            load_weights(self.model, model_dir, self.act_dtype, self.device)
+        else:                                        # the folder holds a config.json only
+            init_random_on_device(self.model, random_weights_seed, self.act_dtype, self.device)
         self.model.finalize_all(self.act_dtype, self.device)
         self.vocab_size = self.model.plan.vocab_size
 

@@ -37,6 +37,7 @@ _PROTOS = {
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
+    "me_test_wait_expires": [_P, _I, _P, _P],
 }
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -89,13 +90,42 @@ def library_file() -> str:
 _fns: dict = {}
 _last_call = None         # (entry point, arguments) of the launch before
 
+# Per-kernel timing for the benchmark's roofline table: while ``timeline`` is a list, every launch made through
+# this module is bracketed by two CUDA events and recorded as (tag, entry point, start, end).  ``tag`` is set by
+# the caller that knows what the launch is for (a Linear part sets it to its output's name).  An event between
+# two launches keeps the second from starting under the first (programmatic dependent launch), so these are the
+# times of kernels run one after the other, not shares of a step replayed from a graph.
+timeline: Optional[list] = None
+tag = ""
+
+
+class _Timed:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if timeline is not None:
+            self.e0, self.e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if timeline is not None:
+            self.e1.record()
+            timeline.append((tag, self.name, self.e0, self.e1))
+
 
 def _call(name: str, *args) -> None:
     global launches, _last_call
     fn = _fns.get(name)
     if fn is None:
         fn = _fns[name] = getattr(_lib or require_extension(), name)
-    if fn(*args) != 0:
+    if timeline is not None:
+        with _Timed(name):
+            rc = fn(*args)
+    else:
+        rc = fn(*args)
+    if rc != 0:
         raise KernelError(_lib.me_last_error().decode())
     launches += 1
     _last_call = (fn, args)
@@ -111,7 +141,7 @@ remember_launches = True  # False: every wrapper runs in full every time (a swit
 
 def _repeat(key, sig) -> bool:
     global launches
-    hit = _repeats.get(key) if remember_launches else None
+    hit = _repeats.get(key) if remember_launches and timeline is None else None
     if hit is None or hit[0] != sig:
         return False
     if hit[1](*hit[2], _stream()) != 0:
@@ -126,6 +156,13 @@ def _remember(key, sig, launches_before: int) -> None:
         if len(_repeats) > 16384:
             _repeats.clear()
         _repeats[key] = (sig, _last_call[0], _last_call[1][:-1])
+
+
+def forget_tensors() -> None:
+    """Drop everything remembered about tensors seen so far (launch arguments, tensor maps): for a process that
+    frees one engine and builds another."""
+    _repeats.clear()
+    _tensor_maps.clear()
 
 
 _device_index: Optional[int] = None
@@ -153,6 +190,26 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
 def _need(cond: bool, msg: str) -> None:
     if not cond:
         raise KernelError(msg)
+
+
+_sm_count = 0
+
+
+def sm_count() -> int:
+    """Multiprocessors of the current device."""
+    global _sm_count
+    if not _sm_count:
+        _sm_count = int((_lib or require_extension()).me_device_sm_count())
+    return _sm_count
+
+
+def wait_expires_selftest(err: torch.Tensor, limit: int = 4096) -> int:
+    """Runs the kernel of csrc/selftest.cu: a bounded wait on a barrier that nothing completes.  It sets flag 1 of
+    ``err`` (int32[4] on the device) as the tensor-map kernels do when a wait runs out; returns the polls made."""
+    _need(err.dtype == torch.int32 and err.numel() >= 4 and err.is_cuda, "wait_expires_selftest: err must be int32[4] on the device")
+    polls = torch.zeros(1, dtype=torch.int32, device=err.device)
+    _call("me_test_wait_expires", err.data_ptr(), int(limit), polls.data_ptr(), _stream())
+    return int(polls.item())
 
 
 def check_attention_sizes(head_dim: int, num_heads: int, num_kv_heads: int) -> None:
@@ -232,10 +289,13 @@ def skinny_splits(M: int, K: int, x: torch.Tensor, weight: torch.Tensor) -> int:
     return (_lib or require_extension()).me_gemm_skinny_splits(K)
 
 
-def linear_partials(x: torch.Tensor, weight: torch.Tensor, workspace, name: str) -> Optional[torch.Tensor]:
+def linear_partials(x: torch.Tensor, weight: torch.Tensor, workspace, name: str,
+                    err: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """``x @ weight.T`` as float32 partial results [splits, M, N] of a split-K product, for a consumer that
     adds them (``add_rmsnorm``); None when the product is not one that is split: the small-batch kernel splits long
-    rows of few requests, the tcgen05 kernel products of a few hundred rows whose tiles would leave most SMs idle."""
+    rows of few requests, the tcgen05 kernel products of a few hundred rows whose tiles would leave most SMs idle.
+    ``err``: the int32[4] error word of the step (the tcgen05 kernel reports a wait that ran out there); without it
+    the tcgen05 kernel is not used."""
     M, K = x.shape
     N = weight.shape[0]
     splits = skinny_splits(M, K, x, weight)
@@ -243,11 +303,11 @@ def linear_partials(x: torch.Tensor, weight: torch.Tensor, workspace, name: str)
         part = workspace(name, (splits, M, N), torch.float32)
         _call("me_gemm_skinny", x.data_ptr(), x.stride(0), weight.data_ptr(), 0, 0, 0, part.data_ptr(), M, N, K, 0, _stream())
         return part
-    if use_tcgen05_gemm and M >= TCGEN05_MIN_ROWS and tcgen05_takes(x, weight) and weight.is_contiguous():
+    if err is not None and use_tcgen05_gemm and M >= TCGEN05_MIN_ROWS and tcgen05_takes(x, weight) and weight.is_contiguous():
         bn, parts = tcgen05_split_plan(M, N, K)
         if parts >= 2:
             part = workspace(name, (parts, M, N), torch.float32)
-            linear_tcgen05(x, weight, part, "none", _gemm_error_word(x.device), tile_n=bn, splits=parts)
+            linear_tcgen05(x, weight, part, "none", err, tile_n=bn, splits=parts)
             return part
     return None
 
@@ -385,16 +445,6 @@ def tcgen05_split_plan(M: int, N: int, K: int) -> tuple[int, int]:
     return (bn, parts) if parts >= 2 and tcgen05_splits(K, parts) == parts else (0, 1)
 
 
-_gemm_err: dict = {}
-
-
-def _gemm_error_word(device) -> torch.Tensor:
-    t = _gemm_err.get(device)
-    if t is None:
-        t = _gemm_err[device] = torch.zeros(4, dtype=torch.int32, device=device)
-    return t
-
-
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "none",
            workspace=None, err: Optional[torch.Tensor] = None) -> None:
     """``out = x @ weight.T`` with float32 accumulation; ``epilogue="silu_mul"`` takes a weight of
@@ -404,11 +454,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
     FMA, no reduced-precision matrix mode.  bfloat16 x bfloat16 products run csrc/gemm_skinny.cu for up
     to 16 rows (decode) and the tcgen05 kernel of csrc/gemm_tcgen05.cu above that; shapes those refuse
     (K no multiple of 8) go to cuBLAS, as all the reference's products do through ``F.linear``
-    (layers/linear.py:26,45), with SiLU-and-multiply as a kernel of ours behind it."""
+    (layers/linear.py:26,45), with SiLU-and-multiply as a kernel of ours behind it.
+
+    ``err``: the int32[4] error word of the step; the tcgen05 kernel sets flag 1 there when one of its bounded
+    waits runs out.  Without it products of 128 rows and more go to cuBLAS."""
     global library_calls
-    err_word = err if err is not None else _gemm_error_word(x.device)
     key = ("linear", id(x), id(weight), id(out), epilogue)
-    sig = (x.data_ptr(), weight.data_ptr(), out.data_ptr(), err_word.data_ptr(), x.shape, x.stride(), x.dtype, weight.shape,
+    sig = (x.data_ptr(), weight.data_ptr(), out.data_ptr(), _ptr(err), x.shape, x.stride(), x.dtype, weight.shape,
            weight.stride(), weight.dtype, out.shape, out.stride(), out.dtype, use_tcgen05_gemm)
     if _repeat(key, sig):
         return
@@ -426,22 +478,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
               0, M, N, K, epi, _stream())
         _remember(key, sig, before)
         return
-    if use_tcgen05_gemm and tcgen05_takes(x, weight) and (epi == 0 or out.dtype == torch.bfloat16):
-        linear_tcgen05(x, weight, out, epilogue, err_word)
+    if err is not None and use_tcgen05_gemm and tcgen05_takes(x, weight) and (epi == 0 or out.dtype == torch.bfloat16):
+        linear_tcgen05(x, weight, out, epilogue, err)
         _remember(key, sig, before)
         return
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.is_cuda:
         if epi == 0 and out.dtype == torch.bfloat16:
-            torch.mm(x, weight.t(), out=out)
+            with _Timed("library_mm"):
+                torch.mm(x, weight.t(), out=out)
             library_calls += 1
             return
         if epi == 0 and out.dtype == torch.float32:
-            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+            with _Timed("library_mm"):
+                torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
             library_calls += 1
             return
         if epi == 1 and out.dtype == torch.bfloat16 and workspace is not None:
             tmp = workspace("linear_gate_up", (M, 2 * N), torch.bfloat16)
-            torch.mm(x, weight.t(), out=tmp)
+            with _Timed("library_mm"):
+                torch.mm(x, weight.t(), out=tmp)
             library_calls += 1
             silu_mul(tmp, out)
             return
@@ -503,7 +558,7 @@ def attention_prefill(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_si
           int(window or 0), _stream())
 
 
-DECODE_KINDS = {"auto": 0, "cuda_cores": 1, "bulk_copy": 2, "tensor_cores": 3, "tensor_cores_tma": 4}
+DECODE_KINDS = {"auto": 0, "cuda_cores": 1, "tensor_cores": 3, "tensor_cores_tma": 4}
 
 _tensor_maps: dict = {}
 
@@ -590,17 +645,14 @@ def decode_fused_takes(qkv: torch.Tensor, head_dim: int, pool: torch.Tensor, pag
             and kv_tensor_map(pool, page_size) is not None)
 
 
-# The form of the decode partition kernel: "one_tile" (mma.sync; K and V pass through the same shared-memory tile,
-# five blocks an SM), "two_tiles" (mma.sync; a tile each, three blocks an SM) or "tcgen05" (the two products on the
-# 5th-generation tensor cores, head size 128 only; measured slower than mma.sync: an accumulator in tensor memory
-# costs a partition two round trips through commit, mbarrier and tcgen05.ld for 16 instructions' worth of arithmetic).
-DECODE_FORMS = {"one_tile": 0, "tcgen05": 1, "two_tiles": 2, "tile_and_half": 3}
+# The form of the decode partition kernel: "one_tile" (K and V pass through the same shared-memory tile, five blocks
+# an SM), "two_tiles" (a tile each, three blocks an SM) or "tile_and_half" (half a tile for V beside K's, four blocks).
+DECODE_FORMS = {"one_tile": 0, "two_tiles": 2, "tile_and_half": 3}
 # "auto": by the number of partitions with keys.  Up to what three blocks an SM hold at once, two tiles (all loads
 # in flight together: batch 1, 0.78 ms a step against 0.80 with one tile); up to about four times that, a tile and a
 # half (batch 8: 0.92 against 0.97, batch 16: 1.23 against 1.27); beyond, one tile (batch 64: 2.60 against 2.90 and
 # 2.98; batch 256: 7.6 against 9.1 and 8.7).
 decode_form = "auto"
-DECODE_RESIDENT_TWO_TILES = 3 * 148
 
 
 def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window,
@@ -616,9 +668,10 @@ def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, pa
         typical = getattr(meta, "typical_context_len", 0) or meta.max_context_len
         blocks = meta.num_decodes * num_kv_heads * ((num_heads // num_kv_heads + 15) // 16) \
             * ((typical + DECODE_PARTITION - 1) // DECODE_PARTITION)
-        if blocks <= DECODE_RESIDENT_TWO_TILES:
+        resident = 3 * sm_count()                   # blocks of the two-tile form that the device holds at once
+        if blocks <= resident:
             form = "two_tiles"
-        elif blocks <= 4 * DECODE_RESIDENT_TWO_TILES and (DECODE_PARTITION // 2) % page_size == 0:
+        elif blocks <= 4 * resident and (DECODE_PARTITION // 2) % page_size == 0:
             form = "tile_and_half"
         else:
             form = "one_tile"

@@ -43,5 +43,6 @@ class LMHead(Part):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         out = ctx.buffer("logits", (x.shape[0], self.vocab_size), torch.float32)
+        ops.tag = "logits"
         ops.linear(x, self.p("weight"), out, workspace=ctx.buffer, err=ctx.error_flag)
         return out

@@ -51,6 +51,7 @@ class Linear(Part):
         runs, since the short dependent kernels of a decode step leave the memory system idle.  With ``may_split`` the
         result may come as float32 partial results [splits, T, N] of a split-K product; only a consumer that adds
         them (the next norm) may ask for that."""
+        ops.tag = out_name
         pending = x if isinstance(x, PendingNorm) else None
         M = pending.residual.shape[0] if pending is not None else x.shape[0]
         fused = ctx.act_dtype == torch.bfloat16 and ops.decode_linear_takes(M, self.in_features, self.weight)
@@ -71,7 +72,7 @@ class Linear(Part):
             return AddedToResidual(sumsq, xw, nw)
         n_out = self.out_features // 2 if epilogue == "silu_mul" else self.out_features
         if may_split and epilogue == "none" and not fused:
-            part = ops.linear_partials(x, self.weight, ctx.buffer, out_name + "_partials")
+            part = ops.linear_partials(x, self.weight, ctx.buffer, out_name + "_partials", err=ctx.error_flag)
             if part is not None:
                 return part
         out = ctx.buffer(out_name, (M, n_out), out_dtype or ctx.act_dtype)

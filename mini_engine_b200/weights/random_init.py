@@ -61,3 +61,33 @@ def write_random_model(folder: str, config: dict[str, Any], seed: int,
         json.dump(config, f, indent=1)
     save_file(tensors, os.path.join(folder, "model.safetensors"))
     return folder
+
+
+def init_random_on_device(model: DecoderModel, seed: int, dtype: torch.dtype, device,
+                          matrix_std: float = 0.02, norm_std: float = 0.1) -> dict[str, torch.Tensor]:
+    """Fill every part's ``params`` with random numbers drawn on ``device``: no files, no host copy.
+
+    For benchmarks at sizes whose files would take minutes to write and read (a 32B shape is 65 GB).  Same laws
+    as ``write_random_model`` (matrices N(0, matrix_std) in ``dtype``, norm weights 1 + N(0, norm_std) in
+    float32), drawn parameter by parameter in declaration order from one generator seeded on the device; the
+    numbers are not those of ``write_random_model`` with the same seed."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(int(seed))
+    params: dict[str, torch.Tensor] = {}
+    tied = []
+    for prefix, part, decl in iter_param_decls(model):
+        full = prefix + decl.name
+        if decl.tied_to is not None:
+            tied.append((full, part, decl))
+            continue
+        if decl.role == "vector":
+            t = torch.empty(decl.shape, dtype=torch.float32, device=device).normal_(0.0, 1.0, generator=gen)
+            t = t.mul_(norm_std).add_(1.0) if decl.init == "norm" else t.mul_(matrix_std)
+        else:
+            t = torch.empty(decl.shape, dtype=dtype, device=device).normal_(0.0, matrix_std, generator=gen)
+            if decl.init == "norm":
+                t = t.mul_(norm_std / matrix_std).add_(1.0)
+        params[full] = part.params[decl.name] = t
+    for full, part, decl in tied:
+        params[full] = part.params[decl.name] = params[decl.tied_to]
+    return params

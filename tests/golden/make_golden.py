@@ -1,6 +1,6 @@
 """Runs the reference's own model code on the CPU once and stores its logits.
 
-Usage:  python tests/golden/make_golden.py [path of the reference tree]
+Usage:  python tests/golden/make_golden.py PATH_OF_THE_REFERENCE_TREE     (or $MINI_ENGINE_REF)
 
 The reference's ``models.qwen3.Qwen3ForCausalLM`` is imported with MINI_ENGINE_OPS=0 (its
 pure-PyTorch attention, layers/attention.py:54-59), built from a plain namespace with the
@@ -20,7 +20,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MINI_ENGINE_REF", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MINI_ENGINE_REF", "")
+if not os.path.isfile(os.path.join(REF, "models", "qwen3.py")):
+    sys.exit("give the path of the reference tree (ankur110/mini_engine) as the argument or in $MINI_ENGINE_REF")
 os.environ["MINI_ENGINE_OPS"] = "0"
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))

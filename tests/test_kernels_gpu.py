@@ -19,6 +19,24 @@ def ops():
     return o
 
 
+_ERR = None
+
+
+def errword():
+    """The error word handed to products (the tcgen05 kernel reports a wait that ran out there)."""
+    global _ERR
+    if _ERR is None:
+        _ERR = torch.zeros(4, dtype=torch.int32, device=DEV)
+    return _ERR
+
+
+@pytest.fixture(autouse=True)
+def no_kernel_reported_an_error():
+    yield
+    if _ERR is not None:
+        assert _ERR.tolist() == [0, 0, 0, 0]
+
+
 def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
     g = torch.Generator().manual_seed(seed + sum(shape))
     return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
@@ -96,7 +114,7 @@ def test_linear(ops, M, N, K, kinds):
     xd, wd, od = (DT[k] for k in kinds)
     x, w = rnd(M, K, dtype=xd, seed=1), rnd(N, K, dtype=wd, seed=2, scale=K ** -0.5)
     out, ref = torch.empty(M, N, dtype=od, device=DEV), torch.empty(M, N, dtype=od, device=DEV)
-    ops.linear(x, w, out)
+    ops.linear(x, w, out, err=errword())
     plain_ops.linear(x, w, ref)
     close(out, ref, od, scale=4)
 
@@ -117,7 +135,7 @@ def test_products_split_along_k(ops, M, N, K):
     assert err.tolist() == [0, 0, 0, 0]
     # the engine's choice, through the call that a feed-forward or attention output makes
     ws = {}
-    part = ops.linear_partials(x, w, lambda name, shape, dt: ws.setdefault(name, torch.full(shape, float("nan"), dtype=dt, device=DEV)), "p")
+    part = ops.linear_partials(x, w, lambda name, shape, dt: ws.setdefault(name, torch.full(shape, float("nan"), dtype=dt, device=DEV)), "p", err=err)
     bn, parts = ops.tcgen05_split_plan(M, N, K)
     assert (part is None) == (parts < 2)
     if part is not None:
@@ -130,7 +148,7 @@ def test_products_split_along_k(ops, M, N, K):
 def test_linear_silu_mul(ops, M, I, K, dt):
     x, w = rnd(M, K, dtype=DT[dt], seed=1), rnd(2 * I, K, dtype=DT[dt], seed=2, scale=K ** -0.5)
     out, ref = torch.empty(M, I, dtype=DT[dt], device=DEV), torch.empty(M, I, dtype=DT[dt], device=DEV)
-    ops.linear(x, w, out, epilogue="silu_mul")
+    ops.linear(x, w, out, epilogue="silu_mul", err=errword())
     plain_ops.linear(x, w, ref, epilogue="silu_mul")
     close(out, ref, DT[dt], scale=4)
 
@@ -148,13 +166,13 @@ def test_small_batch_products(ops, M, N, K):
 
     def workspace(name, shape, dt):
         return ws.setdefault(name, torch.full(tuple(shape), float("nan"), dtype=dt, device=DEV))
-    part = ops.linear_partials(x, w, workspace, "p")
+    part = ops.linear_partials(x, w, workspace, "p", err=errword())
     if splits == 1:
         assert part is None
         for od in (torch.bfloat16, torch.float32):
             before = ops.library_calls
             out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
-            ops.linear(x, w, out)
+            ops.linear(x, w, out, err=errword())
             assert ops.library_calls == before                     # our kernel, not the library
             close(out, ref, od, scale=4)
     else:
@@ -172,7 +190,7 @@ def test_small_batch_products(ops, M, N, K):
         I = N // 2
         out, ref2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV), torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
         before = ops.library_calls
-        ops.linear(x, w, out, epilogue="silu_mul", workspace=workspace)
+        ops.linear(x, w, out, epilogue="silu_mul", workspace=workspace, err=errword())
         assert ops.library_calls == before
         plain_ops.linear(x, w, ref2, epilogue="silu_mul")
         close(out, ref2, torch.bfloat16, scale=4)
@@ -265,8 +283,8 @@ def test_decode_products_with_norm_and_residual_folded_in(ops, M, N, K):
 def test_linear_rows_do_not_depend_on_the_batch(ops):
     x, w = rnd(70, 96, seed=1), rnd(224, 96, seed=2)
     full, one = torch.empty(70, 224, device=DEV), torch.empty(1, 224, device=DEV)
-    ops.linear(x, w, full)
-    ops.linear(x[41:42], w, one)
+    ops.linear(x, w, full, err=errword())
+    ops.linear(x[41:42], w, one, err=errword())
     assert torch.equal(full[41:42], one)
 
 
@@ -278,11 +296,11 @@ def test_remembered_launches_follow_their_tensors(ops):
     x, out, ref = rnd(130, 64, dtype=bf, seed=1), torch.empty(130, 96, dtype=bf, device=DEV), torch.empty(130, 96, dtype=bf, device=DEV)
     for seed in (1, 5, 9):                                   # same tensors, new contents: twice remembered
         x.copy_(rnd(130, 64, dtype=bf, seed=seed))
-        ops.linear(x, w, out)
+        ops.linear(x, w, out, err=errword())
         plain_ops.linear(x, w, ref)
         close(out, ref, bf, scale=4)
     before = ops.launches
-    ops.linear(x, w, out)
+    ops.linear(x, w, out, err=errword())
     assert ops.launches == before + 1
     for M, dt in ((130, torch.float32), (7, bf), (131, bf)):  # other kinds and sizes, some at the same addresses as before
         del x, out, ref
@@ -290,7 +308,7 @@ def test_remembered_launches_follow_their_tensors(ops):
         out, ref = torch.empty(M, 96, dtype=dt, device=DEV), torch.empty(M, 96, dtype=dt, device=DEV)
         for _ in range(2):
             out.fill_(float("nan"))
-            ops.linear(x, w2, out)
+            ops.linear(x, w2, out, err=errword())
             plain_ops.linear(x, w2, ref)
             close(out, ref, dt, scale=4)
     res, delta = rnd(70, 96, seed=4), rnd(70, 96, dtype=bf, seed=5)
@@ -469,7 +487,7 @@ def test_attention_tensor_core_prefill(ops, nh, nkv, hd, page, window):
     assert ops.prefill_tcgen05_heads_per_block(16, 8, 128, 16) == 2 and ops.prefill_tcgen05_heads_per_block(16, 8, 128, 24) == 0
 
 
-@pytest.mark.parametrize("kind", ["cuda_cores", "bulk_copy", "tensor_cores", "tensor_cores_tma"])
+@pytest.mark.parametrize("kind", ["cuda_cores", "tensor_cores", "tensor_cores_tma"])
 @pytest.mark.parametrize("nh, nkv, hd, page", [(16, 8, 128, 16), (8, 1, 64, 32), (4, 4, 64, 8), (12, 4, 128, 16),
                                                   (40, 2, 64, 16), (6, 3, 48, 16), (8, 2, 32, 8)])
 @pytest.mark.parametrize("window", [None, 200])
@@ -494,10 +512,8 @@ def test_attention_decode_kernels_by_name(ops, kind, nh, nkv, hd, page, window):
                                                   (40, 2, 64, 16), (16, 8, 128, 128)])
 @pytest.mark.parametrize("window", [None, 200])
 @pytest.mark.parametrize("norm, rope, writes", [(True, True, True), (False, True, True), (True, False, True), (True, True, False)])
-@pytest.mark.parametrize("form", ["one_tile", "tile_and_half", "two_tiles", "tcgen05"])
+@pytest.mark.parametrize("form", ["one_tile", "tile_and_half", "two_tiles"])
 def test_attention_decode_that_prepares_q_and_the_newest_key_itself(ops, nh, nkv, hd, page, window, norm, rope, writes, form):
-    if form == "tcgen05" and hd != 128:
-        pytest.skip("the tcgen05 form takes head_dim 128")
     if form == "tile_and_half" and 64 % page:
         pytest.skip("half a partition holds whole pages")
     # the same batch through (norm, rotation, cache write) as a pass of its own followed by plain attention, and
