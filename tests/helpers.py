@@ -127,6 +127,55 @@ def trace_mixed(reqs, max_live=4, seed=0, first_step=0, tag="m", decode_tail=12)
     return steps
 
 
+def trace_mixed_shared(reqs, shared, max_live=4, seed=0, first_step=0, tag="s", decode_tail=12):
+    """As ``trace_mixed``, with requests that repeat the start of another.  ``shared``: {i: (j, n, when)}: request i
+    begins with request j's first n tokens and starts only once j has computed at least n tokens and still lives
+    (when = "alive"), or once j has ended (when = "ended").  Its first portion holds those n tokens and a few more,
+    and its logits are wanted from place n on, so that a replayer with prefix reuse may take the n tokens' pages
+    from the cache."""
+    rng = np.random.RandomState(seed)
+    steps, s = [], first_step
+    waiting = list(range(len(reqs)))
+    pos, live, ended = {}, [], set()
+
+    def may_start(i):
+        if i not in shared:
+            return True
+        j, n, when = shared[i]
+        return j in ended if when == "ended" else (j in live and pos[j] >= n)
+    while waiting or live:
+        for i in list(waiting):
+            if len(live) < max_live and may_start(i):
+                waiting.remove(i)
+                live.append(i)
+                pos[i] = 0
+        assert live, "a request waits for one that never comes"
+        entries, done = [], []
+        for i in list(live):
+            r = reqs[i]
+            if len(live) > 1 and pos[i] > 0 and rng.rand() < 0.2:
+                continue                                     # left out of this step
+            left = len(r) - pos[i]
+            if pos[i] == 0 and i in shared:
+                n = shared[i][1] + int(rng.choice([1, 3, 6]))
+                want = list(range(shared[i][1], n))
+            else:
+                n = 1 if left <= decode_tail else int(min(left - decode_tail, rng.choice([2, 3, 5, 8, 13, 21, 40])))
+                want = list(range(n))
+            assert n <= left
+            entries.append({"id": f"{tag}{i}", "tokens": r[pos[i]:pos[i] + n], "want": want})
+            pos[i] += n
+            if pos[i] == len(r):
+                done.append(i)
+        for i in done:
+            live.remove(i)
+            ended.add(i)
+        if entries:
+            steps.append({"step": s, "entries": entries, "end": [f"{tag}{i}" for i in done]})
+            s += 1
+    return steps
+
+
 def collect(steps, outputs) -> dict[str, np.ndarray]:
     """Per request id, the logits of all its positions in order ([len, vocab])."""
     rows: dict[str, list[np.ndarray]] = {}

@@ -69,7 +69,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     nkv = k.shape[1]
     g = nh // nkv
     out = torch.empty_like(q)
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     seen = pos[None, :] <= pos[:, None]
     if window is not None:
         seen &= pos[None, :] > pos[:, None] - window
@@ -110,16 +110,18 @@ def layer_windows(cfg) -> list[Optional[int]]:
     return [cfg["sliding_window"] if t == "sliding_attention" else None for t in types]
 
 
-def forward_logits(cfg: dict, w: dict, token_ids, dtype=torch.float64) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence from position 0.
+def forward_logits(cfg: dict, w: dict, token_ids, dtype=torch.float64, device=None, positions=None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence from position 0 (with ``positions``: of those rows only).
 
     models/qwen3.py:65-74,86-92 with the residual written the usual way (the reference defers
-    each add into the next norm, layers/layernorm.py:19-23, which is the same sum)."""
-    w = {k: v.to(dtype) for k, v in w.items()}
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
+    each add into the next norm, layers/layernorm.py:19-23, which is the same sum).  ``device``: where the
+    arithmetic runs (the same plain torch code; large layer sizes are slow on the host)."""
+    w = {k: v.to(device=device, dtype=dtype) for k, v in w.items()}
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=device)
     T = ids.shape[0]
     theta = (cfg.get("rope_parameters") or {}).get("rope_theta", cfg.get("rope_theta"))
     cos, sin = rope_tables(cfg["head_dim"], T, theta, dtype)
+    cos, sin = cos.to(device), sin.to(device)
     windows = layer_windows(cfg)
     r = w["model.embed_tokens.weight"][ids]                    # layers/embed_head.py:11
     for i in range(cfg["num_hidden_layers"]):
@@ -129,8 +131,10 @@ def forward_logits(cfg: dict, w: dict, token_ids, dtype=torch.float64) -> torch.
         x = rms_norm(r, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
         r = r + swiglu(x, w, p + "mlp.")
     h = rms_norm(r, w["model.norm.weight"], cfg["rms_norm_eps"])
+    if positions is not None:                                  # layers/embed_head.py:19-23: rows gathered before the head
+        h = h[torch.as_tensor(positions, dtype=torch.long, device=device)]
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
-    return h @ head.T                                          # layers/embed_head.py:19-23
+    return (h @ head.T).cpu()                                  # layers/embed_head.py:19-23
 
 
 def greedy_generate(cfg, w, prompt, num_new: int, dtype=torch.float64) -> list[int]:

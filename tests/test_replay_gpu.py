@@ -23,7 +23,7 @@ def _requests(name):
 def _replay(name, dtype, steps, max_tokens=None, **kw):
     from mini_engine_b200.engine.replay import TraceReplayer
     rp = TraceReplayer(helpers.model_folder(name), dtype, max_tokens or helpers.max_live_tokens(steps),
-                       page_size=ALL[name][2], **kw)
+                       page_size=helpers.config_of(name)[2], **kw)
     outs = [rp.run_step(st) for st in steps]
     assert not rp.live
     rp.cache.check([])
@@ -78,6 +78,40 @@ def test_mixed_batches_with_pages_used_again(name, dtype):
     assert need < sum((len(r) + 63) // 64 * 64 for r in reqs)          # fewer pages than all requests: reuse
     got, rp = _replay(name, dtype, steps, max_tokens=need)
     _check(name, dtype, reqs, got, "m")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "A!", "B!"])
+def test_mixed_batches_with_prefix_hits_and_poisoned_pages(name, dtype):
+    """The mixed cutting with two requests that repeat the first two pages (and three tokens) of request 0: one starts
+    while request 0 lives, one after it has ended and its pages are free; both must find the pages instead of
+    computing them.  Every page that no live request wrote holds NaN (the pool at the start, pages handed out,
+    pages let go), so a key or value read from the wrong place shows in the logits."""
+    cfg, _, page = helpers.config_of(name)
+    reqs = _requests(name.rstrip("!")) + _requests(name.rstrip("!"))[:2]
+    n = 2 * page + 3
+    reqs[2] = reqs[0][:n] + reqs[2]
+    reqs[6] = reqs[0][:n] + reqs[6][:40]
+    shared = {2: (0, n, "alive"), 6: (0, n, "ended")}
+    steps = helpers.trace_mixed_shared(reqs, shared, max_live=4, seed=5)
+    need = helpers.max_live_tokens(steps)
+    assert need < sum((len(r) + 63) // 64 * 64 for r in reqs)
+    got, rp = _replay(name, dtype, steps, max_tokens=need + 64, prefix_caching=True, poison=True)
+    assert rp.cache.num_prefix_hit_tokens == 2 * (2 * page)                   # both found their two pages
+    tol = helpers.TOL[dtype] * (1.0 if not name.endswith("!") else 4.0)
+    for i, r in enumerate(reqs):
+        ref = helpers.plain_logits(name, r)
+        first = shared[i][1] if i in shared else 0
+        mine = got[f"s{i}"]
+        assert mine.shape == ref[first:].shape and not np.isnan(mine).any()
+        diff = np.abs(mine - ref[first:]).max(axis=1)
+        bad = np.nonzero(diff > tol * max(1.0, np.abs(ref).max() if name.endswith("!") else 1.0))[0]
+        assert bad.size == 0, f"config {name} {dtype} request {i}: first wrong token at position {first + bad[0]} (diff {diff[bad[0]]:.3e})"
+    # the same trace without reuse computes the shared pages again and gives the same logits
+    got2, rp2 = _replay(name, dtype, steps, max_tokens=need + 64, prefix_caching=False, poison=True)
+    assert rp2.cache.num_prefix_hit_tokens == 0
+    for k in got:
+        assert np.abs(got[k] - got2[k]).max() <= 2 * tol * max(1.0, np.abs(got2[k]).max())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
