@@ -11,14 +11,20 @@
 #include "common.cuh"
 
 constexpr int QK_WARPS = 4;
-constexpr int MAX_PAIRS = 4;      // head_dim/2 <= 32 lanes * 4
+constexpr int QK_MAX_HD = 256;
+constexpr int QK_PER_LANE = QK_MAX_HD / 32;
 
+// Any even head size up to 256, and a rotation over the first ``rd`` <= head_dim elements only (the two halves of
+// those rd elements are paired; elements from rd on pass through the rotation unchanged).  A lane owns elements
+// lane, lane + 32, ...; the normalised values go through a per-warp row of shared memory so that a lane finds its
+// element's partner wherever it lives.  With rd = head_dim this is the arithmetic of the vector kernel below.
 template <typename T>
 __global__ void __launch_bounds__(QK_WARPS * 32)
-qk_rope_kv_kernel(T* __restrict__ qkv, int64_t row_stride, int n_tokens, int nh, int nkv, int hd,
+qk_rope_kv_kernel(T* __restrict__ qkv, int64_t row_stride, int n_tokens, int nh, int nkv, int hd, int rd,
                   const float* __restrict__ qw, const float* __restrict__ kw, float eps,
                   const float* __restrict__ cos_sin, const int* __restrict__ positions,
                   const int* __restrict__ slot_mapping, T* __restrict__ pool, int page_size) {
+  __shared__ float ys[QK_WARPS][QK_MAX_HD];
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -27,7 +33,6 @@ qk_rope_kv_kernel(T* __restrict__ qkv, int64_t row_stride, int n_tokens, int nh,
   if (gw >= (int64_t)n_tokens * heads) return;
   const int t = (int)(gw / heads), head = (int)(gw % heads);
   T* x = qkv + (int64_t)t * row_stride + (int64_t)head * hd;
-  const int half = hd >> 1;
   const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
   const int kvh = is_q ? 0 : (is_k ? head - nh : head - nh - nkv);
 
@@ -44,18 +49,13 @@ qk_rope_kv_kernel(T* __restrict__ qkv, int64_t row_stride, int n_tokens, int nh,
       for (int i = lane; i < hd; i += 32) dst[i] = x[i];
     return;
   }
-  float a[MAX_PAIRS], b[MAX_PAIRS];
+  float v[QK_PER_LANE];
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < MAX_PAIRS; ++j) {
+  for (int j = 0; j < QK_PER_LANE; ++j) {
     const int i = lane + 32 * j;
-    if (i < half) {
-      a[j] = to_f<T>(x[i]);
-      b[j] = to_f<T>(x[i + half]);
-      ss += a[j] * a[j] + b[j] * b[j];
-    } else {
-      a[j] = b[j] = 0.f;
-    }
+    v[j] = i < hd ? to_f<T>(x[i]) : 0.f;
+    ss += v[j] * v[j];
   }
   const float* w = is_q ? qw : kw;
   float inv = 1.f;
@@ -63,29 +63,29 @@ qk_rope_kv_kernel(T* __restrict__ qkv, int64_t row_stride, int n_tokens, int nh,
     ss = warp_sum(ss);
     inv = 1.0f / sqrtf(ss / (float)hd + eps);
   }
-  const int pos = positions[t];
 #pragma unroll
-  for (int j = 0; j < MAX_PAIRS; ++j) {
+  for (int j = 0; j < QK_PER_LANE; ++j) {
     const int i = lane + 32 * j;
-    if (i < half) {
-      float y1 = a[j], y2 = b[j];
-      if (w) {
-        y1 = (y1 * inv) * w[i];
-        y2 = (y2 * inv) * w[i + half];
+    if (i < hd) {
+      if (w) v[j] = (v[j] * inv) * w[i];
+      ys[warp][i] = v[j];
+    }
+  }
+  __syncwarp();
+  const int pos = positions[t], rh = rd >> 1;
+#pragma unroll
+  for (int j = 0; j < QK_PER_LANE; ++j) {
+    const int i = lane + 32 * j;
+    if (i < hd) {
+      float o = v[j];
+      if (cos_sin && i < rd) {
+        const int f = i < rh ? i : i - rh;                          // the pair's frequency
+        const float c = cos_sin[(int64_t)pos * rd + f], s = cos_sin[(int64_t)pos * rd + rh + f];
+        o = i < rh ? v[j] * c - ys[warp][i + rh] * s : v[j] * c + ys[warp][i - rh] * s;
       }
-      float o1 = y1, o2 = y2;
-      if (cos_sin) {
-        const float c = cos_sin[(int64_t)pos * hd + i], s = cos_sin[(int64_t)pos * hd + half + i];
-        o1 = y1 * c - y2 * s;
-        o2 = y2 * c + y1 * s;
-      }
-      const T r1 = from_f<T>(o1), r2 = from_f<T>(o2);
-      x[i] = r1;
-      x[i + half] = r2;
-      if (dst) {
-        dst[i] = r1;
-        dst[i + half] = r2;
-      }
+      const T r = from_f<T>(o);
+      x[i] = r;
+      if (dst) dst[i] = r;
     }
   }
 }
@@ -199,21 +199,27 @@ static int64_t vec_warps(int n_tokens, int heads, int hd) {
   return (int64_t)n_tokens * ((heads + hpw * QK_PASSES - 1) / (hpw * QK_PASSES));
 }
 
+// cos_sin: float32 [positions][rotary_dim] (cos of the rotary_dim / 2 frequencies, then their sines), or null.
+// rotary_dim: how many leading elements of a head are rotated (even, at most head_dim).
 ME_API int me_qk_norm_rope_kv_write(void* qkv, int dtype, int64_t row_stride, int n_tokens, int nh,
                                     int nkv, int hd, const float* qw, const float* kw, float eps,
-                                    const float* cos_sin, const int* positions,
+                                    const float* cos_sin, int rotary_dim, const int* positions,
                                     const int* slot_mapping, void* pool, int page_size,
                                     cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  ME_REQUIRE(hd % 2 == 0 && hd >= 2 && hd <= 64 * MAX_PAIRS,
-             "me_qk_norm_rope_kv_write: head_dim %d is not an even number up to %d", hd, 64 * MAX_PAIRS);
+  ME_REQUIRE(hd % 2 == 0 && hd >= 2 && hd <= QK_MAX_HD,
+             "me_qk_norm_rope_kv_write: head_dim %d is not an even number up to %d", hd, QK_MAX_HD);
+  if (cos_sin == nullptr) rotary_dim = hd;
+  ME_REQUIRE(rotary_dim % 2 == 0 && rotary_dim >= 2 && rotary_dim <= hd,
+             "me_qk_norm_rope_kv_write: rotary_dim %d is not an even number up to head_dim %d", rotary_dim, hd);
   ME_REQUIRE(nh > 0 && nkv > 0 && page_size > 0, "me_qk_norm_rope_kv_write: bad sizes");
   ME_REQUIRE((qw == nullptr) == (kw == nullptr), "me_qk_norm_rope_kv_write: q and k norm weights go together");
   const int64_t warps = (int64_t)n_tokens * (nh + 2 * nkv);
   const int64_t blocks = (warps + QK_WARPS - 1) / QK_WARPS;
   ME_REQUIRE(blocks < 2147483647LL, "me_qk_norm_rope_kv_write: too many tokens");
   const int esize = dtype == ME_BF16 ? 2 : 4;
-  const bool vec_ok = (hd == 64 || hd == 128 || hd == 256) && (row_stride * esize) % 16 == 0 && ((uintptr_t)qkv & 15) == 0;
+  const bool vec_ok = (hd == 64 || hd == 128 || hd == 256) && rotary_dim == hd && (row_stride * esize) % 16 == 0 &&
+                      ((uintptr_t)qkv & 15) == 0;
 #define ME_QK_VEC(HD_)                                                                                  \
   ME_DISPATCH_DTYPE(dtype, T, (me_launch(qk_rope_kv_vec_kernel<T, HD_>,                                 \
       dim3((unsigned)((vec_warps<T>(n_tokens, nh + 2 * nkv, HD_) + QK_WARPS - 1) / QK_WARPS)), dim3(QK_WARPS * 32), 0, \
@@ -227,7 +233,7 @@ ME_API int me_qk_norm_rope_kv_write(void* qkv, int dtype, int64_t row_stride, in
   }
 #undef ME_QK_VEC
   ME_DISPATCH_DTYPE(dtype, T, (me_launch(qk_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(QK_WARPS * 32), 0, stream,
-      (T*)qkv, row_stride, n_tokens, nh, nkv, hd, qw, kw, eps, cos_sin, positions, slot_mapping,
+      (T*)qkv, row_stride, n_tokens, nh, nkv, hd, rotary_dim, qw, kw, eps, cos_sin, positions, slot_mapping,
       (T*)pool, page_size)));
   ME_LAUNCH_CHECK("me_qk_norm_rope_kv_write");
   return 0;

@@ -107,23 +107,19 @@ class ModelRunner:
 
         self.groups, self.slot_location, self.state_needs = plan_cache_groups(self.model)
         self.error_flag = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self.num_pages = num_pages if num_pages > 0 else self._size_pool(gpu_memory_utilization)
-        self.kv_pools = [torch.zeros(len(g.cache_slots), self.num_pages, 2, g.num_kv_heads, page_size,
-                                     g.head_dim, dtype=self.act_dtype, device=self.device)
-                         for g in self.groups]
         self.num_state_slots = max_num_seqs if self.state_needs else 0
-        self.state_storage = {slot: torch.zeros(self.num_state_slots, *need.shape, dtype=torch.float32,
+        self.state_storage = {slot: torch.zeros(self.num_state_slots, *need.shape, dtype=getattr(torch, need.dtype),
                                                 device=self.device)
                               for slot, need in self.state_needs.items()}
         # Four error flags and the tokens drawn by the last step whose results were staged here: one copy to the host,
         # and the place where a step launched ahead of the host finds the tokens it continues from (a token id ~j).
         self.result_dev = torch.zeros(4 + max_num_seqs, dtype=torch.int32, device=self.device)
         self.token_feedback = self.result_dev[4:]
-        self.ctx = StepContext(self)
         self._pins: list[Optional[torch.Tensor]] = [None, None]     # pinned host int32, used in turn
         self._pin_events: list[Any] = [None, None]
         self._pin_turn = 0
         self._staging_dev: Optional[torch.Tensor] = None
+        self.last_h2d_bytes = 0
         # A decode step is replayed from a graph only if every part of the model allows it.
         self.use_cuda_graphs = (use_cuda_graphs and self.device.type == "cuda"
                                 and all(part.capturable for _, part in self.model.walk()))
@@ -137,9 +133,11 @@ class ModelRunner:
         self.prefill_graph_max = 4               # graphs kept (each has work buffers of its own); the oldest goes first
         self._prefill_graphs: dict[tuple, _StepGraph] = {}
         self._prefill_seen: dict[tuple, int] = {}
-        self.sample_tokens = torch.empty(max(max_num_seqs, 1), dtype=torch.int32, device=self.device)
         self.graph_launches = 0          # kernels replayed from graphs (they bypass ops.launches)
-        self.last_h2d_bytes = 0
+        self.pool_sizing: dict = {}      # what the pool was sized from, when it was sized here
+        self.num_pages = num_pages if num_pages > 0 else self._size_pool(gpu_memory_utilization)
+        self.kv_pools = self._make_pools(self.num_pages)
+        self.ctx = StepContext(self)
 
     # ---- sizes -----------------------------------------------------------------------
     def page_bytes(self) -> int:
@@ -147,33 +145,66 @@ class ModelRunner:
         return sum(len(g.cache_slots) * 2 * g.num_kv_heads * self.page_size * g.head_dim
                    for g in self.groups) * self.act_dtype.itemsize
 
+    def _make_pools(self, num_pages: int) -> list[torch.Tensor]:
+        return [torch.zeros(len(g.cache_slots), num_pages, 2, g.num_kv_heads, self.page_size, g.head_dim,
+                            dtype=self.act_dtype, device=self.device) for g in self.groups]
+
     def _size_pool(self, utilization: float) -> int:
-        """Pages that fit into the share of device memory the engine may use, after the weights
-        and the work buffers of the largest step (the reference measures a warm-up step's peak,
-        engine/model_runner.py:59-80; here the work buffers are bounded by arithmetic)."""
-        free, total = torch.cuda.mem_get_info(self.device)
-        plan = self.model.plan
-        widest = max([plan.hidden_size * 4] + [self._widest_row_bytes()])
-        work = self.max_num_batched_tokens * widest * 3 + self.max_num_seqs * self.vocab_size * 4 * 2
-        budget = int(total * utilization) - (total - free) - work
-        per_page = max(self.page_bytes(), 1)
-        n = budget // per_page
+        """Pages that fit into the share of device memory the engine may use, after the weights and the work
+        buffers.  As the reference does (engine/model_runner.py:52-80), the work buffers are measured: with a pool
+        of one page, and block tables that all point at it, the largest step of prompt portions and the largest
+        step of single tokens are run once, kernel by kernel.  What the captured steps will take on top of that
+        (an arena of work buffers per batch bucket, up to ``prefill_graph_max`` prompt graphs with buffers of
+        their own) is counted from those two measurements."""
+        from ..cache.manager import CacheHolder
+        dev = self.device
+        ps = self.page_size
+        self.num_pages, self.kv_pools = 1, self._make_pools(1)
+        self.ctx = StepContext(self)
+        graphs, self.use_cuda_graphs = self.use_cuda_graphs, False
+
+        def dummy(tokens: int) -> CacheHolder:
+            h = CacheHolder()
+            h.block_tables = [[0] * ((tokens + ps - 1) // ps) for _ in self.groups]
+            h.num_released = [0] * len(self.groups)
+            h.state_slot = 0 if self.state_needs else -1
+            return h
+
+        def used() -> int:
+            torch.cuda.synchronize(dev)
+            free, total = torch.cuda.mem_get_info(dev)
+            return total - free
+        torch.cuda.empty_cache()
+        base = used()
+        L = self.max_model_len
+        m = min(L, self.max_num_batched_tokens)
+        n = max(1, min(self.max_num_batched_tokens // m, self.max_num_seqs))
+        self.step([StepItem(dummy(m), [0] * m, 0, [m - 1]) for _ in range(n)], sample=True)
+        after_prompts = used()
+        self.step([StepItem(dummy(L), [0], L - 1, [0], (1.0, 0)) for _ in range(self.max_num_seqs)], sample=True)
+        after_tokens = used()
+        self.check_device_errors()
+        prompt_bytes, token_bytes = after_prompts - base, max(after_tokens - after_prompts, 0)
+        allowance = 0
+        if graphs:
+            # the arena of a batch bucket grows with the bucket: all of them together, in units of the largest step
+            share = sum(self.graph_buckets) / max(self.max_num_seqs, 1)
+            allowance = int((prompt_bytes / max(n * m, 1) * self.max_num_seqs + token_bytes) * share) \
+                + self.prefill_graph_max * prompt_bytes
+        self.use_cuda_graphs = graphs
+        free, total = torch.cuda.mem_get_info(dev)
+        budget = int(total * utilization) - (total - free) - allowance
+        self.pool_sizing = {"work_prompts": prompt_bytes, "work_tokens": token_bytes, "graphs": allowance, "budget": budget}
+        n_pages = budget // max(self.page_bytes(), 1)
         # No request can use more than max_model_len tokens, so more pages than all requests
         # could fill are never touched.
         cap = self.max_num_seqs * ((self.max_model_len + self.page_size - 1) // self.page_size)
-        n = min(n, cap)
-        if n < 1:
+        n_pages = min(n_pages, cap)
+        if n_pages < 1:
             raise RuntimeError("no device memory left for the cache pool: lower max_num_seqs / "
                                "max_num_batched_tokens or raise gpu_memory_utilization")
-        return int(n)
-
-    def _widest_row_bytes(self) -> int:
-        w = 0
-        for _, part in self.model.walk():
-            for d in part.param_decls():
-                if len(d.shape) == 2:
-                    w = max(w, d.shape[0] * 4 if d.shape[0] < self.vocab_size else 0, d.shape[1] * 4)
-        return w
+        self.kv_pools = []
+        return int(n_pages)
 
     def make_cache_manager(self, enable_prefix_caching: bool = True) -> CacheManager:
         return CacheManager(self.groups, self.num_pages, self.page_size,

@@ -108,5 +108,5 @@ class StepContext:
         return KVView(self.runner.kv_pools[g][idx], self.runner.page_size, self._bt[g], self._sm[g], g)
 
     def state(self, cache_slot: int) -> torch.Tensor:
-        """Storage of a mixer's per-request state: [num_state_slots, *shape] float32."""
+        """Storage of a mixer's per-request state: [num_state_slots, *shape] of the dtype its ``StateNeed`` names."""
         return self.runner.state_storage[cache_slot]

@@ -26,7 +26,7 @@ _PROTOS = {
     "me_gemm_skinny": [_P, _L, _P, _P, _I, _L, _P, _I, _I, _I, _I, _P],
     "me_silu_mul": [_P, _P, _I, _I, _I, _P],
     "me_gemm_simt": [_P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P],
-    "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _P],
+    "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
     "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P,
@@ -505,12 +505,33 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
 
 
 # ---- attention ------------------------------------------------------------------------------
+ROTARY_LAYOUTS = ("half_split",)     # what the kernels rotate: element i with element i + rotary_dim / 2, i < rotary_dim / 2
+
+
+def check_rotary(cos_sin: Optional[torch.Tensor], head_dim: int, rotary_dim: Optional[int], layout: str) -> int:
+    """The rotary contract between a position encoding and the kernels: a float32 table [positions, rotary_dim]
+    (cosines of the rotary_dim / 2 frequencies, then their sines), ``rotary_dim`` even and at most ``head_dim``
+    (elements from rotary_dim on are left unrotated), and a layout the kernels know by name.  Returns rotary_dim."""
+    if layout not in ROTARY_LAYOUTS:
+        raise KernelError(f"rotary layout {layout!r} is not supported by the kernels (they take: {', '.join(ROTARY_LAYOUTS)}); "
+                          "another pairing of elements needs another kernel branch")
+    if cos_sin is None:
+        return head_dim
+    rd = head_dim if rotary_dim is None else int(rotary_dim)
+    _need(rd % 2 == 0 and 2 <= rd <= head_dim, f"rotary_dim {rd} must be even and at most head_dim {head_dim}")
+    _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.dim() == 2 and cos_sin.shape[1] == rd,
+          f"the rotary table must be float32 [positions, rotary_dim = {rd}]")
+    return rd
+
+
 def qk_norm_rope_kv_write(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                           q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                           cos_sin: Optional[torch.Tensor], positions: torch.Tensor,
-                          slot_mapping: Optional[torch.Tensor], pool: torch.Tensor, page_size: int) -> None:
-    """In place on the packed rows q|k|v: RMSNorm of every q and k head, rotary embedding, and the
-    write of k and v to ``pool`` [pages, 2, kv_heads, page_size, head_dim] at ``slot_mapping``."""
+                          slot_mapping: Optional[torch.Tensor], pool: torch.Tensor, page_size: int,
+                          rotary_dim: Optional[int] = None, layout: str = "half_split") -> None:
+    """In place on the packed rows q|k|v: RMSNorm of every q and k head, rotary embedding of the first
+    ``rotary_dim`` elements of each (default: all of them), and the write of k and v to ``pool``
+    [pages, 2, kv_heads, page_size, head_dim] at ``slot_mapping``."""
     T = qkv.shape[0]
     _need(qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, "qk_norm_rope: qkv shape")
     _need(pool.dtype == qkv.dtype and pool.is_contiguous()
@@ -518,14 +539,12 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, 
     for w in (q_weight, k_weight):
         if w is not None:
             _need(w.dtype == torch.float32 and w.shape == (head_dim,), "qk_norm_rope: norm weights are float32 [head_dim]")
-    if cos_sin is not None:
-        _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == head_dim,
-              "qk_norm_rope: the rotary table must be float32 [positions, head_dim]")
+    rd = check_rotary(cos_sin, head_dim, rotary_dim, layout)
     _need(positions.dtype == torch.int32 and positions.shape[0] == T, "qk_norm_rope: positions")
     if slot_mapping is not None:
         _need(slot_mapping.dtype == torch.int32 and slot_mapping.shape[0] == T, "qk_norm_rope: slot mapping")
     _call("me_qk_norm_rope_kv_write", qkv.data_ptr(), _dt(qkv), qkv.stride(0), T, num_heads, num_kv_heads,
-          head_dim, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos_sin), positions.data_ptr(),
+          head_dim, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos_sin), rd, positions.data_ptr(),
           _ptr(slot_mapping), pool.data_ptr(), page_size, _stream())
 
 
@@ -636,11 +655,12 @@ def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_siz
     launches += 1          # partition kernel + merge kernel
 
 
-def decode_fused_takes(qkv: torch.Tensor, head_dim: int, pool: torch.Tensor, page_size: int, meta) -> bool:
+def decode_fused_takes(qkv: torch.Tensor, head_dim: int, pool: torch.Tensor, page_size: int, meta,
+                       rotary_dim: Optional[int] = None) -> bool:
     """Whether ``attention_decode_fused`` takes the step: bfloat16, head size 64 or 128, pages of 8 to 128 tokens
-    that divide 128, and a tensor map over the cache."""
+    that divide 128, a tensor map over the cache, and a rotation over the whole head (or none)."""
     lib = _lib or require_extension()
-    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and meta.error_flag is not None
+    return (qkv.is_cuda and (rotary_dim is None or rotary_dim == head_dim) and qkv.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and meta.error_flag is not None
             and bool(lib.me_attn_decode_fused_takes(head_dim, page_size)) and (qkv.stride(0) * 2) % 16 == 0
             and kv_tensor_map(pool, page_size) is not None)
 
@@ -685,8 +705,7 @@ def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, pa
           "attention_decode_fused: cache slot")
     for w in (q_weight, k_weight):
         _need(w is None or (w.dtype == torch.float32 and tuple(w.shape) == (head_dim,)), "attention_decode_fused: norm weights")
-    _need(cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == head_dim),
-          "attention_decode_fused: the rotary table must be float32 [positions, head_dim]")
+    _need(check_rotary(cos_sin, head_dim, None, "half_split") == head_dim, "attention_decode_fused: the rotation covers the whole head")
     _need(slot_mapping is None or slot_mapping.dtype == torch.int32, "attention_decode_fused: slots are int32")
     _call("me_attn_decode_fused", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), pool.data_ptr(), tm.ptr,
           block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), D,

@@ -79,16 +79,19 @@ class GQAAttention(Mixer):
         has_norm = self.qk_norm_eps is not None
         prep = (self.p("q_norm.weight") if has_norm else None, self.p("k_norm.weight") if has_norm else None,
                 self.qk_norm_eps if has_norm else 0.0, self.rope.cos_sin if self.rope is not None else None)
+        rotary_dim = self.rope.rotary_dim if self.rope is not None else None
+        layout = self.rope.layout if self.rope is not None else "half_split"
         slots = kv.slot_mapping if call.writes_cache else None
         # Requests that bring one token come first in the batch.  Where the decode kernel takes the shape it
         # prepares q and the newest key and value itself; the other rows get the separate pass.
         D = meta.num_decodes
-        fused = D > 0 and ops.decode_fused_takes(qkv, self.head_dim, kv.pool, kv.page_size, meta)
+        fused = D > 0 and layout == "half_split" and ops.decode_fused_takes(qkv, self.head_dim, kv.pool, kv.page_size, meta,
+                                                                            rotary_dim)
         first = D if fused else 0
         if first < qkv.shape[0]:
             ops.qk_norm_rope_kv_write(qkv[first:], self.num_heads, self.num_kv_heads, self.head_dim, *prep,
                                       ctx.positions[first:], slots[first:] if slots is not None else None,
-                                      kv.pool, kv.page_size)
+                                      kv.pool, kv.page_size, rotary_dim=rotary_dim, layout=layout)
         out = ctx.buffer("attn_out", (qkv.shape[0], self.q_size), ctx.act_dtype)
         if fused:
             ops.attention_decode_fused(qkv, out, self.num_heads, self.num_kv_heads, self.head_dim, kv.pool, kv.page_size,

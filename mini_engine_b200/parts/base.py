@@ -52,8 +52,9 @@ class KVCacheNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A slot of fixed size per request (float32 elements)."""
+    """A slot of fixed size per request: ``shape`` elements of ``dtype`` (a torch dtype's name)."""
     shape: tuple[int, ...]
+    dtype: str = "float32"
 
 
 @dataclass
@@ -172,4 +173,19 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """Position information applied to queries and keys before the cache write."""
+    """Position information applied to queries and keys before the cache write.
+
+    What the attention mixer hands to its kernels, and so what a position encoding of the rotary family declares:
+
+    * ``cos_sin``: float32 ``[max_position, rotary_dim]`` built in ``finalize``: for every absolute position the
+      cosines of the ``rotary_dim / 2`` angles, then their sines;
+    * ``rotary_dim``: how many leading elements of a head are rotated (even, at most the head size; the rest pass
+      through unchanged);
+    * ``layout``: how elements are paired, by name.  The kernels know ``"half_split"`` (element i with element
+      i + rotary_dim / 2); any other name is refused with an error that says so, and needs a kernel branch.
+
+    A token has ONE position (int32) in the step's metadata; an encoding with several position axes is not covered."""
+
+    rotary_dim: int = 0
+    layout: str = "half_split"
+    cos_sin: "Optional[torch.Tensor]" = None

@@ -11,22 +11,44 @@ from dataclasses import dataclass
 from typing import Optional
 
 from .base import Part, Upcoming
-from .registry import PartSpec, build_part
+from .registry import PartSpec, build_part, register_block
 
 
 @dataclass
 class BlockSpec:
+    """One layer as data: the parts it is made of and (``kind``) how they are arranged.
+
+    ``norm`` is the norm of both places; ``mixer_norm`` / ``feed_forward_norm`` give a place a norm of its own."""
     mixer: PartSpec
     feed_forward: PartSpec
-    norm: PartSpec                     # built twice: before the mixer and before the feed-forward
+    norm: Optional[PartSpec] = None
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
+    kind: str = "pre_norm"             # a name registered with ``register_block``
     mixer_prefix: str = "self_attn."
     feed_forward_prefix: str = "mlp."
     mixer_norm_prefix: str = "input_layernorm."
     feed_forward_norm_prefix: str = "post_attention_layernorm."
 
+    def norm_of(self, place: str) -> PartSpec:
+        spec = getattr(self, place) or self.norm
+        if spec is None:
+            raise ValueError(f"a block needs a norm for {place!r} (give ``norm`` or ``{place}``)")
+        return spec
 
-class PreNormBlock(Part):
-    capturable = True
+
+class Block(Part):
+    """The arrangement of a layer's parts around the residual stream; built by the factory registered for
+    ``BlockSpec.kind``.
+
+    What the model asks of a block: ``mixer`` (its ``cache_needs()`` decide the layer's cache slot),
+    ``sub_parts()`` (for the weights), ``upcoming()`` (what the block starts with, for the block before it; may be
+    an empty ``Upcoming``) and ``forward(residual, delta, ctx, call, upcoming=None)``: ``residual`` is the float32
+    stream [T, hidden], updated in place; ``delta`` is the output of the block before that is not added yet (a
+    tensor, float32 split-K partial results, ``AddedToResidual``, or None); the return value is this block's own
+    last output in the same form (None: everything is in ``residual`` already)."""
+
+    mixer: Part
 
     def __init__(self, spec: BlockSpec, shared: Optional[dict] = None):
         super().__init__()
@@ -39,14 +61,26 @@ class PreNormBlock(Part):
             mixer_spec = PartSpec(mixer_spec.kind, args)
         self.mixer = build_part("mixer", mixer_spec)
         self.feed_forward = build_part("feed_forward", spec.feed_forward)
-        self.mixer_norm = build_part("norm", spec.norm)
-        self.feed_forward_norm = build_part("norm", spec.norm)
+        self.mixer_norm = build_part("norm", spec.norm_of("mixer_norm"))
+        self.feed_forward_norm = build_part("norm", spec.norm_of("feed_forward_norm"))
 
     def sub_parts(self):
         s = self.spec
         return [(s.mixer_norm_prefix, self.mixer_norm), (s.mixer_prefix, self.mixer),
                 (s.feed_forward_norm_prefix, self.feed_forward_norm),
                 (s.feed_forward_prefix, self.feed_forward)]
+
+    def upcoming(self) -> Upcoming:
+        return Upcoming()
+
+    def forward(self, residual, delta, ctx, call, upcoming=None):
+        raise NotImplementedError
+
+
+class PreNormBlock(Block):
+    """``r += mixer(norm(r)); r += feed_forward(norm(r))`` with each sum deferred into the norm that follows
+    (models/qwen3.py:65-74 in the reference)."""
+    capturable = True
 
     def upcoming(self) -> Upcoming:
         """What this block starts with, for the block that runs before it."""
@@ -73,3 +107,6 @@ class PreNormBlock(Part):
 class SharedRef:
     """Stands in a PartSpec's args for an object that the model builds once and shares."""
     key: str
+
+
+register_block("pre_norm", PreNormBlock)

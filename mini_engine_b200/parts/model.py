@@ -16,9 +16,9 @@ from typing import Any, Iterator, Optional
 import torch
 
 from .base import Part, ParamDecl
-from .block import BlockSpec, PreNormBlock, SharedRef
+from .block import BlockSpec, SharedRef
 from .embed import LMHead, TokenEmbedding
-from .registry import PartSpec, build_part
+from .registry import PartSpec, build_block, build_part
 
 
 @dataclass(frozen=True)
@@ -52,7 +52,7 @@ class DecoderModel(Part):
         self.plan = plan
         self.shared = {k: build_part("position_encoding", s) for k, s in plan.shared.items()}
         self.embed = TokenEmbedding(plan.vocab_size, plan.hidden_size)
-        self.blocks = [PreNormBlock(s, self.shared) for s in plan.blocks]
+        self.blocks = [build_block(s, self.shared) for s in plan.blocks]
         self.final_norm = build_part("norm", plan.final_norm)
         tied = plan.embed_prefix + "weight" if plan.tie_word_embeddings else None
         self.head = LMHead(plan.vocab_size, plan.hidden_size, tied)

@@ -10,7 +10,7 @@ from dataclasses import dataclass, field
 from typing import Any, Callable
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "block": {},
 }
 
 
@@ -41,6 +41,20 @@ def register_norm(kind, factory, *, replace=False):
 
 def register_position_encoding(kind, factory, *, replace=False):
     _register("position_encoding", kind, factory, replace)
+
+
+def register_block(kind, factory, *, replace=False):
+    """``factory(spec: BlockSpec, shared: dict) -> Block``: how a layer's norms, mixer and feed-forward are arranged
+    around the residual stream (``BlockSpec.kind`` names it)."""
+    _register("block", kind, factory, replace)
+
+
+def build_block(spec, shared):
+    reg = _REGISTRIES["block"]
+    if spec.kind not in reg:
+        known = ", ".join(sorted(reg)) or "(none)"
+        raise ValueError(f"unknown block kind {spec.kind!r}; registered: {known}")
+    return reg[spec.kind](spec, shared)
 
 
 def build_part(family: str, spec: PartSpec):

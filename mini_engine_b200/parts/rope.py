@@ -18,11 +18,13 @@ from .registry import register_position_encoding
 class RotaryEmbedding(PositionEncoding):
     capturable = True
 
+    layout = "half_split"
+
     def __init__(self, rotary_dim: int, max_position: int, theta: float):
         super().__init__()
         if rotary_dim % 2:
             raise ValueError(f"rotary_dim {rotary_dim} must be even")
-        self.rotary_dim = rotary_dim
+        self.rotary_dim = rotary_dim                  # the leading elements of a head that are rotated
         self.max_position = max_position
         self.theta = float(theta)
         self.cos_sin: torch.Tensor | None = None      # [max_position, rotary_dim] = cos | sin halves

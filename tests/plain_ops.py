@@ -69,7 +69,7 @@ def linear(x, weight, out, epilogue="none", workspace=None, err=None):
 
 
 def qk_norm_rope_kv_write(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, cos_sin,
-                          positions, slot_mapping, pool, page_size):
+                          positions, slot_mapping, pool, page_size, rotary_dim=None, layout="half_split"):
     # models/qwen3.py:34-36, layers/rotary_embedding.py:20-25, layers/attention.py:13-18
     T = qkv.shape[0]
     nh, nkv, d = num_heads, num_kv_heads, head_dim
@@ -82,12 +82,14 @@ def qk_norm_rope_kv_write(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_we
         return (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)) * w
 
     def rope(t):
+        # the first rd elements are rotated (their two halves paired), the rest pass through
         if cos_sin is None:
             return t
+        rd = d if rotary_dim is None else rotary_dim
         cs = cos_sin[positions.long()]
-        cos, sin = cs[:, None, : d // 2], cs[:, None, d // 2:]
-        a, b = t[..., : d // 2], t[..., d // 2:]
-        return torch.cat((a * cos - b * sin, b * cos + a * sin), dim=-1)
+        cos, sin = cs[:, None, : rd // 2], cs[:, None, rd // 2:]
+        a, b, rest = t[..., : rd // 2], t[..., rd // 2:rd], t[..., rd:]
+        return torch.cat((a * cos - b * sin, b * cos + a * sin, rest), dim=-1)
 
     q, k = rope(norm(q, q_weight)), rope(norm(k, k_weight))
     res = torch.cat((q, k, v), dim=1).reshape(T, -1).to(qkv.dtype)

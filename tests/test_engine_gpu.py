@@ -115,6 +115,23 @@ def test_running_out_of_pages_preempts_and_gives_the_same_tokens():
     assert tight.cache.num_free_pages == [7]
 
 
+def test_the_pool_is_sized_from_a_measured_step_when_no_page_count_is_given():
+    from mini_engine_b200 import LLM, SamplingParams
+    name = "B!"
+    args = dict(dtype="bfloat16", kvcache_block_size=8, max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256)
+    llm = LLM(helpers.model_folder(name), num_kvcache_blocks=-1, **args)
+    sizing = llm.model_runner.pool_sizing
+    assert llm.model_runner.num_pages == 4 * 256 // 8             # all that four requests of 256 tokens can ever fill
+    assert llm.config.num_kvcache_blocks == llm.model_runner.num_pages
+    assert sizing["work_prompts"] > 0 and sizing["graphs"] > 0 and sizing["budget"] > 0
+    prompts = helpers.random_requests(helpers.config_of(name)[0]["vocab_size"], (40, 3, 21), seed=6)
+    out = llm.generate(prompts, SamplingParams(temperature=0, max_tokens=6), use_tqdm=False)
+    for p, o in zip(prompts, out):
+        _check_greedy(name, "bfloat16", p, o["token_ids"])
+    with pytest.raises(RuntimeError, match="no device memory left"):
+        LLM(helpers.model_folder(name), num_kvcache_blocks=-1, gpu_memory_utilization=1e-6, **args)
+
+
 def test_request_too_large_is_refused():
     from mini_engine_b200 import SamplingParams
     llm = _llm("A", "float32", num_kvcache_blocks=4)

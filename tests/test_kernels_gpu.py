@@ -359,6 +359,33 @@ def test_qk_norm_rope_kv_write(ops, nh, nkv, hd, dt, norm, rope):
     assert not pool2.any()
 
 
+@pytest.mark.parametrize("dt", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh, nkv, hd, rd", [(4, 2, 64, 32), (16, 8, 128, 64), (3, 1, 48, 16), (8, 2, 32, 2), (2, 2, 256, 192),
+                                             (5, 1, 80, 80)])
+def test_rotation_of_the_first_elements_of_a_head_only(ops, nh, nkv, hd, rd, dt):
+    # partial rotary: the first rd elements of each head are rotated, the others only normalised
+    T, page, pages = 29, 16, 5
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=DT[dt], seed=3)
+    qw, kw = 1 + 0.1 * rnd(hd, seed=1), 1 + 0.1 * rnd(hd, seed=2)
+    pos = torch.randint(0, 200, (T,), dtype=torch.int32, device=DEV)
+    inv = 1.0 / (5000.0 ** (torch.arange(0, rd, 2).float() / rd))
+    fr = torch.outer(torch.arange(200).float(), inv)
+    cs = torch.cat((fr.cos(), fr.sin()), -1).to(DEV)
+    slots = torch.randperm(pages * page)[:T].to(torch.int32).to(DEV)
+    pool = torch.full((pages, 2, nkv, page, hd), float("nan"), dtype=DT[dt], device=DEV)
+    ref_qkv, ref_pool = qkv.clone(), pool.clone()
+    ops.qk_norm_rope_kv_write(qkv, nh, nkv, hd, qw, kw, 1e-5, cs, pos, slots, pool, page, rotary_dim=rd)
+    plain_ops.qk_norm_rope_kv_write(ref_qkv, nh, nkv, hd, qw, kw, 1e-5, cs, pos, slots, ref_pool, page, rotary_dim=rd)
+    close(qkv, ref_qkv, DT[dt], scale=4)
+    assert torch.equal(pool.isnan(), ref_pool.isnan())
+    close(pool.nan_to_num(0), ref_pool.nan_to_num(0), DT[dt], scale=4)
+    if rd < hd:                                       # and the table must have the width that is named
+        with pytest.raises(ops.KernelError, match="rotary"):
+            ops.qk_norm_rope_kv_write(qkv, nh, nkv, hd, qw, kw, 1e-5, cs, pos, slots, pool, page)
+    with pytest.raises(ops.KernelError, match="interleaved"):
+        ops.qk_norm_rope_kv_write(qkv, nh, nkv, hd, qw, kw, 1e-5, cs, pos, slots, pool, page, rotary_dim=rd, layout="interleaved")
+
+
 def test_head_dim_is_checked(ops):
     with pytest.raises(ValueError, match="head_dim"):
         ops.check_attention_sizes(40, 4, 2)

@@ -87,9 +87,9 @@ def test_parts_alone(name, dtype):
 # ---- a toy architecture defined here -------------------------------------------------------------
 def _register_toy():
     from mini_engine_b200.config import Architecture, ModelConfig, register_architecture
-    from mini_engine_b200.parts import (BlockSpec, FeedForward, LayerCall, Linear, Mixer, ModelPlan, PartSpec, PositionEncoding,
-                                        SharedRef, StateNeed, register_feed_forward, register_mixer,
-                                        register_position_encoding)
+    from mini_engine_b200.parts import (Block, BlockSpec, FeedForward, LayerCall, Linear, Mixer, ModelPlan, PartSpec,
+                                        PositionEncoding, SharedRef, StateNeed, register_block, register_feed_forward,
+                                        register_mixer, register_position_encoding)
 
     class RunningMean(Mixer):
         """out[t] = mean over the request's tokens 0..t of proj(x): its state (a sum and a count) has a
@@ -104,11 +104,12 @@ def _register_toy():
             return [("", self.proj)]
 
         def cache_needs(self):
-            return [StateNeed((self.h + 1,))]
+            return [StateNeed((self.h + 1,), "float64")]         # sums over a whole request: kept in 64 bits
 
         def forward(self, x, ctx, call):
-            y = self.proj.forward(x, ctx, "toy_proj").float()
+            y = self.proj.forward(x, ctx, "toy_proj").double()
             state = ctx.state(call.cache_slot)
+            assert state.dtype == torch.float64
             out = torch.empty_like(y)
             t = 0
             for start, n, slot in zip(ctx.host.starts, ctx.host.lengths, ctx.host.state_slots):
@@ -149,6 +150,28 @@ def _register_toy():
                 act = torch.nn.functional.silu(hid.float()).to(ctx.act_dtype)
                 out += probs[:, i:i + 1] * self.downs[i].forward(act, ctx, f"toy_down{i}").float()
             return out.to(ctx.act_dtype)
+
+    class PostNormBlock(Block):
+        """Another arrangement of a layer: ``r = norm(r + mixer(r)); r = norm(r + feed_forward(r))``, each place with a
+        norm of its own.  Nothing is left pending: the stream holds the block's result when it returns."""
+
+        def forward(self, residual, delta, ctx, call, upcoming=None):
+            assert delta is None                                   # (every block of this toy model is of this kind)
+            for norm, part, args in ((self.mixer_norm, self.mixer, (ctx, call)), (self.feed_forward_norm, self.feed_forward, (ctx,))):
+                out = part.forward(residual.to(ctx.act_dtype), *args)
+                residual.copy_(norm.forward(residual, out, ctx).float())
+            return None
+
+    class Interleaved(PositionEncoding):
+        """A rotary table whose pairing of elements the kernels do not know: refused by name at the first step."""
+        layout = "interleaved"
+
+        def __init__(self, rotary_dim, max_position):
+            super().__init__()
+            self.rotary_dim, self.max_position = rotary_dim, max_position
+
+        def finalize(self, dtype, device):
+            self.cos_sin = torch.zeros(self.max_position, self.rotary_dim, device=device)
 
     class InterpolatedRotary(PositionEncoding):
         """Another position encoding: rotary angles of position / factor (the table is all the attention mixer asks for)."""
@@ -192,7 +215,19 @@ def _register_toy():
         blocks = [BlockSpec(mixer=toy if i % 2 else attn, feed_forward=ffn, norm=norm)
                   for i in range(cfg.num_hidden_layers)]
         rope = PartSpec("rope", {"rotary_dim": cfg.head_dim, "max_position": cfg.max_position_embeddings, "theta": cfg.rope_theta})
-        if cfg.pattern == "routed":          # attention everywhere with the other position encoding; every second feed-forward routed
+        if cfg.pattern == "postnorm":        # every layer arranged the other way round, with two different norms
+            blocks = [BlockSpec(mixer=attn, feed_forward=ffn, kind="toy_post_norm",
+                                mixer_norm=PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": 1e-3}),
+                                feed_forward_norm=PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": 1e-6}))
+                      for i in range(cfg.num_hidden_layers)]
+            schedule = [LayerCall(i, i) for i in range(cfg.num_hidden_layers)]
+        elif cfg.pattern in ("partial", "unknown_layout"):   # attention everywhere; half of each head is rotated
+            blocks = [BlockSpec(mixer=attn, feed_forward=ffn, norm=norm) for i in range(cfg.num_hidden_layers)]
+            rope = PartSpec("rope", dict(rope.args, rotary_dim=cfg.head_dim // 2))
+            if cfg.pattern == "unknown_layout":
+                rope = PartSpec("toy_interleaved", {"rotary_dim": cfg.head_dim // 2, "max_position": cfg.max_position_embeddings})
+            schedule = [LayerCall(i, i) for i in range(cfg.num_hidden_layers)]
+        elif cfg.pattern == "routed":          # attention everywhere with the other position encoding; every second feed-forward routed
             experts = PartSpec("toy_soft_experts", {"hidden_size": cfg.hidden_size, "expert_size": 24, "num_experts": 3})
             blocks = [BlockSpec(mixer=attn, feed_forward=experts if i % 2 else ffn, norm=norm) for i in range(cfg.num_hidden_layers)]
             rope = PartSpec("toy_interpolated_rope", dict(rope.args, factor=2.5))
@@ -208,6 +243,8 @@ def _register_toy():
     register_mixer("toy_running_mean", RunningMean, replace=True)
     register_feed_forward("toy_soft_experts", SoftExperts, replace=True)
     register_position_encoding("toy_interpolated_rope", InterpolatedRotary, replace=True)
+    register_position_encoding("toy_interleaved", Interleaved, replace=True)
+    register_block("toy_post_norm", PostNormBlock, replace=True)
     register_architecture(Architecture("ToyStateLM", ToyConfig.from_dict, plan), replace=True)
 
 
@@ -227,12 +264,18 @@ def _toy_plain(cfg, w, ids):
         cos, sin = torch.cat((ang.cos(), ang.cos()), -1), torch.cat((ang.sin(), ang.sin()), -1)
     r = w["model.embed_tokens.weight"][ids]
     eps = cfg["rms_norm_eps"]
+    rd = cfg["head_dim"] // 2 if cfg["pattern"] == "partial" else cfg["head_dim"]
+    if cfg["pattern"] == "partial":
+        cos, sin = plain_model.rope_tables(rd, T, cfg["rope_theta"], torch.float64)
+
+    def rotate(t):                                       # the first rd elements of each head; the rest pass through
+        return torch.cat((plain_model.apply_rope(t[..., :rd], cos, sin), t[..., rd:]), dim=-1)
 
     def attn(x, p, kv_from=None):
         nh, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
-        q = plain_model.apply_rope(plain_model.rms_norm((x @ w[p + "q_proj.weight"].T).view(T, nh, d), w[p + "q_norm.weight"], eps), cos, sin)
+        q = rotate(plain_model.rms_norm((x @ w[p + "q_proj.weight"].T).view(T, nh, d), w[p + "q_norm.weight"], eps))
         if kv_from is None:
-            k = plain_model.apply_rope(plain_model.rms_norm((x @ w[p + "k_proj.weight"].T).view(T, nkv, d), w[p + "k_norm.weight"], eps), cos, sin)
+            k = rotate(plain_model.rms_norm((x @ w[p + "k_proj.weight"].T).view(T, nkv, d), w[p + "k_norm.weight"], eps))
             v = (x @ w[p + "v_proj.weight"].T).view(T, nkv, d)
         else:
             k, v = kv_from
@@ -248,7 +291,13 @@ def _toy_plain(cfg, w, ids):
         return sum(probs[:, i:i + 1] * (torch.nn.functional.silu(x @ w[p + f"experts.{i}.up.weight"].T) @ w[p + f"experts.{i}.down.weight"].T)
                    for i in range(3))
 
-    if cfg["pattern"] in ("state", "routed"):
+    if cfg["pattern"] == "postnorm":
+        for layer in range(cfg["num_hidden_layers"]):
+            p = f"model.layers.{layer}."
+            r = plain_model.rms_norm(r + attn(r, p + "self_attn.")[0], w[p + "input_layernorm.weight"], 1e-3)
+            r = plain_model.rms_norm(r + plain_model.swiglu(r, w, p + "mlp."), w[p + "post_attention_layernorm.weight"], 1e-6)
+        return (plain_model.rms_norm(r, w["model.norm.weight"], eps) @ w["lm_head.weight"].T).numpy()
+    if cfg["pattern"] in ("state", "routed", "partial"):
         calls = [(i, None) for i in range(cfg["num_hidden_layers"])]
     else:
         calls = [(0, None), (2, "write"), (0, None), (2, "read")]
@@ -256,7 +305,7 @@ def _toy_plain(cfg, w, ids):
     for layer, mode in calls:
         p = f"model.layers.{layer}."
         x = plain_model.rms_norm(r, w[p + "input_layernorm.weight"], eps)
-        if layer % 2 and cfg["pattern"] != "routed":
+        if layer % 2 and cfg["pattern"] not in ("routed", "partial"):
             m = mean_mixer(x, p + "self_attn.")
         else:
             m, kv = attn(x, p + "self_attn.", saved if mode == "read" else None)
@@ -269,7 +318,7 @@ def _toy_plain(cfg, w, ids):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("pattern", ["state", "twice", "routed"])
+@pytest.mark.parametrize("pattern", ["state", "twice", "routed", "postnorm", "partial", "partial64"])
 def test_toy_architecture_is_registered_built_and_stepped(pattern, dtype):
     """Parts defined here, in the test (a mixer with state of its own, a feed-forward with routing, another position
     encoding) and orders of layers that name a layer twice or share a cache are registered, built from a model
@@ -278,6 +327,8 @@ def test_toy_architecture_is_registered_built_and_stepped(pattern, dtype):
     from mini_engine_b200.engine.replay import TraceReplayer
     from mini_engine_b200.weights import write_random_model
     raw = dict(TOY, pattern=pattern)
+    if pattern == "partial64":            # head size 64: bfloat16 single tokens would take the decode kernel that rotates
+        raw.update(pattern="partial", head_dim=64)     # whole heads; with half a head rotated they take the separate pass
     folder = write_random_model(tempfile.mkdtemp(prefix="me_toy_"), raw, seed=9)
     cfg, w = plain_model.load_folder(folder, torch.float64)
     reqs = helpers.random_requests(raw["vocab_size"], (60, 45, 90, 38), seed=8)
@@ -288,6 +339,10 @@ def test_toy_architecture_is_registered_built_and_stepped(pattern, dtype):
         assert rp.runner.state_needs and rp.cache.state_slots.num_slots > 0 and not rp.cache.prefix_caching
     elif pattern == "twice":
         assert len(rp.runner.model.slot_needs) == 3           # three cache slots for four calls
+    elif pattern == "postnorm":
+        assert type(rp.runner.model.blocks[0]).__name__ == "PostNormBlock" and rp.runner.model.blocks[0].mixer_norm.eps == 1e-3
+    elif pattern.startswith("partial"):
+        assert rp.runner.model.shared["rope"].rotary_dim == raw["head_dim"] // 2
     else:
         assert rp.runner.use_cuda_graphs == (rp.runner.device.type == "cuda")     # these toy parts may be captured
     got = helpers.collect(steps, [rp.run_step(st) for st in steps])
@@ -298,3 +353,52 @@ def test_toy_architecture_is_registered_built_and_stepped(pattern, dtype):
             ref = _toy_plain(cfg, w, r)
             diff = np.abs(got[f"{tag}{i}"] - ref).max(axis=1)
             assert diff.max() <= tol, f"{pattern} {tag}{i}: first wrong token at {int(np.argmax(diff > tol))} ({diff.max():.3e})"
+
+
+def test_a_rotary_layout_the_kernels_do_not_know_is_refused_by_name():
+    _register_toy()
+    from mini_engine_b200 import ops
+    from mini_engine_b200.engine.replay import TraceReplayer
+    from mini_engine_b200.weights import write_random_model
+    folder = write_random_model(tempfile.mkdtemp(prefix="me_toy_"), dict(TOY, pattern="unknown_layout"), seed=9)
+    rp = TraceReplayer(folder, "float32", 64, page_size=16)
+    with pytest.raises(ops.KernelError, match="rotary layout 'interleaved' is not supported"):
+        rp.run_step({"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3], "want": [2]}], "end": []})
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_mixer_with_state_through_the_engine(dtype):
+    """The running-mean mixer through ``LLM.generate``: portions under a small budget, several requests, one ending
+    unforeseen on its end-of-sequence token.  The engine launches no step ahead of the host for such a model (a
+    dropped guess would advance the state twice), so the tokens are the plain implementation's either way."""
+    _register_toy()
+    from mini_engine_b200 import LLM, SamplingParams
+    from mini_engine_b200.weights import write_random_model
+    raw = dict(TOY, pattern="state")
+    folder = write_random_model(tempfile.mkdtemp(prefix="me_toy_"), raw, seed=9, matrix_std=0.1)
+    cfg, w = plain_model.load_folder(folder, torch.float64)
+    prompts = helpers.random_requests(raw["vocab_size"], (30, 7, 19), seed=4)
+
+    def plain_greedy(p, n, eos=None):
+        ids = list(p)
+        for _ in range(n):
+            ids.append(int(_toy_plain(cfg, w, ids)[-1].argmax()))
+            if ids[-1] == eos:
+                break
+        return ids[len(p):]
+    want = [plain_greedy(p, 10) for p in prompts]
+    i, k = next((i, k) for k in range(2, 9) for i in range(3) if want[i][k] not in want[i][:k])
+    eos = want[i][k]                                   # request i ends on it, unforeseen, while others go on
+    want = [plain_greedy(p, 10, eos) for p in prompts]
+    assert len(want[i]) == k + 1 and max(len(x) for x in want) > k + 1
+    outs = []
+    for overlap in (True, False):
+        llm = LLM(folder, dtype=dtype, kvcache_block_size=16, num_kvcache_blocks=32, max_num_seqs=4, max_num_batched_tokens=16,
+                  max_model_len=128, overlap_steps=overlap)
+        llm.scheduler.eos = eos
+        out = llm.generate(prompts, SamplingParams(temperature=0, max_tokens=10), use_tqdm=False)
+        assert llm.steps_ahead_used == 0 and llm.steps_ahead_dropped == 0
+        outs.append([o["token_ids"] for o in out])
+    assert outs[0] == outs[1]
+    if dtype == "float32":
+        assert outs[0] == want
