@@ -13,8 +13,8 @@ gives, for each kind of kernel of one decode step and one prefill step run kerne
 its mean time, its bytes or flops and the fraction of the measured peak.  ``points`` holds decode at batch 1 and
 64, the reference's offline workload (256 random requests through ``LLM.generate``), and the two larger shapes:
 the 8B shape's mixed workload (64 random requests, prompts of 100 to 2,048 tokens, 100 to 512 tokens out, token
-budget 8,192, through ``LLM.generate``) and the 32B shape's decode at batch 1, 8 and 64 after 2,048-token
-prompts, each with its fraction of the memory roofline.  ``--extras 0`` leaves the offline workload and the
+budget 8,192, through ``LLM.generate``), the 8B and 32B shapes' decode at batch 1, 8 and 64 after 2,048-token
+prompts, each with its fraction of the memory roofline, and prompts of 8,192 and 16,384 tokens in portions of 2,048.  ``--extras 0`` leaves the offline workload and the
 larger shapes out.
 
 Every size comes from the configuration that is loaded: ``--shape`` picks one of the three built-in ones (its
@@ -668,8 +668,30 @@ def extra_points(args, pk: dict) -> dict:
             out[f"32b_decode_b{b}_hbm_frac"] = v["hbm_frac"]
         out["32b_layers"] = m.layers
 
+    def long_prompts():
+        # one prompt of 8,192 and of 16,384 tokens at the 0.6B shape, in portions of 2,048 (each portion attends to all before it)
+        m = Model(args, "0.6b")
+        llm = make_engine(m, args, max_seqs=4, budget=2048, context=16384 + 64, pages=16384 // 16 + 64, enable_prefix_caching=False)
+        for T in (8192, 16384):
+            (prompt,) = random_prompts(1, T, m.vocab, args.seed + 5)
+            ms = prefill_on_device(llm.model_runner, llm.cache, prompt, reps=3, warmup=2, portion=2048)
+            flops = sum(prefill_flops(m.cfg, m.layers, 2048, a) for a in range(0, T, 2048))
+            out[f"prefill_{T}_tok_s"] = round(T * 1000.0 / ms, 1)
+            out[f"prefill_{T}_frac"] = round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+        del llm
+        release_memory()
+
+    def decode_8b():
+        m = Model(args, "8b")
+        pts = decode_points(m, args, [1, 8, 64], 2048, 20, 3, pk)
+        for b, v in pts.items():
+            out[f"8b_decode_b{b}"] = v["tok_s"]
+            out[f"8b_decode_b{b}_hbm_frac"] = v["hbm_frac"]
+
+    attempt("long_prompts", long_prompts)
     attempt("offline", offline)
     attempt("8b_mixed64", mixed_8b)
+    attempt("8b_decode", decode_8b)
     attempt("32b_decode", decode_32b)
     return out
 

@@ -32,6 +32,7 @@ _PROTOS = {
     "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P,
                              _I, _I, _P, _P],
     "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, ctypes.c_uint64, _P],
+    "me_gemm_stream": [_I, _P, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _L, _P, _P],
     "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
@@ -70,6 +71,8 @@ def require_extension() -> ctypes.CDLL:
     lib.me_sample_chunks.argtypes = [_I]
     lib.me_gemm_tcgen05_splits.argtypes = [_I, _I]
     lib.me_gemm_decode_sumsq_parts.argtypes = [_I]
+    lib.me_gemm_stream_sumsq_parts.argtypes = [_I, _I]
+    lib.me_gemm_stream_x_box_rows.argtypes = [_I]
     lib.me_attn_decode_fused_takes.argtypes = [_I, _I]
     lib.me_gemm_skinny_splits.argtypes = [_I]
     _lib = lib
@@ -312,23 +315,56 @@ def linear_partials(x: torch.Tensor, weight: torch.Tensor, workspace, name: str,
     return None
 
 
-DECODE_MAX_K = 3072       # largest K of csrc/gemm_decode.cu (one block covers all of K)
+DECODE_MAX_K = 3072       # largest K of csrc/gemm_decode.cu (one block covers all of K); beyond: csrc/gemm_stream.cu
+# Which of the two kernels a decode product runs: "auto" (gemm_decode up to DECODE_MAX_K, gemm_stream beyond),
+# "stream" (gemm_stream for every K) or "decode" (gemm_decode only; larger K is then not taken).  A switch for comparisons.
+decode_kernel = "auto"
 
 
-def decode_linear_takes(M: int, K: int, weight: torch.Tensor) -> bool:
-    """Whether csrc/gemm_decode.cu (products of up to 16 rows with norm / residual folded in) takes the shape."""
-    return (weight.is_cuda and weight.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0
-            and K <= DECODE_MAX_K and weight.data_ptr() % 16 == 0)
+def _decode_uses_stream(K: int) -> bool:
+    return decode_kernel == "stream" or (decode_kernel == "auto" and K > DECODE_MAX_K)
 
 
-def decode_linear_sumsq_parts(N: int) -> int:
-    """Strips of columns for which the residual epilogue of ``decode_linear`` writes sums of squares."""
-    return (_lib or require_extension()).me_gemm_decode_sumsq_parts(N)
+# Which products over a K beyond DECODE_MAX_K run csrc/gemm_stream.cu: "residual" (those that add into the residual
+# stream: no partial results for a norm kernel to add up; the others go to the library, which streams plain weights
+# faster) or "all".  A switch for comparisons.
+stream_products = "residual"
+
+
+def decode_linear_takes(M: int, K: int, weight: torch.Tensor, adds_to_residual: bool = True) -> bool:
+    """Whether a decode product with norm / residual folded in (csrc/gemm_decode.cu, csrc/gemm_stream.cu: up to 16
+    rows) takes the shape; ``adds_to_residual``: the product is one whose result is added to the residual stream."""
+    if not (weight.is_cuda and weight.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0
+            and weight.data_ptr() % 16 == 0):
+        return False
+    if _decode_uses_stream(K):
+        return decode_kernel == "stream" or stream_products == "all" or adds_to_residual
+    return K <= DECODE_MAX_K
+
+
+_stream_ws: dict = {}
+
+
+def _stream_work_buffers(device) -> tuple[torch.Tensor, torch.Tensor]:
+    """What csrc/gemm_stream.cu needs beside its operands: room for the sums a block leaves to the block that finishes its
+    group of rows, and a flag a block (zero between launches).  One pair a device: launches in one stream never overlap."""
+    ws = _stream_ws.get(device)
+    if ws is None:
+        lib = _lib or require_extension()
+        ws = _stream_ws[device] = (torch.empty(lib.me_gemm_stream_partial_floats(), dtype=torch.float32, device=device),
+                                   torch.zeros(lib.me_gemm_stream_flag_ints(), dtype=torch.int32, device=device))
+    return ws
+
+
+def decode_linear_sumsq_parts(N: int, K: int = 0) -> int:
+    """Parts in which the residual epilogue of ``decode_linear`` writes sums of squares, for N columns over K."""
+    lib = _lib or require_extension()
+    return lib.me_gemm_stream_sumsq_parts(N, K) if _decode_uses_stream(K) else lib.me_gemm_decode_sumsq_parts(N)
 
 
 def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.Tensor] = None, epilogue: str = "none",
                   row_scale=None, residual_out: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None,
-                  next_norm=None, fetch_ahead: Optional[torch.Tensor] = None) -> None:
+                  next_norm=None, fetch_ahead: Optional[torch.Tensor] = None, err: Optional[torch.Tensor] = None) -> None:
     """One decode product with its neighbours folded in (csrc/gemm_decode.cu).
 
     ``x``: bfloat16 [M, K].  ``row_scale`` = (sums of squares float32 [parts, M], eps): x is a residual times a
@@ -351,7 +387,7 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
     if epi == 2:
         _need(residual_out.dtype == torch.float32 and residual_out.is_contiguous() and tuple(residual_out.shape) == (M, N)
               and sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous()
-              and tuple(sumsq_out.shape) == (decode_linear_sumsq_parts(N), M), "decode_linear: residual output")
+              and tuple(sumsq_out.shape) == (decode_linear_sumsq_parts(N, K), M), "decode_linear: residual output")
         if nw is not None:
             _need(nw.dtype == torch.float32 and tuple(nw.shape) == (N,) and nw.is_contiguous() and xw.dtype == torch.bfloat16
                   and tuple(xw.shape) == (M, N) and xw.is_contiguous(), "decode_linear: pre-weighted output")
@@ -360,6 +396,15 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
         _need(next_norm is None, "decode_linear: the pre-weighted output belongs to the residual epilogue")
         _need(tuple(out.shape) == (M, N) and out.stride(1) == 1, "decode_linear: output shape")
         yp, ydt, ldy = out.data_ptr(), _dt(out), out.stride(0)
+    if _decode_uses_stream(K):
+        _need(err is not None, "decode_linear: the streaming kernel needs the step's error word (err=)")
+        lib = _lib or require_extension()
+        partials, flags = _stream_work_buffers(x.device)
+        _call("me_gemm_stream", epi, matrix_tensor_map(x, lib.me_gemm_stream_x_box_rows(M)).ptr, _ptr(sumsq),
+              sumsq.shape[0] if sumsq is not None else 0, float(eps), matrix_tensor_map(weight, 16).ptr, yp, ydt, ldy,
+              _ptr(residual_out), _ptr(sumsq_out), _ptr(nw), _ptr(xw), M, N, K, partials.data_ptr(), flags.data_ptr(),
+              err.data_ptr(), _stream())
+        return
     _call("me_gemm_decode", epi, x.data_ptr(), x.stride(0), _ptr(sumsq), sumsq.shape[0] if sumsq is not None else 0, float(eps),
           weight.data_ptr(), yp, ydt, ldy, _ptr(residual_out), _ptr(sumsq_out), _ptr(nw), _ptr(xw), M, N, K,
           _ptr(fetch_ahead), fetch_ahead.numel() * fetch_ahead.element_size() if fetch_ahead is not None else 0, _stream())

@@ -54,7 +54,8 @@ class Linear(Part):
         ops.tag = out_name
         pending = x if isinstance(x, PendingNorm) else None
         M = pending.residual.shape[0] if pending is not None else x.shape[0]
-        fused = ctx.act_dtype == torch.bfloat16 and ops.decode_linear_takes(M, self.in_features, self.weight)
+        fused = ctx.act_dtype == torch.bfloat16 and ops.decode_linear_takes(M, self.in_features, self.weight,
+                                                                            residual is not None and epilogue == "none")
         row_scale = None
         if pending is not None:
             if fused:
@@ -64,11 +65,12 @@ class Linear(Part):
         fused = fused and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
         assert fused or row_scale is None, "a pre-weighted residual can only go through the kernel that finishes its norm"
         if fused and residual is not None and epilogue == "none":
-            sumsq = ctx.buffer(out_name + "_sumsq", (ops.decode_linear_sumsq_parts(self.out_features), M), torch.float32)
+            sumsq = ctx.buffer(out_name + "_sumsq", (ops.decode_linear_sumsq_parts(self.out_features, self.in_features), M), torch.float32)
             nw = next_norm.separable_weight() if next_norm is not None else None
             xw = ctx.buffer(out_name + "_preweighted", (M, self.out_features), torch.bfloat16) if nw is not None else None
             ops.decode_linear(self.weight, x, row_scale=row_scale, epilogue="residual", residual_out=residual,
-                              sumsq_out=sumsq, next_norm=(nw, xw) if nw is not None else None, fetch_ahead=fetch_ahead)
+                              sumsq_out=sumsq, next_norm=(nw, xw) if nw is not None else None, fetch_ahead=fetch_ahead,
+                              err=ctx.error_flag)
             return AddedToResidual(sumsq, xw, nw)
         n_out = self.out_features // 2 if epilogue == "silu_mul" else self.out_features
         if may_split and epilogue == "none" and not fused:
@@ -77,7 +79,8 @@ class Linear(Part):
                 return part
         out = ctx.buffer(out_name, (M, n_out), out_dtype or ctx.act_dtype)
         if fused:
-            ops.decode_linear(self.weight, x, out=out, epilogue=epilogue, row_scale=row_scale, fetch_ahead=fetch_ahead)
+            ops.decode_linear(self.weight, x, out=out, epilogue=epilogue, row_scale=row_scale, fetch_ahead=fetch_ahead,
+                              err=ctx.error_flag)
             return out
         ops.linear(x, self.weight, out, epilogue=epilogue, workspace=ctx.buffer, err=ctx.error_flag)
         return out

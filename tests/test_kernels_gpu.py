@@ -218,9 +218,21 @@ def test_tcgen05_products(ops, M, N, K, tile_n):
         close(out, ref, torch.bfloat16, scale=4)
 
 
+@pytest.fixture
+def decode_kernel(ops, request):
+    """Which of the two decode product kernels ``ops.decode_linear`` runs: one block over all of K (csrc/gemm_decode.cu)
+    or blocks that walk their rows along any K (csrc/gemm_stream.cu)."""
+    old, ops.decode_kernel = ops.decode_kernel, request.param
+    yield request.param
+    ops.decode_kernel = old
+
+
 @pytest.mark.parametrize("M", [1, 5, 8, 16])
-@pytest.mark.parametrize("N, K", [(96, 64), (1000, 200), (4096, 1024), (1024, 2048), (1032, 3072)])
-def test_decode_products_with_norm_and_residual_folded_in(ops, M, N, K):
+@pytest.mark.parametrize("decode_kernel, N, K", [
+    ("decode", 96, 64), ("decode", 1000, 200), ("decode", 4096, 1024), ("decode", 1024, 2048), ("decode", 1032, 3072),
+    ("stream", 96, 64), ("stream", 1000, 200), ("stream", 4096, 1024), ("stream", 1032, 3072), ("stream", 1000, 4096 + 72),
+    ("stream", 5120, 5120), ("stream", 2600, 2056), ("auto", 520, 12288)], indirect=["decode_kernel"])
+def test_decode_products_with_norm_and_residual_folded_in(ops, decode_kernel, M, N, K):
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5)
     assert ops.decode_linear_takes(M, K, w)
     ref = torch.empty(M, N, dtype=torch.float32, device=DEV)
@@ -228,27 +240,33 @@ def test_decode_products_with_norm_and_residual_folded_in(ops, M, N, K):
     # plain input, float32 and bfloat16 output
     for od in (torch.bfloat16, torch.float32):
         out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
-        ops.decode_linear(w, x, out=out)
+        ops.decode_linear(w, x, err=errword(), out=out)
         close(out, ref, od, scale=4)
     # residual epilogue: residual += x W^T, the sums of squares of the new residual per strip of 16 columns, and
     # the new residual times the next norm's weight
     res = rnd(M, N, seed=3)
     want = res + ref
-    parts = ops.decode_linear_sumsq_parts(N)
-    width = 16 if parts == (N + 15) // 16 else 8             # narrow strips where 16 columns would make few blocks
-    assert parts == (N + width - 1) // width
+    parts = ops.decode_linear_sumsq_parts(N, K)
+    if decode_kernel == "decode":
+        width = 16 if parts == (N + 15) // 16 else 8         # narrow strips where 16 columns would make few blocks
+        assert parts == (N + width - 1) // width
+        edges = [min(N, p * width) for p in range(parts + 1)]
+    else:        # a part a block: block b adds the columns of the groups (of 32) whose first piece of K lies in its share
+        groups, its = (N + 31) // 32, (K + 511) // 512
+        assert parts == min(groups * its, ops.sm_count())
+        ends = [-(-(groups * its * b // parts) // its) for b in range(parts + 1)]   # groups begun before block b starts
+        edges = [min(N, 32 * e) for e in ends]
     sumsq = torch.full((parts, M), float("nan"), device=DEV)
     next_w = 1 + 0.3 * rnd(N, seed=6)
     xw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.decode_linear(w, x, epilogue="residual", residual_out=res, sumsq_out=sumsq, next_norm=(next_w, xw))
+    ops.decode_linear(w, x, err=errword(), epilogue="residual", residual_out=res, sumsq_out=sumsq, next_norm=(next_w, xw))
     close(res, want, torch.float32, scale=50)
-    padded = torch.nn.functional.pad(res, (0, parts * width - N))
-    want_sq = padded.view(M, parts, width).pow(2).sum(-1).t()
+    want_sq = torch.stack([res[:, a:b].pow(2).sum(-1) for a, b in zip(edges, edges[1:])])
     assert torch.allclose(sumsq, want_sq, rtol=1e-4, atol=1e-5)
     assert torch.equal(xw, (res * next_w).to(torch.bfloat16))
     res2, sumsq2 = rnd(M, N, seed=3), torch.empty_like(sumsq)
     later = rnd(777, 40, dtype=torch.bfloat16, seed=9)                                       # asked into L2 on the way
-    ops.decode_linear(w, x, epilogue="residual", residual_out=res2, sumsq_out=sumsq2, fetch_ahead=later)    # no next norm
+    ops.decode_linear(w, x, err=errword(), epilogue="residual", residual_out=res2, sumsq_out=sumsq2, fetch_ahead=later)    # no next norm
     assert torch.equal(res2, res) and torch.equal(sumsq2, sumsq)
     # the other half of that norm: a product over a pre-weighted residual applies the rows' factors to its results
     K_parts = (K + 15) // 16
@@ -265,17 +283,17 @@ def test_decode_products_with_norm_and_residual_folded_in(ops, M, N, K):
     sharp = ((pre.double() @ w.double().t()) * factor).float()
     for od in (torch.bfloat16, torch.float32):
         out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
-        ops.decode_linear(w, pre, out=out, row_scale=(sq_in, 1e-5))
+        ops.decode_linear(w, pre, err=errword(), out=out, row_scale=(sq_in, 1e-5))
         close(out, sharp, od, scale=4)
         close(out, refn, torch.bfloat16, scale=4)
     res3, sumsq3 = rnd(M, N, seed=7), torch.empty_like(sumsq)
     want3 = res3 + sharp
-    ops.decode_linear(w, pre, epilogue="residual", residual_out=res3, sumsq_out=sumsq3, row_scale=(sq_in, 1e-5))
+    ops.decode_linear(w, pre, err=errword(), epilogue="residual", residual_out=res3, sumsq_out=sumsq3, row_scale=(sq_in, 1e-5))
     close(res3, want3, torch.float32, scale=50)
     if N % 2 == 0:
         I = N // 2
         out2, ref2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV), torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
-        ops.decode_linear(w, pre, out=out2, epilogue="silu_mul", row_scale=(sq_in, 1e-5))
+        ops.decode_linear(w, pre, err=errword(), out=out2, epilogue="silu_mul", row_scale=(sq_in, 1e-5))
         plain_ops.linear(xn, w, ref2, epilogue="silu_mul")
         close(out2, ref2, torch.bfloat16, scale=4)
 
