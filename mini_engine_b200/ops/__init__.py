@@ -713,10 +713,10 @@ def decode_fused_takes(qkv: torch.Tensor, head_dim: int, pool: torch.Tensor, pag
 # The form of the decode partition kernel: "one_tile" (K and V pass through the same shared-memory tile, five blocks
 # an SM), "two_tiles" (a tile each, three blocks an SM) or "tile_and_half" (half a tile for V beside K's, four blocks).
 DECODE_FORMS = {"one_tile": 0, "two_tiles": 2, "tile_and_half": 3}
-# "auto": by the number of partitions with keys.  Up to what three blocks an SM hold at once, two tiles (all loads
-# in flight together: batch 1, 0.78 ms a step against 0.80 with one tile); up to about four times that, a tile and a
-# half (batch 8: 0.92 against 0.97, batch 16: 1.23 against 1.27); beyond, one tile (batch 64: 2.60 against 2.90 and
-# 2.98; batch 256: 7.6 against 9.1 and 8.7).
+# "auto": by the number of partitions with keys.  Up to what three blocks an SM hold at once, two tiles (all loads in
+# flight together); beyond, one tile (more blocks an SM).  In a step of the 0.6B shape at 1,024 tokens of context:
+# batch 4, 0.770 ms against 0.815 with one tile; batch 8, 0.885 with one tile against 0.898 with two and 0.938 with a
+# tile and a half; batch 16, 1.199 against 1.221 and 1.252; batch 64, 2.50 against 2.89 and 3.08.
 decode_form = "auto"
 
 
@@ -734,12 +734,7 @@ def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, pa
         blocks = meta.num_decodes * num_kv_heads * ((num_heads // num_kv_heads + 15) // 16) \
             * ((typical + DECODE_PARTITION - 1) // DECODE_PARTITION)
         resident = 3 * sm_count()                   # blocks of the two-tile form that the device holds at once
-        if blocks <= resident:
-            form = "two_tiles"
-        elif blocks <= 4 * resident and (DECODE_PARTITION // 2) % page_size == 0:
-            form = "tile_and_half"
-        else:
-            form = "one_tile"
+        form = "two_tiles" if blocks <= resident else "one_tile"
     D = meta.num_decodes
     parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
     room = max(parts, (getattr(meta, "scratch_context_len", 0) + DECODE_PARTITION - 1) // DECODE_PARTITION)
