@@ -387,8 +387,10 @@ def prefill_on_device(runner, cache, prompt, reps: int, warmup: int, portion: in
 
 def kernel_table(model: Model, runner, cache, args, pk: dict, batch: int, prompt_len: int, T: int) -> dict:
     """One decode step of ``batch`` requests and one prefill step of ``T`` tokens launched kernel by kernel, every
-    launch between two CUDA events: per kind of kernel the mean microseconds of a launch, the bytes (decode) or
-    flops (prefill) it has to move or do, and the fraction of the measured peak that makes."""
+    launch between two CUDA events: per kind of kernel the mean microseconds of a launch (less what an empty event
+    pair measures, ``event_pair_us``), the bytes (decode) or flops (prefill) it has to move or do, and the fraction
+    of the measured peak that makes.  Kernels run one after the other here; in the step itself each starts under its
+    predecessor, so these add up to more than the step."""
     import torch
     from mini_engine_b200 import ops
     from mini_engine_b200.cache.manager import CacheHolder
@@ -421,7 +423,22 @@ def kernel_table(model: Model, runner, cache, args, pk: dict, batch: int, prompt
             ops.timeline = None
         return got
 
-    out = {}
+    # What two events around NOTHING measure, in the same setting (device kept busy, commands queued): an event pair
+    # costs the stream a few microseconds by itself, which is not the kernel's time.  It is taken off every figure.
+    def event_overhead_us() -> float:
+        busy = torch.empty(1 << 28, dtype=torch.float32, device="cuda")
+        for _ in range(8):
+            busy.add_(1.0)
+        pairs = []
+        for _ in range(200):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            e1.record()
+            pairs.append((e0, e1))
+        torch.cuda.synchronize()
+        return statistics.median(a.elapsed_time(b) for a, b in pairs) * 1e3
+    overhead = event_overhead_us()
+    out = {"event_pair_us": round(overhead, 2)}
     # decode
     prompts = random_prompts(batch, prompt_len, model.vocab, args.seed + 3)
     holders = prefill_requests(runner, cache, prompts, 4)
@@ -433,7 +450,7 @@ def kernel_table(model: Model, runner, cache, args, pk: dict, batch: int, prompt
     work = {name: n * k * item for name, (n, k) in shapes.items()}
     work["attn_decode_fused"] = work["attn_decode"] = batch * ctx * 2 * nkv * hd * item
     for key, us in sorted(got.items()):
-        mean = sum(us) / len(us)
+        mean = max(sum(us) / len(us) - overhead, 0.1)
         row = {"us": round(mean, 2), "launches": len(us)}
         if key in work:
             row["bytes"] = int(work[key])
@@ -448,7 +465,7 @@ def kernel_table(model: Model, runner, cache, args, pk: dict, batch: int, prompt
     flops = {name: 2.0 * T * n * k for name, (n, k) in shapes.items() if name != "logits"}
     flops["attn_prefill_tcgen05"] = flops["attn_prefill"] = flops["attn_chunk"] = 2.0 * nh * hd * T * T
     for key, us in sorted(got.items()):
-        mean = sum(us) / len(us)
+        mean = max(sum(us) / len(us) - overhead, 0.1)
         row = {"us": round(mean, 2), "launches": len(us)}
         if key in flops:
             row["flops"] = flops[key]
