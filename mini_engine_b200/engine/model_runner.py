@@ -60,6 +60,7 @@ class _StepGraph:
         self.logits: Optional[torch.Tensor] = None
         self.tokens: Optional[torch.Tensor] = None
         self.launches = 0
+        self.form: Optional[str] = None          # the decode attention form the capture was tuned to, if it was
 
 
 def plan_cache_groups(model: DecoderModel) -> tuple[list[GroupSpec], dict[int, tuple[int, int]], dict[int, StateNeed]]:
@@ -134,6 +135,7 @@ class ModelRunner:
         self._prefill_graphs: dict[tuple, _StepGraph] = {}
         self._prefill_seen: dict[tuple, int] = {}
         self.graph_launches = 0          # kernels replayed from graphs (they bypass ops.launches)
+        self.tune_decode_form = True     # a captured decode step keeps the fastest form of the decode attention kernel
         self.pool_sizing: dict = {}      # what the pool was sized from, when it was sized here
         self.num_pages = num_pages if num_pages > 0 else self._size_pool(gpu_memory_utilization)
         self.kv_pools = self._make_pools(self.num_pages)
@@ -464,6 +466,34 @@ class ModelRunner:
         g.launches = ops.launches - before
         g.graph = graph
 
+    def _capture_fastest_form(self, g: _StepGraph, token_ids: torch.Tensor) -> None:
+        """Capture a decode step once for every form of the decode attention kernel that takes the shape, replay each a
+        few times and keep the fastest.  Which form wins depends on the batch, the context and the GPU at hand (two B200
+        boxes ranked them differently at a batch of 8), so it is measured where it matters instead of guessed; a replay
+        of the same step writes the same values again, so the extra replays change nothing."""
+        forms = ops.decode_forms_for(self.page_size) if (self.tune_decode_form and ops.decode_form == "auto") else [None]
+        best = None
+        try:
+            for form in forms:
+                ops.decode_form = form or "auto"
+                self._capture(g, token_ids, True)
+                if len(forms) == 1:
+                    return
+                for _ in range(2):
+                    g.graph.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(6):
+                    g.graph.replay()
+                e1.record()
+                e1.synchronize()
+                t = e0.elapsed_time(e1)
+                if best is None or t < best[0]:
+                    best = (t, form, g.graph, g.logits, g.tokens, g.launches)
+        finally:
+            ops.decode_form = "auto"
+        _, g.form, g.graph, g.logits, g.tokens, g.launches = best
+
     def _step_prefill_graph(self, items: Sequence[StepItem], sample: bool) -> Optional[StepResult]:
         """One request's portion of a prompt from a graph; None while the shape has not come twice.
 
@@ -529,7 +559,7 @@ class ModelRunner:
                                         fill_ctx=g.graph is None,
                                         typical_context=ctx_bucket * 3 // 4 if bucket < 32 else max(ctx_bucket - 128, 1))
         if g.graph is None:
-            self._capture(g, token_ids, True)
+            self._capture_fastest_form(g, token_ids)
         g.graph.replay()
         self.graph_launches += g.launches
         n = self.last_num_wanted

@@ -720,6 +720,11 @@ DECODE_FORMS = {"one_tile": 0, "two_tiles": 2, "tile_and_half": 3}
 decode_form = "auto"
 
 
+def decode_forms_for(page_size: int) -> list[str]:
+    """The forms of the fused decode kernel that take pages of ``page_size`` tokens (for a caller that times them)."""
+    return [f for f in DECODE_FORMS if f != "tile_and_half" or (DECODE_PARTITION // 2) % page_size == 0]
+
+
 def attention_decode_fused(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta, scale, window,
                            q_weight, k_weight, eps, cos_sin, slot_mapping, form: Optional[str] = None) -> None:
     """Decode attention over requests [0, meta.num_decodes) straight from the q|k|v product's rows: the kernel
