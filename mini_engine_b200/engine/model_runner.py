@@ -176,17 +176,24 @@ class ModelRunner:
             torch.cuda.synchronize(dev)
             free, total = torch.cuda.mem_get_info(dev)
             return total - free
+
+        def held() -> int:
+            return torch.cuda.memory_allocated(dev)
+        # What a step takes is the growth of the device's used memory, or, where the allocator served the step from
+        # memory it held already (a process that has run other engines), the growth of what the allocator has given out.
         torch.cuda.empty_cache()
-        base = used()
+        base, base_held = used(), held()
+        torch.cuda.reset_peak_memory_stats(dev)
         L = self.max_model_len
         m = min(L, self.max_num_batched_tokens)
         n = max(1, min(self.max_num_batched_tokens // m, self.max_num_seqs))
         self.step([StepItem(dummy(m), [0] * m, 0, [m - 1]) for _ in range(n)], sample=True)
-        after_prompts = used()
+        after_prompts, prompts_held = used(), held()
+        prompt_bytes = max(after_prompts - base, torch.cuda.max_memory_allocated(dev) - base_held)
+        torch.cuda.reset_peak_memory_stats(dev)
         self.step([StepItem(dummy(L), [0], L - 1, [0], (1.0, 0)) for _ in range(self.max_num_seqs)], sample=True)
-        after_tokens = used()
+        token_bytes = max(used() - after_prompts, torch.cuda.max_memory_allocated(dev) - prompts_held, 0)
         self.check_device_errors()
-        prompt_bytes, token_bytes = after_prompts - base, max(after_tokens - after_prompts, 0)
         allowance = 0
         if graphs:
             # the arena of a batch bucket grows with the bucket: all of them together, in units of the largest step

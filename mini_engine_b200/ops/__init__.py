@@ -73,6 +73,7 @@ def require_extension() -> ctypes.CDLL:
     lib.me_gemm_decode_sumsq_parts.argtypes = [_I]
     lib.me_gemm_stream_sumsq_parts.argtypes = [_I, _I]
     lib.me_gemm_stream_x_box_rows.argtypes = [_I]
+    lib.me_gemm_stream_w_box_rows.argtypes = [_I]
     lib.me_attn_decode_fused_takes.argtypes = [_I, _I]
     lib.me_gemm_skinny_splits.argtypes = [_I]
     _lib = lib
@@ -325,17 +326,23 @@ def _decode_uses_stream(K: int) -> bool:
     return decode_kernel == "stream" or (decode_kernel == "auto" and K > DECODE_MAX_K)
 
 
-# Which products over a K beyond DECODE_MAX_K run csrc/gemm_stream.cu: "residual" (those that add into the residual
-# stream: no partial results for a norm kernel to add up; the others go to the library, which streams plain weights
-# faster) or "all".  A switch for comparisons.
-stream_products = "residual"
+# Which products over a K beyond DECODE_MAX_K run csrc/gemm_stream.cu: "all", or "residual" (only those that add into
+# the residual stream; the others go to the library).  A switch for comparisons.
+stream_products = "all"
+# Weights from this many elements on (32 MB of bfloat16: the LM head) go through csrc/gemm_stream.cu in ``linear`` too
+# when the batch has up to 16 rows: a product that long is all stream, and that kernel streams fastest.
+STREAM_MIN_WEIGHT_ELEMENTS = 1 << 24
+
+
+def _decode_operands_ok(M: int, K: int, weight: torch.Tensor) -> bool:
+    return (weight.is_cuda and weight.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0
+            and weight.data_ptr() % 16 == 0)
 
 
 def decode_linear_takes(M: int, K: int, weight: torch.Tensor, adds_to_residual: bool = True) -> bool:
     """Whether a decode product with norm / residual folded in (csrc/gemm_decode.cu, csrc/gemm_stream.cu: up to 16
     rows) takes the shape; ``adds_to_residual``: the product is one whose result is added to the residual stream."""
-    if not (weight.is_cuda and weight.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0
-            and weight.data_ptr() % 16 == 0):
+    if not _decode_operands_ok(M, K, weight):
         return False
     if _decode_uses_stream(K):
         return decode_kernel == "stream" or stream_products == "all" or adds_to_residual
@@ -356,16 +363,20 @@ def _stream_work_buffers(device) -> tuple[torch.Tensor, torch.Tensor]:
     return ws
 
 
-def decode_linear_sumsq_parts(N: int, K: int = 0) -> int:
-    """Parts in which the residual epilogue of ``decode_linear`` writes sums of squares, for N columns over K."""
+def decode_linear_sumsq_parts(N: int, K: int = 0, stream: Optional[bool] = None) -> int:
+    """Parts in which the residual epilogue of ``decode_linear`` writes sums of squares, for N columns over K
+    (``stream``: by which of the two kernels; None: the one that ``decode_kernel`` picks for K)."""
     lib = _lib or require_extension()
-    return lib.me_gemm_stream_sumsq_parts(N, K) if _decode_uses_stream(K) else lib.me_gemm_decode_sumsq_parts(N)
+    stream = _decode_uses_stream(K) if stream is None else stream
+    return lib.me_gemm_stream_sumsq_parts(N, K) if stream else lib.me_gemm_decode_sumsq_parts(N)
 
 
 def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.Tensor] = None, epilogue: str = "none",
                   row_scale=None, residual_out: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None,
-                  next_norm=None, fetch_ahead: Optional[torch.Tensor] = None, err: Optional[torch.Tensor] = None) -> None:
-    """One decode product with its neighbours folded in (csrc/gemm_decode.cu).
+                  next_norm=None, fetch_ahead: Optional[torch.Tensor] = None, err: Optional[torch.Tensor] = None,
+                  kernel: Optional[str] = None) -> None:
+    """One decode product with its neighbours folded in (csrc/gemm_decode.cu, csrc/gemm_stream.cu; ``kernel``:
+    "stream" asks for the latter whatever ``decode_kernel`` says).
 
     ``x``: bfloat16 [M, K].  ``row_scale`` = (sums of squares float32 [parts, M], eps): x is a residual times a
     norm's weight, and the float32 results of row m are multiplied by rsqrt(sum / K + eps), which completes that
@@ -377,7 +388,9 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
     epi = {"none": 0, "silu_mul": 1, "residual": 2}[epilogue]
     M, K = x.shape
     _need(x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "decode_linear: x")
-    _need(decode_linear_takes(M, K, weight) and weight.shape[1] == K and weight.is_contiguous(), "decode_linear: shape not taken")
+    stream = kernel == "stream" or _decode_uses_stream(K)
+    _need((stream or K <= DECODE_MAX_K) and _decode_operands_ok(M, K, weight) and weight.shape[1] == K
+          and weight.is_contiguous(), "decode_linear: shape not taken")
     sumsq, eps = row_scale if row_scale is not None else (None, 0.0)
     if sumsq is not None:
         _need(sumsq.dtype == torch.float32 and sumsq.is_contiguous() and sumsq.dim() == 2 and sumsq.shape[1] == M,
@@ -387,7 +400,7 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
     if epi == 2:
         _need(residual_out.dtype == torch.float32 and residual_out.is_contiguous() and tuple(residual_out.shape) == (M, N)
               and sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous()
-              and tuple(sumsq_out.shape) == (decode_linear_sumsq_parts(N, K), M), "decode_linear: residual output")
+              and tuple(sumsq_out.shape) == (decode_linear_sumsq_parts(N, K, stream), M), "decode_linear: residual output")
         if nw is not None:
             _need(nw.dtype == torch.float32 and tuple(nw.shape) == (N,) and nw.is_contiguous() and xw.dtype == torch.bfloat16
                   and tuple(xw.shape) == (M, N) and xw.is_contiguous(), "decode_linear: pre-weighted output")
@@ -396,12 +409,12 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
         _need(next_norm is None, "decode_linear: the pre-weighted output belongs to the residual epilogue")
         _need(tuple(out.shape) == (M, N) and out.stride(1) == 1, "decode_linear: output shape")
         yp, ydt, ldy = out.data_ptr(), _dt(out), out.stride(0)
-    if _decode_uses_stream(K):
+    if stream:
         _need(err is not None, "decode_linear: the streaming kernel needs the step's error word (err=)")
         lib = _lib or require_extension()
         partials, flags = _stream_work_buffers(x.device)
         _call("me_gemm_stream", epi, matrix_tensor_map(x, lib.me_gemm_stream_x_box_rows(M)).ptr, _ptr(sumsq),
-              sumsq.shape[0] if sumsq is not None else 0, float(eps), matrix_tensor_map(weight, 16).ptr, yp, ydt, ldy,
+              sumsq.shape[0] if sumsq is not None else 0, float(eps), matrix_tensor_map(weight, lib.me_gemm_stream_w_box_rows(epi)).ptr, yp, ydt, ldy,
               _ptr(residual_out), _ptr(sumsq_out), _ptr(nw), _ptr(xw), M, N, K, partials.data_ptr(), flags.data_ptr(),
               err.data_ptr(), _stream())
         return
@@ -517,6 +530,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
     N = weight.shape[0] // 2 if epi else weight.shape[0]
     _need(tuple(out.shape) == (M, N), f"linear: output is {tuple(out.shape)}, expected {(M, N)}")
     if M == 0:
+        return
+    if (err is not None and epi == 0 and weight.numel() >= STREAM_MIN_WEIGHT_ELEMENTS and skinny_splits(M, K, x, weight) > 0
+            and out.dtype in (torch.bfloat16, torch.float32)):
+        decode_linear(weight, x, out=out, err=err, kernel="stream")
+        _remember(key, sig, before)
         return
     if skinny_splits(M, K, x, weight) == 1 and (epi == 0 or out.dtype == torch.bfloat16):
         _call("me_gemm_skinny", x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), _dt(out), out.stride(0),

@@ -251,11 +251,11 @@ def test_decode_products_with_norm_and_residual_folded_in(ops, decode_kernel, M,
         width = 16 if parts == (N + 15) // 16 else 8         # narrow strips where 16 columns would make few blocks
         assert parts == (N + width - 1) // width
         edges = [min(N, p * width) for p in range(parts + 1)]
-    else:        # a part a block: block b adds the columns of the groups (of 32) whose first piece of K lies in its share
-        groups, its = (N + 31) // 32, (K + 511) // 512
+    else:        # a part a block: block b adds the columns of the groups (of 128) whose first piece of K lies in its share
+        groups, its = (N + 127) // 128, (K + 127) // 128
         assert parts == min(groups * its, ops.sm_count())
         ends = [-(-(groups * its * b // parts) // its) for b in range(parts + 1)]   # groups begun before block b starts
-        edges = [min(N, 32 * e) for e in ends]
+        edges = [min(N, 128 * e) for e in ends]
     sumsq = torch.full((parts, M), float("nan"), device=DEV)
     next_w = 1 + 0.3 * rnd(N, seed=6)
     xw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
@@ -296,6 +296,27 @@ def test_decode_products_with_norm_and_residual_folded_in(ops, decode_kernel, M,
         ops.decode_linear(w, pre, err=errword(), out=out2, epilogue="silu_mul", row_scale=(sq_in, 1e-5))
         plain_ops.linear(xn, w, ref2, epilogue="silu_mul")
         close(out2, ref2, torch.bfloat16, scale=4)
+
+
+@pytest.mark.parametrize("M", [1, 7, 16])
+@pytest.mark.parametrize("N, K", [(17001, 1000), (8300, 2048 + 24)])
+def test_vocabulary_sized_products_of_few_rows(ops, M, N, K):
+    # a weight of 32 MB and more under up to 16 rows (the LM head in decode) streams through csrc/gemm_stream.cu:
+    # our kernel, both output types, rows beyond N and columns beyond K filled with zeros by the tensor maps
+    assert N * K >= ops.STREAM_MIN_WEIGHT_ELEMENTS
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5)
+    w[N - 3] *= 400                                                 # one row that stands out, near the ragged end
+    ref = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    plain_ops.linear(x, w, ref)
+    for od in (torch.float32, torch.bfloat16):
+        before, launched = ops.library_calls, ops.launches
+        out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
+        ops.linear(x, w, out, err=errword())
+        assert ops.library_calls == before and ops.launches == launched + 1
+        assert (out.float().abs().argmax(dim=1) == N - 3).all()
+        shrink = torch.ones(N, device=DEV)
+        shrink[N - 3] = 1 / 400                                         # (that column at the others' magnitude)
+        close(out.float() * shrink, ref * shrink, od, scale=4)
 
 
 def test_linear_rows_do_not_depend_on_the_batch(ops):
