@@ -80,6 +80,7 @@ def parse_args():
     p.add_argument("--batches", default="1,8,64", help="decode mode: the batch sizes")
     p.add_argument("--prompt-len", type=int, default=0, help="0: 1,024 (2,048 for the 32B decode points and prefill mode)")
     p.add_argument("--context", type=int, default=0, help="engine context length; 0: 4,096 (8,192 for 8b and 32b)")
+    p.add_argument("--page-size", type=int, default=16, help="tokens a page of the cache")
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
     p.add_argument("--dtype", default="bfloat16")
     p.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
@@ -265,7 +266,7 @@ def decode_bytes(cfg: dict, layers: int, itemsize: int, batch: int, mean_ctx: fl
 # ---- timed pieces ------------------------------------------------------------------------------------------------
 def make_engine(model: Model, args, *, max_seqs: int, budget: int, context: int, pages: int = -1, **kw):
     from mini_engine_b200 import LLM
-    opts = dict(dtype=args.dtype, kvcache_block_size=16, num_kvcache_blocks=pages, max_num_seqs=max_seqs,
+    opts = dict(dtype=args.dtype, kvcache_block_size=args.page_size, num_kvcache_blocks=pages, max_num_seqs=max_seqs,
                 max_num_batched_tokens=budget, max_model_len=context, seed=args.seed, use_cuda_graphs=not args.no_graphs)
     opts.update(model.engine_args)
     opts.update(kw)

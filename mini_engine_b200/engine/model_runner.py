@@ -136,6 +136,7 @@ class ModelRunner:
         self._prefill_seen: dict[tuple, int] = {}
         self.graph_launches = 0          # kernels replayed from graphs (they bypass ops.launches)
         self.tune_decode_form = True     # a captured decode step keeps the fastest form of the decode attention kernel
+        self.tune_decode_max_bucket = 32 # ... measured for batch buckets below this one; by rule from there on
         self.pool_sizing: dict = {}      # what the pool was sized from, when it was sized here
         self.num_pages = num_pages if num_pages > 0 else self._size_pool(gpu_memory_utilization)
         self.kv_pools = self._make_pools(self.num_pages)
@@ -477,8 +478,14 @@ class ModelRunner:
         """Capture a decode step once for every form of the decode attention kernel that takes the shape, replay each a
         few times and keep the fastest.  Which form wins depends on the batch, the context and the GPU at hand (two B200
         boxes ranked them differently at a batch of 8), so it is measured where it matters instead of guessed; a replay
-        of the same step writes the same values again, so the extra replays change nothing."""
-        forms = ops.decode_forms_for(self.page_size) if (self.tune_decode_form and ops.decode_form == "auto") else [None]
+        of the same step writes the same values again, so the extra replays change nothing.
+
+        Only small batches are measured (buckets below ``tune_decode_max_bucket``): there the step is a chain of short
+        kernels and the forms lie close together; a large batch has many blocks an SM, where one form wins by rule, its
+        graphs are many (narrow context buckets) and each measurement costs a tenth of a second: a workload of 256
+        requests that end one after the other spent a third of its time measuring."""
+        tune = self.tune_decode_form and ops.decode_form == "auto" and g.bucket < self.tune_decode_max_bucket
+        forms = ops.decode_forms_for(self.page_size) if tune else [None]
         best = None
         try:
             for form in forms:
@@ -490,7 +497,7 @@ class ModelRunner:
                     g.graph.replay()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                for _ in range(6):
+                for _ in range(4):
                     g.graph.replay()
                 e1.record()
                 e1.synchronize()
