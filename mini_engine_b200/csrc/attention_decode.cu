@@ -173,6 +173,58 @@ decode_partition_kernel(const T* __restrict__ qkv, int64_t q_row_stride, const T
   }
 }
 
+// The end of a partition step on the tensor cores: the four warps' (m, l, O) for the rows that are real heads, merged in
+// warp order and written as the partition's result.  The results [4][16][HD] float32 go over the K tile ``po`` (every warp
+// is done with it), the 8-float pieces of row r at piece ^ (r & 7): the eight rows that a warp's store touches then lie in
+// different banks (unswizzled, rows 512 bytes apart, they shared them all).  The weight of warp w's share of row r,
+// exp2((m_w - M) scale) with M the row's maximum over the warps, is computed once per (w, r), not once per element.
+template <int HD>
+__device__ __forceinline__ void merge_warps_of_partition(float* po, float (*w_m)[16], float (*w_l)[16], float (*w_f)[16],
+                                                         float (*w_fl)[16], const float (&o)[HD / 8][4], float mx0, float l0,
+                                                         float mx1, float l1, int n_g, float sl2, float scale,
+                                                         float* __restrict__ tmp_out, float* __restrict__ tmp_m,
+                                                         float* __restrict__ tmp_l, int64_t slot0, int max_parts) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  auto po_at = [&](int w, int r, int d) -> float* { return po + (w * 16 + r) * HD + ((((d >> 3) ^ (r & 7)) << 3) | (d & 7)); };
+  if (t4 == 0) {
+    w_m[warp][g] = mx0;
+    w_l[warp][g] = l0;
+    w_m[warp][g + 8] = mx1;
+    w_l[warp][g + 8] = l1;
+  }
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) {
+    if (g < n_g) *reinterpret_cast<float2*>(po_at(warp, g, i * 8 + 2 * t4)) = make_float2(o[i][0], o[i][1]);
+    if (g + 8 < n_g) *reinterpret_cast<float2*>(po_at(warp, g + 8, i * 8 + 2 * t4)) = make_float2(o[i][2], o[i][3]);
+  }
+  __syncthreads();
+  if (tid < 64) {
+    const int w = tid >> 4, r = tid & 15;
+    const float M = fmaxf(fmaxf(w_m[0][r], w_m[1][r]), fmaxf(w_m[2][r], w_m[3][r]));
+    const float mw = w_m[w][r];
+    const float f = (M == -INFINITY || mw == -INFINITY) ? 0.f : exp2f((mw - M) * sl2);
+    w_f[w][r] = f;
+    w_fl[w][r] = f * w_l[w][r];
+    if (w == 0 && r < n_g) tmp_m[slot0 + (int64_t)r * max_parts] = M == -INFINITY ? -INFINITY : M * scale;   // natural-log units, as the merge kernel expects
+  }
+  __syncthreads();
+  if (tid < n_g) tmp_l[slot0 + (int64_t)tid * max_parts] = ((w_fl[0][tid] + w_fl[1][tid]) + w_fl[2][tid]) + w_fl[3][tid];
+  for (int idx = tid; idx < n_g * (HD / 4); idx += DEC_THREADS) {
+    const int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = w_f[w][r];
+      const float4 v = *reinterpret_cast<const float4*>(po_at(w, r, d));
+      acc.x += f * v.x;
+      acc.y += f * v.y;
+      acc.z += f * v.z;
+      acc.w += f * v.w;
+    }
+    *reinterpret_cast<float4*>(tmp_out + (slot0 + (int64_t)r * max_parts) * HD + d) = acc;
+  }
+}
+
 // ---- the partition step on the tensor cores -----------------------------------------------------
 // The query heads of one key/value head (up to 16) form the rows of an m16 strip; each of the four
 // warps takes 32 keys of the 128-key partition: S = Q K^T and O = P V with mma.sync m16n8k16, softmax
@@ -189,13 +241,13 @@ decode_partition_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, 
                             float* __restrict__ tmp_l, int max_parts) {
   using namespace mma_prims;
   extern __shared__ __align__(128) unsigned char dec_smem[];
-  __shared__ float w_m[4][16], w_l[4][16];
+  __shared__ float w_m[4][16], w_l[4][16], w_f[4][16], w_fl[4][16];
   constexpr int PIECES = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8;
   const int G = nh / nkv, head_tiles = (G + 15) / 16;
   const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * 16;
   const int z = blockIdx.z;
   const int L = context_lens[b];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, t4 = lane & 3;
   const int n_g = min(16, G - g0);
   const int lo_w = window > 0 ? max(0, L - window) : 0;
   const int part_lo = z * DEC_PART, part_hi = min(L, part_lo + DEC_PART);
@@ -318,42 +370,8 @@ decode_partition_mma_kernel(const bf16* __restrict__ qkv, int64_t q_row_stride, 
       mma_bf16(o[2 * np + 1], pf[kk], bfr[2], bfr[3]);
     }
   }
-  // Each warp's (m, l, O) for the rows that are real heads, then the merge in warp order.
-  float* po = reinterpret_cast<float*>(ks);          // [4][16][HD] float32, over the K tile
-  if (t4 == 0) {
-    w_m[warp][g] = mx0;
-    w_l[warp][g] = l0;
-    w_m[warp][g + 8] = mx1;
-    w_l[warp][g + 8] = l1;
-  }
-#pragma unroll
-  for (int i = 0; i < NT_O; ++i) {
-    if (g < n_g) *reinterpret_cast<float2*>(po + ((warp * 16 + g) * HD + i * 8 + 2 * t4)) = make_float2(o[i][0], o[i][1]);
-    if (g + 8 < n_g) *reinterpret_cast<float2*>(po + ((warp * 16 + g + 8) * HD + i * 8 + 2 * t4)) = make_float2(o[i][2], o[i][3]);
-  }
-  __syncthreads();
-  for (int idx = tid; idx < n_g * HD; idx += DEC_THREADS) {
-    const int r = idx / HD, d = idx - r * HD;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, w_m[w][r]);
-    float lt = 0.f, acc = 0.f;
-    if (M > -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float mw = w_m[w][r];
-        const float f = mw == -INFINITY ? 0.f : exp2f((mw - M) * sl2);
-        lt += f * w_l[w][r];
-        acc += f * po[(w * 16 + r) * HD + d];
-      }
-    }
-    const int64_t slot = slot0 + (int64_t)r * max_parts;
-    tmp_out[slot * HD + d] = acc;
-    if (d == 0) {
-      tmp_m[slot] = M == -INFINITY ? -INFINITY : M * scale;     // natural-log units, as the merge kernel expects
-      tmp_l[slot] = lt;
-    }
-  }
+  merge_warps_of_partition<HD>(reinterpret_cast<float*>(ks), w_m, w_l, w_f, w_fl, o, mx0, l0, mx1, l1, n_g, sl2, scale, tmp_out,
+                               tmp_m, tmp_l, slot0, max_parts);
 }
 
 template <int HD>
@@ -440,17 +458,19 @@ struct DecodePrep {
 // tokens then fits the GPU in one wave with most of its loads in flight before the dependency resolves).
 // With at most 8 query heads a group the Q tile keeps 8 rows (the upper half of the m16 strip reads one chunk of
 // zeros), and with VBUF 0 the registers are held to what lets six blocks share an SM.
-template <int HD, bool FUSED, int VBUF, int QROWS>
-__global__ void __launch_bounds__(DEC_THREADS, (VBUF == 0 && QROWS == 8) ? 6 : 1)
+// TILED: a block walks ``tiles`` tiles of 128 keys, one after the other with a running softmax (else one: what the
+// loop carries, the output's 64 registers above all, would not fit the registers of six blocks an SM; four share it then).
+template <int HD, bool FUSED, int VBUF, int QROWS, bool TILED>
+__global__ void __launch_bounds__(DEC_THREADS, (VBUF == 0 && QROWS == 8) ? (TILED ? 4 : 6) : 1)
 decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ qkv,
                                 int64_t q_row_stride, const int* __restrict__ block_tables, int bt_stride,
                                 const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
                                 int nh, int nkv, int page_size, float scale, int window,
                                 float* __restrict__ tmp_out, float* __restrict__ tmp_m,
-                                float* __restrict__ tmp_l, int max_parts, int* __restrict__ err, DecodePrep prep) {
+                                float* __restrict__ tmp_l, int max_parts, int tiles, int* __restrict__ err, DecodePrep prep) {
   using namespace mma_prims;
   extern __shared__ unsigned char dec_smem_raw[];
-  __shared__ float w_m[4][16], w_l[4][16];
+  __shared__ float w_m[4][16], w_l[4][16], w_f[4][16], w_fl[4][16];
   __shared__ __align__(8) unsigned long long bar_k, bar_v, bar_v2;
   __shared__ __align__(16) bf16 zero_chunk[8];
   constexpr int PIECES = HD / 8, KSTEPS = HD / 16, NT_O = HD / 8, HALVES = HD / 64;
@@ -458,18 +478,21 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * 16;
   const int z = blockIdx.z;
   const int L = context_lens[b];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, t4 = lane & 3;
   const int n_g = min(16, G - g0);
   // The page of this lane's piece of the partition is asked for together with the context length (which page it
   // is depends on the partition alone; whether it holds keys of the request is decided afterwards): one
   // round trip to memory before the loads can be issued, not two.
+  const int part_keys = (TILED ? tiles : 1) * DEC_PART;      // keys of a block: tiles of 128, walked one after the other
+  const int n_pages = DEC_PART / page_size;
+  auto page_of = [&](int tile_lo_) -> int {          // warp 0, lane < n_pages: the page of this lane's piece of a tile
+    const int pi = tile_lo_ / page_size + lane;
+    return pi < bt_stride ? block_tables[(int64_t)b * bt_stride + pi] : -1;
+  };
   int page_ahead = -1;
-  if (warp == 0 && lane < DEC_PART / page_size) {
-    const int pi = (z * DEC_PART) / page_size + lane;
-    if (pi < bt_stride) page_ahead = block_tables[(int64_t)b * bt_stride + pi];
-  }
+  if (warp == 0 && lane < n_pages) page_ahead = page_of(z * part_keys);
   const int lo_w = window > 0 ? max(0, L - window) : 0;
-  const int part_lo = z * DEC_PART, part_hi = min(L, part_lo + DEC_PART);
+  const int part_lo = z * part_keys, part_hi = min(L, part_lo + part_keys);
   const int64_t slot0 = ((int64_t)b * nh + kvh * G + g0) * max_parts + z;
   if (part_hi <= part_lo || part_hi <= lo_w) {
     pdl_wait();
@@ -505,6 +528,11 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   const bool has_new = part_hi == L;
   const bool makes_new = FUSED && has_new && prep.slot_mapping != nullptr;
   const bool wait_first = has_new && !makes_new;
+  // the tiles of the partition that hold keys the request sees: [t_first, n_tiles)
+  const int t_first = (TILED && lo_w > part_lo) ? (lo_w - part_lo) / DEC_PART : 0;
+  const int n_tiles = TILED ? (part_hi - part_lo + DEC_PART - 1) / DEC_PART : 1;
+  int tile_lo = part_lo + t_first * DEC_PART, tile_hi = min(part_hi, tile_lo + DEC_PART);
+  if (t_first > 0 && warp == 0 && lane < n_pages) page_ahead = page_of(tile_lo);
   if (wait_first) {
     pdl_wait();
     pdl_launch_dependents();
@@ -520,12 +548,15 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   // looks up page i, lane 0 announces the bytes, then box x = ((k|v) * HALVES + half) * pages + page goes out from
   // lane x % 32.
   int first_row = -1;                                  // warp 0: row of the pool's 2-D view where this lane's page keeps K
-  const int n_pages = DEC_PART / page_size;
-  if (warp == 0 && lane < n_pages) {
-    const int j0 = part_lo + lane * page_size;
-    const int page = (j0 < part_hi && j0 + page_size > lo_w) ? page_ahead : -1;
-    if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size;
-  }
+  auto rows_of_tile = [&]() {
+    first_row = -1;
+    if (warp == 0 && lane < n_pages) {
+      const int j0 = tile_lo + lane * page_size;
+      const int page = (j0 < tile_hi && j0 + page_size > lo_w) ? page_ahead : -1;
+      if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size;
+    }
+  };
+  rows_of_tile();
   // what: bit 0 K, bit 1 the values of the partition's first half of pages, bit 2 those of the second half
   auto request = [&](int what) {                       // warp 0
     const unsigned box_bytes = (unsigned)page_size * 64 * sizeof(bf16);
@@ -625,10 +656,9 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     cp_async_wait<0>();
   }
   __syncthreads();                                   // barriers initialised, Q in place
-  bool landed = tma::mbar_wait(&bar_k, 0);
   // The newest key and value go to their row of the tiles (over whatever the slot held) and to the cache.
   auto put_new = [&](bf16* tile, int kv) {
-    const int row = L - 1 - part_lo, i0 = lane * VEC;
+    const int row = L - 1 - tile_lo, i0 = lane * VEC;
     const int slot = new_slot;
     bf16* dst = nullptr;
     if (slot >= 0 && g0 == 0) {
@@ -646,147 +676,152 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       }
     }
   };
-  if (makes_new) {
-    if (warp == 0) {
-      put_new(ks, 0);
-    }
-    __syncthreads();                                 // the row is in place before any warp reads K
-  }
   const float sl2 = scale * 1.4426950408889634f;
   const int mi = lane >> 3;
-  float s[4][4];
+  // Each warp keeps the running maximum, sum and output of its 32 keys of every tile (rows g and g + 8 of the strip);
+  // the sums stay per thread until the end (the factor a new maximum brings is the same for the four threads of a row).
+  float mx0 = -INFINITY, mx1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[NT_O][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll
-  for (int kk = 0; kk < KSTEPS; ++kk) {
-    uint32_t qf[4];
-    ldmatrix_x4(qf, (QROWS == 8 && (mi & 1)) ? zero_chunk : tile_ptr<HD>(qs, (mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
-#pragma unroll
-    for (int np = 0; np < 2; ++np) {
-      uint32_t bfr[4];
-      const int piece = kk * 2 + (mi & 1);
-      ldmatrix_x4(bfr, tma::swz128(ks + (piece >> 3) * DEC_PART * 64, warp * 32 + np * 16 + (mi >> 1) * 8 + (lane & 7), piece & 7));
-      mma_bf16(s[2 * np], qf, bfr[0], bfr[1]);
-      mma_bf16(s[2 * np + 1], qf, bfr[2], bfr[3]);
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  bool landed = true;
+  for (int t = t_first; t < n_tiles; ++t) {
+    const int phase = (t - t_first) & 1;
+    const bool newest_here = makes_new && tile_hi == L;
+    if (t > t_first) {
+      // the tile before is read by every warp (the barrier at its end): its place takes this tile's keys
+      rows_of_tile();
+      if (warp == 0) {
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // (rows of the tile were written by threads)
+        request(VBUF == 2 ? 7 : (VBUF == 1 ? 3 : 1));
+      }
     }
-  }
-  if (VBUF < 2) {
-    __syncthreads();                                 // every warp has its scores: K's tile is free for V
-    if (warp == 0) {
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // (the newest key's row was written by threads)
-      request(VBUF == 1 ? 4 : 6);
+    // the pages of the tile after this one: asked for now, needed at the end of this tile
+    int page_next = -1;
+    if (t + 1 < n_tiles && warp == 0 && lane < n_pages) page_next = page_of(tile_lo + DEC_PART);
+    landed = tma::mbar_wait(&bar_k, phase) && landed;
+    if (newest_here) {
+      if (warp == 0) put_new(ks, 0);
+      __syncthreads();                               // the row is in place before any warp reads K
     }
-  }
-  float mx0 = -INFINITY, mx1 = -INFINITY;
+    float s[4][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int j = part_lo + warp * 32 + i * 8 + 2 * t4 + e;
-      if (j >= part_hi || j < lo_w) s[i][e] = s[i][e + 2] = -INFINITY;
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      uint32_t qf[4];
+      ldmatrix_x4(qf, (QROWS == 8 && (mi & 1)) ? zero_chunk : tile_ptr<HD>(qs, (mi & 1) * 8 + (lane & 7), kk * 2 + (mi >> 1)));
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t bfr[4];
+        const int piece = kk * 2 + (mi & 1);
+        ldmatrix_x4(bfr, tma::swz128(ks + (piece >> 3) * DEC_PART * 64, warp * 32 + np * 16 + (mi >> 1) * 8 + (lane & 7), piece & 7));
+        mma_bf16(s[2 * np], qf, bfr[0], bfr[1]);
+        mma_bf16(s[2 * np + 1], qf, bfr[2], bfr[3]);
+      }
     }
-    mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
-    mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
-  }
-  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-  const float mu0 = mx0 == -INFINITY ? 0.f : mx0, mu1 = mx1 == -INFINITY ? 0.f : mx1;
-  float l0 = 0.f, l1 = 0.f;
-  uint32_t pf[2][4];
+    if (VBUF < 2) {
+      __syncthreads();                               // every warp has its scores: K's tile is free for V
+      if (warp == 0) {
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // (the newest key's row was written by threads)
+        request(VBUF == 1 ? 4 : 6);
+      }
+    }
+    float tm0 = -INFINITY, tm1 = -INFINITY;          // the tile's maxima
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float p0 = exp2f((s[i][0] - mu0) * sl2), p1 = exp2f((s[i][1] - mu0) * sl2);
-    const float p2 = exp2f((s[i][2] - mu1) * sl2), p3 = exp2f((s[i][3] - mu1) * sl2);
-    l0 += p0 + p1;
-    l1 += p2 + p3;
-    pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
-    pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = tile_lo + warp * 32 + i * 8 + 2 * t4 + e;
+        if (j >= tile_hi || j < lo_w) s[i][e] = s[i][e + 2] = -INFINITY;
+      }
+      tm0 = fmaxf(tm0, fmaxf(s[i][0], s[i][1]));
+      tm1 = fmaxf(tm1, fmaxf(s[i][2], s[i][3]));
+    }
+    tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 1));
+    tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, 2));
+    tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1));
+    tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
+    const float nm0 = fmaxf(mx0, tm0), nm1 = fmaxf(mx1, tm1);
+    const float mu0 = nm0 == -INFINITY ? 0.f : nm0, mu1 = nm1 == -INFINITY ? 0.f : nm1;
+    if (t > t_first) {                               // what the tiles before left, at the new maximum (0 while there was none)
+      const float a0 = exp2f((mx0 - mu0) * sl2), a1 = exp2f((mx1 - mu1) * sl2);
+      l0 *= a0;
+      l1 *= a1;
+#pragma unroll
+      for (int i = 0; i < NT_O; ++i) {
+        o[i][0] *= a0;
+        o[i][1] *= a0;
+        o[i][2] *= a1;
+        o[i][3] *= a1;
+      }
+    }
+    mx0 = nm0;
+    mx1 = nm1;
+    uint32_t pf[2][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float p0 = exp2f((s[i][0] - mu0) * sl2), p1 = exp2f((s[i][1] - mu0) * sl2);
+      const float p2 = exp2f((s[i][2] - mu1) * sl2), p3 = exp2f((s[i][3] - mu1) * sl2);
+      l0 += p0 + p1;
+      l1 += p2 + p3;
+      pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+    landed = tma::mbar_wait(&bar_v, phase) && landed;
+    if (VBUF == 1) landed = tma::mbar_wait(&bar_v2, phase) && landed;
+    if (newest_here && warp == 1) put_new(vs, 1);
+    {                                                // rows of V that are no keys of this request: zero
+      const int j = tile_lo + tid;                   // 128 threads, 128 rows
+      if (j >= tile_hi || j < lo_w)
+        for (int p = 0; p < PIECES; ++p) *reinterpret_cast<uint4*>(v_at(tid, p)) = make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();                                 // V complete and cleaned; every warp is done reading K
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int np = 0; np < NT_O / 2; ++np) {
+        uint32_t bfr[4];
+        const int piece = np * 2 + (mi >> 1);
+        ldmatrix_x4_trans(bfr, v_at(warp * 32 + kk * 16 + (mi & 1) * 8 + (lane & 7), piece));
+        mma_bf16(o[2 * np], pf[kk], bfr[0], bfr[1]);
+        mma_bf16(o[2 * np + 1], pf[kk], bfr[2], bfr[3]);
+      }
+    }
+    if (t + 1 < n_tiles) {
+      __syncthreads();                               // every warp is done with this tile's V (and K)
+      tile_lo += DEC_PART;
+      tile_hi = min(part_hi, tile_lo + DEC_PART);
+      page_ahead = page_next;
+    }
   }
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  landed = tma::mbar_wait(&bar_v, 0) && landed;
-  if (VBUF == 1) landed = tma::mbar_wait(&bar_v2, 0) && landed;
-  if (makes_new && warp == 1) put_new(vs, 1);
-  {                                                  // rows of V that are no keys of this request: zero
-    const int j = part_lo + tid;                     // 128 threads, 128 rows
-    if (j >= part_hi || j < lo_w)
-      for (int p = 0; p < PIECES; ++p) *reinterpret_cast<uint4*>(v_at(tid, p)) = make_uint4(0, 0, 0, 0);
-  }
-  __syncthreads();                                   // V complete and cleaned; every warp is done reading K
-  float o[NT_O][4];
-#pragma unroll
-  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-#pragma unroll
-  for (int kk = 0; kk < 2; ++kk) {
-#pragma unroll
-    for (int np = 0; np < NT_O / 2; ++np) {
-      uint32_t bfr[4];
-      const int piece = np * 2 + (mi >> 1);
-      ldmatrix_x4_trans(bfr, v_at(warp * 32 + kk * 16 + (mi & 1) * 8 + (lane & 7), piece));
-      mma_bf16(o[2 * np], pf[kk], bfr[0], bfr[1]);
-      mma_bf16(o[2 * np + 1], pf[kk], bfr[2], bfr[3]);
-    }
-  }
   if (VBUF < 2) __syncthreads();                     // every warp is done reading V: K's tile now takes the warps' results
-  float* po = reinterpret_cast<float*>(ks);          // [4][16][HD] float32, over the K tile
-  if (t4 == 0) {
-    w_m[warp][g] = mx0;
-    w_l[warp][g] = l0;
-    w_m[warp][g + 8] = mx1;
-    w_l[warp][g + 8] = l1;
-  }
-#pragma unroll
-  for (int i = 0; i < NT_O; ++i) {
-    if (g < n_g) *reinterpret_cast<float2*>(po + ((warp * 16 + g) * HD + i * 8 + 2 * t4)) = make_float2(o[i][0], o[i][1]);
-    if (g + 8 < n_g) *reinterpret_cast<float2*>(po + ((warp * 16 + g + 8) * HD + i * 8 + 2 * t4)) = make_float2(o[i][2], o[i][3]);
-  }
-  __syncthreads();
   if (!landed && tid == 0) atomicOr(err + 1, 1);     // a load did not land in time: the result is reported as invalid
-  for (int idx = tid; idx < n_g * HD; idx += DEC_THREADS) {
-    const int r = idx / HD, d = idx - r * HD;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, w_m[w][r]);
-    float lt = 0.f, acc = 0.f;
-    if (M > -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float mw = w_m[w][r];
-        const float f = mw == -INFINITY ? 0.f : exp2f((mw - M) * sl2);
-        lt += f * w_l[w][r];
-        acc += f * po[(w * 16 + r) * HD + d];
-      }
-    }
-    const int64_t slot = slot0 + (int64_t)r * max_parts;
-    tmp_out[slot * HD + d] = acc;
-    if (d == 0) {
-      tmp_m[slot] = M == -INFINITY ? -INFINITY : M * scale;
-      tmp_l[slot] = lt;
-    }
-  }
+  merge_warps_of_partition<HD>(reinterpret_cast<float*>(ks), w_m, w_l, w_f, w_fl, o, mx0, l0, mx1, l1, n_g, sl2, scale, tmp_out,
+                               tmp_m, tmp_l, slot0, max_parts);
 }
 
-template <int HD, bool FUSED, int VBUF, int QROWS>
+template <int HD, bool FUSED, int VBUF, int QROWS, bool TILED = false>
 static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_parts, cudaStream_t stream, const void* qkv,
                                     int64_t q_row_stride, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
-                                    int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int* err,
-                                    const DecodePrep& prep) {
+                                    int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int tiles,
+                                    int* err, const DecodePrep& prep) {
   const size_t smem = (size_t)(QROWS + DEC_PART + VBUF * DEC_PART / 2) * HD * sizeof(bf16) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, VBUF, QROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_partition_tma_mma_kernel<HD, FUSED, VBUF, QROWS, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_attn_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   const int G = nh / nkv;
   dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
-  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, VBUF, QROWS>, grid, dim3(DEC_THREADS), smem, stream,
+  me_launch(decode_partition_tma_mma_kernel<HD, FUSED, VBUF, QROWS, TILED>, grid, dim3(DEC_THREADS), smem, stream,
       *reinterpret_cast<const CUtensorMap*>(kv_map), (const bf16*)qkv, q_row_stride, bt, bt_stride, cu, cl, nh, nkv, page_size,
-      scale, window, to, tm, tl, max_parts, err, prep);
+      scale, window, to, tm, tl, max_parts, tiles, err, prep);
   return 0;
 }
 
@@ -798,7 +833,7 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
                                     const int* __restrict__ cu_seqlens,
                                     const int* __restrict__ context_lens,
                                     const float* __restrict__ tmp_out, const float* __restrict__ tmp_m,
-                                    const float* __restrict__ tmp_l, int nh, int hd, int max_parts) {
+                                    const float* __restrict__ tmp_l, int nh, int hd, int max_parts, int part_keys) {
   constexpr int CHUNK = 128;                         // partitions whose factors are held in shared memory at a time
   __shared__ float f_s[CHUNK], red[32];
   const int b = blockIdx.x, h = blockIdx.y;
@@ -806,7 +841,7 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
   const int64_t tok = cu_seqlens[b];
   pdl_wait();
   pdl_launch_dependents();
-  const int P = max(1, min(max_parts, (L + DEC_PART - 1) / DEC_PART));
+  const int P = max(1, min(max_parts, (L + part_keys - 1) / part_keys));
   const int64_t row0 = ((int64_t)b * nh + h) * max_parts;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = (blockDim.x + 31) >> 5;
   if (P <= 16 && hd <= (int)blockDim.x) {
@@ -927,9 +962,9 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   if (tma_mma) {
     const DecodePrep none = {};
     int rc = hd == 64 ? launch_partition_tma_mma<64, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
-                                                            cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none)
+                                                            cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, 1, err, none)
                       : launch_partition_tma_mma<128, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
-                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, err, none);
+                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, 1, err, none);
     if (rc) return rc;
   }
   if (mma) {
@@ -955,7 +990,7 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   dim3 mgrid(num_reqs, nh);
   const int mthreads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
   ME_DISPATCH_DTYPE(dtype, T, (me_launch(decode_merge_kernel<T>, mgrid, dim3(mthreads), 0, stream,
-      (T*)out, out_row_stride, cu_seqlens, context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts)));
+      (T*)out, out_row_stride, cu_seqlens, context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART)));
   ME_LAUNCH_CHECK("me_attn_decode (merge)");
   return 0;
 }
@@ -970,14 +1005,17 @@ ME_API int me_attn_decode_fused_takes(int hd, int page_size) {
 // whole step) happen inside the partition kernel, for requests [0, num_reqs) that bring one token each
 // (token row = cu_seqlens[request], position = context_lens[request] - 1).  q_weight/k_weight (both or neither), cos_sin and slot_mapping may be
 // null; with a null slot_mapping the newest key and value are expected in the cache already.  The q rows of
-// ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode.  form (of the partition kernel):
-// 0 K and V through one tile, 2 a tile each, 3 half a tile for V beside K's.
+// ``qkv`` are left as the product wrote them.  Scratch as for me_attn_decode, with max_parts >= ceil(max context /
+// (128 tiles)).  form (of the partition kernel): 0 K and V through one tile, 2 a tile each, 3 half a tile for V beside
+// K's.  tiles: how many tiles of 128 keys a block walks, one after the other with a running softmax: what a block does
+// once (q's norm and rotation, the merge of its warps, its partial result and the merge kernel's share of it) is then
+// spread over that many keys; for batches whose blocks are many times what the device holds at once.
 ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out, int64_t out_row_stride, void* pool,
                                 const void* kv_map, const int* block_tables, int bt_stride, const int* cu_seqlens,
                                 const int* context_lens, int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
                                 int window, const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
                                 const int* slot_mapping, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts, int form,
-                                int* err, cudaStream_t stream) {
+                                int tiles, int* err, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   ME_REQUIRE(me_attn_decode_fused_takes(hd, page_size), "me_attn_decode_fused: head_dim %d with pages of %d is not taken", hd, page_size);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "me_attn_decode_fused: %d heads, %d kv heads", nh, nkv);
@@ -989,28 +1027,39 @@ ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out
   ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode_fused: too many heads");
   DecodePrep prep = {q_weight, k_weight, eps, cos_sin, slot_mapping, (bf16*)pool};
   ME_REQUIRE(form == 0 || form == 2 || form == 3, "me_attn_decode_fused: unknown form %d", form);
+  ME_REQUIRE(tiles >= 1 && tiles <= 64, "me_attn_decode_fused: %d tiles a block", tiles);
   int rc = 1;
 #define ME_FUSED(HD_, VBUF_, Q_)                                                                                    \
   rc = launch_partition_tma_mma<HD_, true, VBUF_, Q_>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, \
                                                            bt_stride, cu_seqlens, context_lens, nh, nkv, page_size, scale, window, \
-                                                           tmp_out, tmp_m, tmp_l, err, prep)
+                                                           tmp_out, tmp_m, tmp_l, tiles, err, prep)
   const bool few_heads = G <= 8;                     // a group's query heads fit the lower half of the m16 strip
   ME_REQUIRE(form != 3 || (DEC_PART / 2) % page_size == 0, "me_attn_decode_fused: pages of %d do not fit half a partition", page_size);
 #define ME_FUSED_Q(HD_, VBUF_)                                                                                           \
   do { if (few_heads) ME_FUSED(HD_, VBUF_, 8); else ME_FUSED(HD_, VBUF_, 16); } while (0)
+#define ME_FUSED_TILED(HD_, Q_)                                                                                          \
+  rc = launch_partition_tma_mma<HD_, true, 0, Q_, true>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, \
+                                                        bt_stride, cu_seqlens, context_lens, nh, nkv, page_size, scale, window, \
+                                                        tmp_out, tmp_m, tmp_l, tiles, err, prep)
+  ME_REQUIRE(tiles == 1 || form == 0, "me_attn_decode_fused: several tiles a block go with form 0 only");
+  if (tiles > 1) {
+    if (hd == 64) { if (few_heads) ME_FUSED_TILED(64, 8); else ME_FUSED_TILED(64, 16); }
+    else { if (few_heads) ME_FUSED_TILED(128, 8); else ME_FUSED_TILED(128, 16); }
+  } else
   if (hd == 64 && form == 2) ME_FUSED(64, 2, 16);
   else if (hd == 64 && form == 3) ME_FUSED_Q(64, 1);
   else if (hd == 64) ME_FUSED_Q(64, 0);
   else if (form == 2) ME_FUSED(128, 2, 16);
   else if (form == 3) ME_FUSED_Q(128, 1);
   else ME_FUSED_Q(128, 0);
+#undef ME_FUSED_TILED
 #undef ME_FUSED_Q
 #undef ME_FUSED
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_attn_decode_fused (partitions)");
   dim3 mgrid(num_reqs, nh);
   me_launch(decode_merge_kernel<bf16>, mgrid, dim3(hd >= 128 ? 128 : 64), 0, stream, (bf16*)out, out_row_stride, cu_seqlens,
-            context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts);
+            context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART * tiles);
   ME_LAUNCH_CHECK("me_attn_decode_fused (merge)");
   return 0;
 }

@@ -578,13 +578,17 @@ def test_attention_decode_kernels_by_name(ops, kind, nh, nkv, hd, page, window):
                                                   (40, 2, 64, 16), (16, 8, 128, 128)])
 @pytest.mark.parametrize("window", [None, 200])
 @pytest.mark.parametrize("norm, rope, writes", [(True, True, True), (False, True, True), (True, False, True), (True, True, False)])
-@pytest.mark.parametrize("form", ["one_tile", "tile_and_half", "two_tiles"])
+@pytest.mark.parametrize("form", ["one_tile", "tile_and_half", "two_tiles", "one_tile*2", "one_tile*3", "one_tile*8"])
 def test_attention_decode_that_prepares_q_and_the_newest_key_itself(ops, nh, nkv, hd, page, window, norm, rope, writes, form):
     if form == "tile_and_half" and 64 % page:
         pytest.skip("half a partition holds whole pages")
+    # "one_tile*n": a block walks n tiles of 128 keys with a running softmax (partitions of 256, 384 and 1,024 keys: the
+    # contexts below end before, at and after their edges; with the window the first tiles of a partition are skipped)
+    form, _, tiles = form.partition("*")
+    tiles = int(tiles or 1)
     # the same batch through (norm, rotation, cache write) as a pass of its own followed by plain attention, and
     # through the decode kernel that does all of it; the newest slots of its cache start as NaN
-    ctx = [1, 127, 128, 129, 300, 1000, 16, 255, 256, 257, 513]
+    ctx = [1, 127, 128, 129, 300, 1000, 16, 255, 256, 257, 513, 384, 385, 1024, 1025]
     b = Batch(ctx, [1] * len(ctx), nh, nkv, hd, page, torch.bfloat16, seed=nh + hd, window=window)
     B = len(ctx)
     L = b.meta.context_lens.tolist()
@@ -613,7 +617,7 @@ def test_attention_decode_that_prepares_q_and_the_newest_key_itself(ops, nh, nkv
     out = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
     assert ops.decode_fused_takes(qkv, hd, pool, page, b.meta)
     ops.attention_decode_fused(qkv, out, *args, pool, page, b.bt, b.meta, hd ** -0.5, window, qw, kw, 1e-5, cs,
-                               slots if writes else None, form=form)
+                               slots if writes else None, form=form, tiles=tiles)
     assert not out.isnan().any() and b.meta.error_flag.tolist() == [0, 0, 0, 0]
     close(out, ref, torch.bfloat16)
     assert torch.equal(qkv, b.qkv)                   # the rows of the product are left alone
