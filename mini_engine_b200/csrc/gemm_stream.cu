@@ -219,10 +219,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           flags[b] = 0;
         }
         consumers_sync();                            // all flags are seen: the sums behind them may be read
-        for (int b = blockIdx.x + 1; b <= b_last; ++b) {
-          const float* theirs = partials + (int64_t)b * GS_PARTIAL;
+        // four blocks' sums asked for at a time (one trip to L2, not four), added in block order
+        for (int b0 = blockIdx.x + 1; b0 <= b_last; b0 += 4) {
+          float theirs[4][GS_PER];
 #pragma unroll
-          for (int i = 0; i < GS_PER; ++i) v[i] += __ldcg(theirs + tid + i * GS_CONSUMERS);
+          for (int u = 0; u < 4; ++u) {
+            const bool there = b0 + u <= b_last;
+            const float* src = partials + (int64_t)(there ? b0 + u : b0) * GS_PARTIAL;
+#pragma unroll
+            for (int i = 0; i < GS_PER; ++i) theirs[u][i] = there ? __ldcg(src + tid + i * GS_CONSUMERS) : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int i = 0; i < GS_PER; ++i) v[i] += theirs[u][i];
         }
       }
       // back into shared memory (a thread rewrites the places it read), scaled by the batch row's norm factor
