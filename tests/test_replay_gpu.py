@@ -129,6 +129,26 @@ def test_long_decoding_and_first_tokens(dtype):
         _check(name, dtype, [r[:n]], got, "w")
 
 
+@pytest.mark.parametrize("tiles", [2, 3])
+def test_long_decoding_with_several_key_tiles_a_block(tiles):
+    # the decode attention kernel in the form that large batches take (a block walks several tiles of 128 keys with a
+    # running softmax), forced on one request: contexts from 100 to 420 tokens cross the tiles' and the partitions'
+    # edges one token at a time, in a layer that sees all keys and in one with a window of 40 (config D)
+    from mini_engine_b200 import ops
+    name = "D"
+    (r,) = helpers.random_requests(ALL[name][0]["vocab_size"], (420,), seed=7)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": r[:100], "want": list(range(100))}], "end": []}]
+    steps += [{"step": p - 99, "entries": [{"id": "x", "tokens": [r[p]], "want": [0]}], "end": ["x"] if p == 419 else []}
+              for p in range(100, 420)]
+    old = ops.decode_form, ops.decode_tiles
+    ops.decode_form, ops.decode_tiles = "one_tile", tiles
+    try:
+        got, _ = _replay(name, "bfloat16", steps)
+    finally:
+        ops.decode_form, ops.decode_tiles = old
+    _check(name, "bfloat16", [r], {"x0": got["x"]}, "x")
+
+
 def test_page_exhaustion_is_a_clear_error():
     reqs = _requests("A")
     steps = helpers.trace_whole(reqs[:1])
