@@ -749,7 +749,7 @@ def decode_tiles_for(rows: int, key_tiles: int) -> int:
     in all but one case (there 4% behind)."""
     want = 4 * sm_count()
     tiles = 1
-    while tiles < 32 and rows * -(-key_tiles // (2 * tiles)) >= want:
+    while tiles < 32 and tiles < key_tiles and rows * -(-key_tiles // (2 * tiles)) >= want:
         tiles *= 2
     return tiles
 
