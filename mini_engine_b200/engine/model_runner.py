@@ -582,9 +582,11 @@ class ModelRunner:
         return StepResult(g.logits[:n], g.tokens[:n] if sample else None)
 
     def check_device_errors(self) -> None:
-        """Raise if a kernel flagged bad input (a token id outside the vocabulary)."""
+        """Raise if a kernel flagged bad input (a token id outside the vocabulary) or gave up a bounded wait."""
         flags = self.error_flag.tolist()
         if any(flags):
             self.error_flag.zero_()
-            raise RuntimeError(f"a kernel reported bad input: flags {flags} "
-                               "(flag 0: token id outside the vocabulary; flag 1: a bulk copy did not land in time)")
+            ops.reset_stream_work_buffers()
+            raise RuntimeError(f"a kernel reported an error: flags {flags} "
+                               "(flag 0: token id outside the vocabulary; flag 1: a bounded wait ran out: a tensor-map load that "
+                               "did not land, or a neighbouring block's sums that did not come)")

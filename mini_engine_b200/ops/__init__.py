@@ -363,6 +363,14 @@ def _stream_work_buffers(device) -> tuple[torch.Tensor, torch.Tensor]:
     return ws
 
 
+def reset_stream_work_buffers() -> None:
+    """Clear the flags of csrc/gemm_stream.cu's work buffers.  Every launch leaves them zero, except one whose bounded
+    wait ran out (flag 1 of the error word): the caller that reports that error calls this, so that a later launch does
+    not take a stale flag for a neighbour's finished sums."""
+    for _, flags in _stream_ws.values():
+        flags.zero_()
+
+
 def decode_linear_sumsq_parts(N: int, K: int = 0, stream: Optional[bool] = None) -> int:
     """Parts in which the residual epilogue of ``decode_linear`` writes sums of squares, for N columns over K
     (``stream``: by which of the two kernels; None: the one that ``decode_kernel`` picks for K)."""

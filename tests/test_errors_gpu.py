@@ -20,9 +20,12 @@ def test_a_wait_that_runs_out_is_reported_once_and_the_next_step_is_clean():
     runner = rp.runner
     assert ops.wait_expires_selftest(runner.error_flag, limit=3000) == 3000
     assert runner.error_flag.tolist() == [0, 1, 0, 0]
-    with pytest.raises(RuntimeError, match="did not land in time"):
+    _, flags = ops._stream_work_buffers(runner.device)   # a streaming product that gave up may leave a neighbour's flag set
+    flags[3] = 1
+    with pytest.raises(RuntimeError, match="a bounded wait ran out"):
         runner.check_device_errors()
     runner.check_device_errors()                       # cleared by the report
+    assert int(flags.sum()) == 0                       # ... and so are the flags between the streaming products' blocks
     (r,) = helpers.random_requests(cfg["vocab_size"], (150,), seed=3)
     steps = helpers.trace_decode_tail([r], tail=4)
     got = helpers.collect(steps, [rp.run_step(st) for st in steps])["d0"]
