@@ -467,13 +467,17 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epi
     epi = {"none": 0, "silu_mul": 1}[epilogue]
     N = weight.shape[0] // 2 if epi else weight.shape[0]
     if tile_n is None:
-        # The widest accumulator that still gives every SM about two tiles; the SiLU epilogue (half as many
-        # output columns per tile) does best at 128 until there are very many rows.
+        # The widest accumulator that still leaves enough tiles: about two an SM where a tile is short (K up to 3,072),
+        # one for every other SM where it is long (measured at the 8B and 32B sizes: with 512 rows the 256-wide tile is a
+        # third faster than the 64-wide one that two tiles an SM would ask for).  The SiLU epilogue (half as many output
+        # columns per tile) does best at 128 while both the rows and K are few, and again where the output is so large
+        # (a quarter of a GB and more) that the wide tiles' order through it stops fitting L2.
         m_tiles = (M + 127) // 128
         if epi:
-            tile_n = 256 if M >= 4096 else 128
+            tile_n = 256 if (M >= 4096 or K >= 4096) and m_tiles * ((N + 127) // 128) <= 10000 else 128
         else:
-            tile_n = next((bn for bn in (256, 128) if m_tiles * ((N + bn - 1) // bn) >= 200), 64)
+            need = 200 if K < 4096 else 64
+            tile_n = next((bn for bn in (256, 128) if m_tiles * ((N + bn - 1) // bn) >= need), 64)
     bn = tile_n
     _need(tcgen05_takes(x, weight) or M < TCGEN05_MIN_ROWS, "linear_tcgen05: operands not taken")
     box_w = bn // 2 if epi else bn
