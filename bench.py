@@ -388,7 +388,7 @@ def prefill_on_device(runner, cache, prompt, reps: int, warmup: int, portion: in
 
 def kernel_table(model: Model, runner, cache, args, pk: dict, batch: int, prompt_len: int, T: int) -> dict:
     """One decode step of ``batch`` requests and one prefill step of ``T`` tokens launched kernel by kernel, every
-    launch between two CUDA events: per kind of kernel the mean microseconds of a launch (less what an empty event
+    launch between two CUDA events: per kind of kernel the median microseconds of a launch (less what an empty event
     pair measures, ``event_pair_us``), the bytes (decode) or flops (prefill) it has to move or do, and the fraction
     of the measured peak that makes.  Kernels run one after the other here; in the step itself each starts under its
     predecessor, so these add up to more than the step."""
@@ -413,7 +413,11 @@ def kernel_table(model: Model, runner, cache, args, pk: dict, batch: int, prompt
             busy = torch.empty(1 << 28, dtype=torch.float32, device="cuda")         # 1 GiB
             for _ in range(24):
                 busy.add_(1.0)                           # some 8 ms of work ahead of the step
-            run()
+            gc.disable()                                 # (a collection in the middle of the queueing starves the device: one
+            try:                                         # launch then "took" 72 ms)
+                run()
+            finally:
+                gc.enable()
             torch.cuda.synchronize()
             del busy
             got = {}
@@ -451,7 +455,7 @@ def kernel_table(model: Model, runner, cache, args, pk: dict, batch: int, prompt
     work = {name: n * k * item for name, (n, k) in shapes.items()}
     work["attn_decode_fused"] = work["attn_decode"] = batch * ctx * 2 * nkv * hd * item
     for key, us in sorted(got.items()):
-        mean = max(sum(us) / len(us) - overhead, 0.1)
+        mean = max(statistics.median(us) - overhead, 0.1)
         row = {"us": round(mean, 2), "launches": len(us)}
         if key in work:
             row["bytes"] = int(work[key])
@@ -466,7 +470,7 @@ def kernel_table(model: Model, runner, cache, args, pk: dict, batch: int, prompt
     flops = {name: 2.0 * T * n * k for name, (n, k) in shapes.items() if name != "logits"}
     flops["attn_prefill_tcgen05"] = flops["attn_prefill"] = flops["attn_chunk"] = 2.0 * nh * hd * T * T
     for key, us in sorted(got.items()):
-        mean = max(sum(us) / len(us) - overhead, 0.1)
+        mean = max(statistics.median(us) - overhead, 0.1)
         row = {"us": round(mean, 2), "launches": len(us)}
         if key in flops:
             row["flops"] = flops[key]

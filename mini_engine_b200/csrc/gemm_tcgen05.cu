@@ -195,6 +195,179 @@ int launch_tg(const void* map_a, const void* map_w, void* C, int64_t ldc, int M,
   return 0;
 }
 
+// ---- the persistent form: one block an SM walks tiles --------------------------------------------------------
+// For products with many tiles (several an SM).  A block keeps its ring of stages and its tensor memory over all the
+// tiles it computes (tile blockIdx.x, blockIdx.x + gridDim.x, ...; rows fastest, so that the blocks running at one
+// time share few W tiles): the loads of the next tile are on their way while this tile's last products run, and with
+// two accumulators the epilogue of a tile runs beside the products of the next.  The ring has the SM's whole shared
+// memory (four stages of 128 x 64 and 256 x 64, or six with a 128-wide tile).
+template <int BN> constexpr int tp_stages() { return BN <= 128 ? 6 : 4; }
+
+template <int BN, int EPI, typename TO>
+__global__ void __launch_bounds__(TG_THREADS, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                               TO* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err) {
+  constexpr int STAGES = tp_stages<BN>();
+  constexpr int B_BYTES = BN * TG_BK * 2, STAGE_BYTES = TG_A_BYTES + B_BYTES;
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
+  constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators
+  extern __shared__ unsigned char tg_smem_raw[];
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  unsigned char* smem = tg_smem_raw + ((1024u - (tma::smem_addr(tg_smem_raw) & 1023u)) & 1023u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + TG_BM - 1) / TG_BM, n_tiles = (N + OUT_COLS - 1) / OUT_COLS, num_kb = (K + TG_BK - 1) / TG_BK;
+  const int tiles = m_tiles * n_tiles;
+  const int my_tiles = blockIdx.x < tiles ? (tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const long long total = (long long)my_tiles * num_kb;      // stages of this block
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tma::mbar_init(&full_bar[s], 1);
+      tma::mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tma::mbar_init(&acc_full[i], 1);
+      tma::mbar_init(&acc_empty[i], 4);
+    }
+    tma::mbar_fence_init();
+    tma::prefetch_map(&map_a);
+    tma::prefetch_map(&map_w);
+  }
+  if (warp == 1) tc5::tmem_alloc(&tmem_slot, TMEM_COLS);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      auto place = [&](long long item, int& m0, int& n0, int& k0) {
+        const int tile = blockIdx.x + (int)(item / num_kb) * gridDim.x;
+        m0 = (tile % m_tiles) * TG_BM;
+        n0 = (tile / m_tiles) * OUT_COLS;
+        k0 = (int)(item % num_kb) * TG_BK;
+      };
+      auto issue_w = [&](long long item) {
+        int m0, n0, k0;
+        place(item, m0, n0, k0);
+        const int s = (int)(item % STAGES);
+        unsigned char* b_dst = smem + s * STAGE_BYTES + TG_A_BYTES;
+        tma::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        if (EPI == 1) {
+          tma::load_2d(b_dst, &map_w, k0, n0, &full_bar[s]);
+          tma::load_2d(b_dst + B_BYTES / 2, &map_w, k0, N + n0, &full_bar[s]);
+        } else {
+          tma::load_2d(b_dst, &map_w, k0, n0, &full_bar[s]);
+        }
+      };
+      auto issue_a = [&](long long item) {
+        int m0, n0, k0;
+        place(item, m0, n0, k0);
+        const int s = (int)(item % STAGES);
+        tma::load_2d(smem + s * STAGE_BYTES, &map_a, k0, m0, &full_bar[s]);
+      };
+      // The weights are no output of the kernel before this one; the activations are.
+      const long long ahead = total < STAGES ? total : STAGES;
+      for (long long item = 0; item < ahead; ++item) issue_w(item);
+      pdl_wait();
+      for (long long item = 0; item < ahead; ++item) issue_a(item);
+      for (long long item = ahead; item < total && ok; ++item) {
+        ok = tma::mbar_wait(&empty_bar[item % STAGES], (uint32_t)(((item / STAGES) & 1) ^ 1));
+        if (!ok) break;
+        issue_w(item);
+        issue_a(item);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc5::instr_desc_bf16(TG_BM, BN);
+      long long item = 0;
+      for (int i = 0; i < my_tiles; ++i) {
+        const int buf = i & 1;
+        if (i >= 2 && ok) ok = tma::mbar_wait(&acc_empty[buf], (uint32_t)(((i >> 1) - 1) & 1));      // read out by the epilogue
+        tc5::fence_after_sync();
+        for (int kb = 0; kb < num_kb; ++kb, ++item) {
+          const int s = (int)(item % STAGES);
+          if (ok) ok = tma::mbar_wait(&full_bar[s], (uint32_t)((item / STAGES) & 1));
+          tc5::fence_after_sync();
+          if (ok) {
+            const uint64_t a_desc = tc5::smem_desc_k_major_sw128(smem + s * STAGE_BYTES);
+            const uint64_t b_desc = tc5::smem_desc_k_major_sw128(smem + s * STAGE_BYTES + TG_A_BYTES);
+#pragma unroll
+            for (int k = 0; k < TG_BK / 16; ++k)     // 32 bytes further along K per step: +2 in units of 16 bytes
+              tc5::mma_f16(tmem + buf * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > 0 || k > 0);
+          }
+          tc5::commit(&empty_bar[s]);                // the stage is free once these MMAs have read it
+        }
+        tc5::commit(&acc_full[buf]);                 // the tile's sums are complete
+      }
+    }
+  } else {
+    // Epilogue: warp w reads lanes 32 (w % 4) .. +31 of tensor memory; a lane is a row of the tile.
+    const int lane_base = (warp & 3) * 32;
+    for (int i = 0; i < my_tiles; ++i) {
+      const int tile = blockIdx.x + i * gridDim.x, buf = i & 1;
+      const int m0 = (tile % m_tiles) * TG_BM, n0 = (tile / m_tiles) * OUT_COLS;
+      const int m = m0 + lane_base + lane;
+      if (ok) ok = tma::mbar_wait(&acc_full[buf], (uint32_t)((i >> 1) & 1));
+      tc5::fence_after_sync();
+      const uint32_t acc = tmem + ((uint32_t)lane_base << 16) + buf * BN;
+      const bool vec = (ldc * sizeof(TO)) % 16 == 0 && (n0 * sizeof(TO)) % 16 == 0 && ((uintptr_t)C & 15) == 0;
+      if (ok) {
+        if (EPI == 1) {
+#pragma unroll 1
+          for (int c = 0; c < OUT_COLS; c += 32) {
+            float g[32], u[32];
+            tc5::ld_32cols(acc + c, g);
+            tc5::ld_32cols(acc + OUT_COLS + c, u);
+            tc5::wait_ld();
+            if (m < M && n0 + c < N) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
+              store_row32(C + (int64_t)m * ldc + n0 + c, g, N - n0 - c, vec);
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < OUT_COLS; c += 32) {
+            float v[32];
+            tc5::ld_32cols(acc + c, v);
+            tc5::wait_ld();
+            if (m < M && n0 + c < N) store_row32(C + (int64_t)m * ldc + n0 + c, v, N - n0 - c, vec);
+          }
+        }
+      }
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tma::smem_addr(&acc_empty[buf])) : "memory");
+    }
+  }
+  if (!ok) atomicOr(err + 1, 1);
+  pdl_launch_dependents();
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tc5::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+template <int BN, int EPI, typename TO>
+int launch_tp(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, int* err, cudaStream_t stream) {
+  const size_t smem = (size_t)tp_stages<BN>() * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ME_REQUIRE(e == cudaSuccess, "me_gemm_tcgen05: cannot raise shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
+  const long long tiles = (long long)((N + OUT_COLS - 1) / OUT_COLS) * ((M + TG_BM - 1) / TG_BM);
+  ME_REQUIRE(tiles < (1ll << 30), "me_gemm_tcgen05: too many tiles");
+  const int blocks = (int)(tiles < me_sm_count() ? tiles : me_sm_count());
+  me_launch(gemm_tcgen05_persistent_kernel<BN, EPI, TO>, dim3(blocks), dim3(TG_THREADS), smem, stream,
+            *reinterpret_cast<const CUtensorMap*>(map_a), *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, err);
+  return 0;
+}
+
 }  // namespace
 
 // How many partial results a product over K asked to be split ``splits`` ways writes (whole blocks of 64 along K each).
@@ -206,6 +379,28 @@ ME_API int me_gemm_tcgen05_splits(int K, int splits) {
 
 // Rows of W that one block's TMA box covers for a given tile width and epilogue (the caller encodes the map so).
 ME_API int me_gemm_tcgen05_w_box_rows(int bn, int epi) { return epi == 1 ? bn / 2 : bn; }
+
+// The persistent form of me_gemm_tcgen05 (same operands, no split along K): bn 128 or 256.
+ME_API int me_gemm_tcgen05_persistent(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, int M, int N,
+                                      int K, int epi, int bn, int* err, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  ME_REQUIRE(M > 0 && N > 0 && K > 0 && K % 8 == 0, "me_gemm_tcgen05_persistent: bad sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
+  ME_REQUIRE(map_a != nullptr && map_w != nullptr && err != nullptr, "me_gemm_tcgen05_persistent: tensor maps and the error word are required");
+  ME_REQUIRE(epi == 0 || (epi == 1 && c_dtype == ME_BF16), "me_gemm_tcgen05_persistent: epilogue %d", epi);
+  ME_REQUIRE(bn == 128 || bn == 256, "me_gemm_tcgen05_persistent: tile width %d is not 128 or 256", bn);
+  int rc = 1;
+#define ME_TP_CASE(BN_)                                                                                  \
+  if (bn == BN_) {                                                                                       \
+    if (epi == 1) rc = launch_tp<BN_, 1, bf16>(map_a, map_w, C, ldc, M, N, K, err, stream);              \
+    else if (c_dtype == ME_BF16) rc = launch_tp<BN_, 0, bf16>(map_a, map_w, C, ldc, M, N, K, err, stream); \
+    else rc = launch_tp<BN_, 0, float>(map_a, map_w, C, ldc, M, N, K, err, stream);                      \
+  }
+  ME_TP_CASE(128) ME_TP_CASE(256)
+#undef ME_TP_CASE
+  if (rc) return rc;
+  ME_LAUNCH_CHECK("me_gemm_tcgen05_persistent");
+  return 0;
+}
 
 // map_a: X as [M][K], boxes 128 x 64, 128-byte swizzle; map_w: W as [rows][K], boxes
 // me_gemm_tcgen05_w_box_rows(bn, epi) x 64.  N counts output columns (epi 1: W has 2N rows).

@@ -34,6 +34,7 @@ _PROTOS = {
     "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, ctypes.c_uint64, _P],
     "me_gemm_stream": [_I, _P, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _L, _P, _P],
+    "me_gemm_tcgen05_persistent": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
     "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -458,8 +459,21 @@ def tcgen05_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+tcgen05_persistent = "auto"     # the persistent form of the tcgen05 product: "auto", True or False (for comparisons)
+
+
+def tcgen05_persistent_pays(M: int, N: int, epi: int) -> bool:
+    """Whether a product of M rows and N output columns runs the persistent form of the tcgen05 kernel (one block an
+    SM walking 128 x 256 tiles with two accumulators): from two tiles an SM on.  There the loads of the next tile and
+    the epilogue of the last one run beside a tile's products, which is worth a fifth to a third of gate|up at every
+    size measured and of q|k|v at 2,048 rows; with fewer tiles (o_proj, down_proj up to a few thousand rows) the form
+    with two blocks an SM is level or ahead."""
+    out_cols = 128 if epi else 256
+    return ((M + 127) // 128) * ((N + out_cols - 1) // out_cols) >= 2 * sm_count()
+
+
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str, err: torch.Tensor,
-                   tile_n: Optional[int] = None, splits: int = 1) -> None:
+                   tile_n: Optional[int] = None, splits: int = 1, persistent: Optional[bool] = None) -> None:
     """The tcgen05 product of csrc/gemm_tcgen05.cu: TMA -> swizzled shared memory -> tcgen05.mma -> tensor memory.
 
     With ``splits`` > 1 ``out`` is float32 [tcgen05_splits(K, splits), M, N]: partial results over parts of K."""
@@ -473,7 +487,9 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epi
         # columns per tile) does best at 128 while both the rows and K are few, and again where the output is so large
         # (a quarter of a GB and more) that the wide tiles' order through it stops fitting L2.
         m_tiles = (M + 127) // 128
-        if epi:
+        if persistent is None and tcgen05_persistent == "auto" and splits == 1 and tcgen05_persistent_pays(M, N, epi):
+            tile_n, persistent = 256, True
+        elif epi:
             tile_n = 256 if (M >= 4096 or K >= 4096) and m_tiles * ((N + 127) // 128) <= 10000 else 128
         else:
             need = 200 if K < 4096 else 64
@@ -487,6 +503,14 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epi
         ldc, split_stride = out.stride(1), out.stride(0)
     else:
         ldc, split_stride = out.stride(0), 0
+    if persistent is None:
+        persistent = tcgen05_persistent
+    if persistent == "auto":
+        persistent = False
+    if persistent and splits == 1 and bn >= 128:
+        _call("me_gemm_tcgen05_persistent", matrix_tensor_map(x, 128).ptr, matrix_tensor_map(weight, box_w).ptr, out.data_ptr(),
+              _dt(out), ldc, M, N, K, epi, bn, err.data_ptr(), _stream())
+        return
     _call("me_gemm_tcgen05", matrix_tensor_map(x, 128).ptr, matrix_tensor_map(weight, box_w).ptr, out.data_ptr(), _dt(out),
           ldc, M, N, K, epi, bn, splits, split_stride, err.data_ptr(), _stream())
 

@@ -197,22 +197,23 @@ def test_small_batch_products(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M, N, K", [(128, 64, 64), (128, 128, 64), (129, 200, 136), (300, 4096, 1024), (2048, 1024, 2048),
-                                     (1000, 1032, 3072), (64, 151936 // 16, 1024)])
-@pytest.mark.parametrize("tile_n", [64, 128, 256])
-def test_tcgen05_products(ops, M, N, K, tile_n):
-    # the tcgen05 kernel by name: every tile width, edges in M, N and K, bfloat16 and float32 results, SiLU epilogue
+                                     (1000, 1032, 3072), (64, 151936 // 16, 1024), (3000, 9000, 264)])
+@pytest.mark.parametrize("tile_n, persistent", [(64, False), (128, False), (256, False), (128, True), (256, True)])
+def test_tcgen05_products(ops, M, N, K, tile_n, persistent):
+    # the tcgen05 kernels by name: every tile width, edges in M, N and K, bfloat16 and float32 results, SiLU epilogue;
+    # one tile a block, and the persistent form (a block walks tiles: none, one, or half a dozen with the last shape)
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5)
     err = torch.zeros(4, dtype=torch.int32, device=DEV)
     for od in (torch.bfloat16, torch.float32):
         out, ref = torch.full((M, N), float("nan"), dtype=od, device=DEV), torch.empty(M, N, dtype=od, device=DEV)
-        ops.linear_tcgen05(x, w, out, "none", err, tile_n=tile_n)
+        ops.linear_tcgen05(x, w, out, "none", err, tile_n=tile_n, persistent=persistent)
         plain_ops.linear(x, w, ref)
         assert err.tolist() == [0, 0, 0, 0]
         close(out, ref, od, scale=4)
     if N % 2 == 0:
         I = N // 2
         out, ref = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV), torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
-        ops.linear_tcgen05(x, w, out, "silu_mul", err, tile_n=tile_n)
+        ops.linear_tcgen05(x, w, out, "silu_mul", err, tile_n=tile_n, persistent=persistent)
         plain_ops.linear(x, w, ref, epilogue="silu_mul")
         assert err.tolist() == [0, 0, 0, 0]
         close(out, ref, torch.bfloat16, scale=4)
