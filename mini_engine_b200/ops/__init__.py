@@ -462,14 +462,16 @@ def tcgen05_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
 tcgen05_persistent = "auto"     # the persistent form of the tcgen05 product: "auto", True or False (for comparisons)
 
 
-def tcgen05_persistent_pays(M: int, N: int, epi: int) -> bool:
+def tcgen05_persistent_pays(M: int, N: int, K: int, epi: int) -> bool:
     """Whether a product of M rows and N output columns runs the persistent form of the tcgen05 kernel (one block an
-    SM walking 128 x 256 tiles with two accumulators): from two tiles an SM on.  There the loads of the next tile and
+    SM walking 128 x 256 tiles with two accumulators): from two tiles an SM on (a little earlier where K is short and a
+    tile's fixed part weighs more: q|k|v of 2,048 rows at the 0.6B sizes).  There the loads of the next tile and
     the epilogue of the last one run beside a tile's products, which is worth a fifth to a third of gate|up at every
     size measured and of q|k|v at 2,048 rows; with fewer tiles (o_proj, down_proj up to a few thousand rows) the form
     with two blocks an SM is level or ahead."""
     out_cols = 128 if epi else 256
-    return ((M + 127) // 128) * ((N + out_cols - 1) // out_cols) >= 2 * sm_count()
+    tiles = ((M + 127) // 128) * ((N + out_cols - 1) // out_cols)
+    return tiles >= 2 * sm_count() or (K <= 1024 and 10 * tiles >= 17 * sm_count())
 
 
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str, err: torch.Tensor,
@@ -487,7 +489,7 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epi
         # columns per tile) does best at 128 while both the rows and K are few, and again where the output is so large
         # (a quarter of a GB and more) that the wide tiles' order through it stops fitting L2.
         m_tiles = (M + 127) // 128
-        if persistent is None and tcgen05_persistent == "auto" and splits == 1 and tcgen05_persistent_pays(M, N, epi):
+        if persistent is None and tcgen05_persistent == "auto" and splits == 1 and tcgen05_persistent_pays(M, N, K, epi):
             tile_n, persistent = 256, True
         elif epi:
             tile_n = 256 if (M >= 4096 or K >= 4096) and m_tiles * ((N + 127) // 128) <= 10000 else 128
