@@ -137,6 +137,8 @@ class ModelRunner:
         self.graph_launches = 0          # kernels replayed from graphs (they bypass ops.launches)
         self.tune_decode_form = True     # a captured decode step keeps the fastest form of the decode attention kernel
         self.tune_decode_max_bucket = 32 # ... measured for batch buckets below this one; by rule from there on
+        self.tune_decode_max_step_ms = 2.0   # ... and only while a step is shorter than this: a capture of 36 large layers
+                                             # costs 0.1 s, which the few microseconds a layer between the forms never repay
         self.pool_sizing: dict = {}      # what the pool was sized from, when it was sized here
         self.num_pages = num_pages if num_pages > 0 else self._size_pool(gpu_memory_utilization)
         self.kv_pools = self._make_pools(self.num_pages)
@@ -504,6 +506,8 @@ class ModelRunner:
                 t = e0.elapsed_time(e1)
                 if best is None or t < best[0]:
                     best = (t, form, g.graph, g.logits, g.tokens, g.launches)
+                if t / 4 > self.tune_decode_max_step_ms:
+                    break                            # a long step (large layers): the forms differ by a per cent of it at most
         finally:
             ops.decode_form = "auto"
         _, g.form, g.graph, g.logits, g.tokens, g.launches = best
