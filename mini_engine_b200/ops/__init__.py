@@ -782,12 +782,12 @@ decode_tiles = "auto"     # tiles of 128 keys that a block of the "one_tile" for
 def decode_tiles_for(rows: int, key_tiles: int) -> int:
     """How many tiles of 128 keys a block of the fused decode kernel's "one_tile" form walks, for ``rows`` = requests x
     key/value heads (x strips of 16 query heads) and contexts of ``key_tiles`` tiles: the largest power of two (up to 32)
-    that still leaves as many blocks as the device holds at once (four of the tiled kernel share an SM).  Measured on
-    batches of 16 to 256 at contexts of 1,100 to 4,100 with 2 and 8 query heads a group: the best count was this one
-    in all but one case (there 4% behind)."""
+    that still leaves two partitions a request and as many blocks as the device holds at once (four of the tiled
+    kernel share an SM).  Measured on batches of 16 to 256 at contexts of 1,100 to 4,100 with 2 and 8 query heads a
+    group: the best count was this one in every case (one partition for the whole context was 2 to 4% behind two)."""
     want = 4 * sm_count()
     tiles = 1
-    while tiles < 32 and tiles < key_tiles and rows * -(-key_tiles // (2 * tiles)) >= want:
+    while tiles < 32 and 2 * tiles < key_tiles and rows * -(-key_tiles // (2 * tiles)) >= want:
         tiles *= 2
     return tiles
 

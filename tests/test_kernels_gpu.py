@@ -634,16 +634,16 @@ def test_attention_decode_that_prepares_q_and_the_newest_key_itself(ops, nh, nkv
 
 def test_how_many_key_tiles_a_block_of_decode_attention_walks(ops):
     # the rule of ops.decode_tiles_for: one tile while single tiles make no more blocks than the device holds at once, then
-    # the largest power of two (up to 32, and no more than the context has) that still leaves that many blocks
+    # the largest power of two (up to 32, and less than the context's tiles: two partitions at least) that still leaves that many blocks
     want = 4 * ops.sm_count()
     assert ops.decode_tiles_for(8 * 8, 9) == 1                       # 8 requests x 8 key/value heads at 1,100 tokens
     assert ops.decode_tiles_for(10 ** 6, 1) == 1                     # a context of one tile has nothing to walk
     for rows, key_tiles in ((512, 9), (512, 17), (512, 33), (2048, 9), (128, 32), (256, 9), (128, 17), (4096, 400)):
         t = ops.decode_tiles_for(rows, key_tiles)
-        assert t in (1, 2, 4, 8, 16, 32) and (t == 1 or t // 2 < key_tiles)
+        assert t in (1, 2, 4, 8, 16, 32) and (t == 1 or t < key_tiles)
         if t > 1:
             assert rows * -(-key_tiles // t) >= want                 # enough blocks are left
-        if t < 32 and t < key_tiles:
+        if t < 32 and 2 * t < key_tiles:
             assert rows * -(-key_tiles // (2 * t)) < want            # and twice as many tiles would leave too few
 
 
