@@ -106,6 +106,20 @@ def test_whole_requests(name, dtype):
     _check(name, dtype, reqs, got, kept, "w", "whole")
 
 
+@pytest.mark.parametrize("name", ["0.6B", "8B"])
+def test_a_prompt_of_so_many_rows_that_a_block_of_the_products_walks_tiles(name):
+    # 1,900 tokens in one step: q|k|v and gate|up have two tiles an SM and more and run the persistent form of the tcgen05
+    # product (at the 8B sizes the other two as well)
+    from mini_engine_b200 import ops
+    _, cfg, _, _ = _model(name)
+    T = 1900
+    assert ops.tcgen05_persistent_pays(T, cfg["intermediate_size"], cfg["hidden_size"], 1)
+    (r,) = helpers.random_requests(2000, (T,), seed=12)
+    steps = helpers.trace_whole([r])
+    got, kept, _, _ = _run(name, "bfloat16", steps, helpers.max_live_tokens(steps))
+    _check(name, "bfloat16", [r], got, kept, "w", "one long prompt")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["0.6B", "8B", "32B"])
 def test_last_32_tokens_one_by_one(name, dtype):
