@@ -547,10 +547,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
     rows gate | up and writes ``silu(x Wg^T) * (x Wu^T)``.
 
     float32 operands (and any mix of dtypes) run the CUDA-core kernel of csrc/gemm_simt.cu: plain
-    FMA, no reduced-precision matrix mode.  bfloat16 x bfloat16 products run csrc/gemm_skinny.cu for up
-    to 16 rows (decode) and the tcgen05 kernel of csrc/gemm_tcgen05.cu above that; shapes those refuse
-    (K no multiple of 8) go to cuBLAS, as all the reference's products do through ``F.linear``
-    (layers/linear.py:26,45), with SiLU-and-multiply as a kernel of ours behind it.
+    FMA, no reduced-precision matrix mode.  bfloat16 x bfloat16 products of up to 16 rows run csrc/gemm_stream.cu
+    where the weight has 32 MB and more (the vocabulary product of a decode step) and csrc/gemm_skinny.cu else
+    (the layers' own products in decode do not come here: ``decode_linear``); 128 rows and more run the tcgen05 kernels
+    of csrc/gemm_tcgen05.cu; 17 to 127 rows, and shapes those refuse (K no multiple of 8), go to cuBLAS, as all the
+    reference's products do through ``F.linear`` (layers/linear.py:26,45), with SiLU-and-multiply as a kernel of ours
+    behind it.
 
     ``err``: the int32[4] error word of the step; the tcgen05 kernel sets flag 1 there when one of its bounded
     waits runs out.  Without it products of 128 rows and more go to cuBLAS."""
