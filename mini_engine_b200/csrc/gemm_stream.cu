@@ -1,6 +1,7 @@
 // Products of a decode step (up to 16 rows) over ANY K, with the neighbouring element-wise work folded in:
 // the kernel of gemm_decode.cu for layers whose rows are too long for one block to hold (K beyond 3,072: the
-// 8B and 32B layer sizes), where a product is a long stream of weights and what counts is bytes in flight.
+// 8B and 32B layer sizes) and for the vocabulary product at every size, where a product is a long stream of weights and what
+// counts is bytes in flight.
 //
 // As there, the weight rows fill the M side of mma.sync m16n8k16, the batch sits on the N side, and the epilogues
 // are the same three (see gemm_decode.cu): plain results; SiLU(gate) * up for a weight of rows gate | up
