@@ -638,12 +638,14 @@ def test_how_many_key_tiles_a_block_of_decode_attention_walks(ops):
     want = 4 * ops.sm_count()
     assert ops.decode_tiles_for(8 * 8, 9) == 1                       # 8 requests x 8 key/value heads at 1,100 tokens
     assert ops.decode_tiles_for(10 ** 6, 1) == 1                     # a context of one tile has nothing to walk
-    for rows, key_tiles in ((512, 9), (512, 17), (512, 33), (2048, 9), (128, 32), (256, 9), (128, 17), (4096, 400)):
+    assert ops.decode_tiles_for(8, 64) == 4 and ops.decode_tiles_for(8, 235) == 4     # one request, 8,192 / 30,000 tokens
+    assert ops.decode_tiles_for(8, 40) == 2 and ops.decode_tiles_for(8, 20) == 1        # (four tiles a block would leave 80 blocks; 2,560 tokens are not long)
+    for rows, key_tiles in ((512, 9), (512, 17), (512, 33), (2048, 9), (128, 9), (256, 9), (128, 16), (4096, 400)):
         t = ops.decode_tiles_for(rows, key_tiles)
         assert t in (1, 2, 4, 8, 16, 32) and (t == 1 or t < key_tiles)
-        if t > 1:
+        if t > 1 and not (key_tiles > 32 and t <= 4):
             assert rows * -(-key_tiles // t) >= want                 # enough blocks are left
-        if t < 32 and 2 * t < key_tiles:
+        if t < 32 and 2 * t < key_tiles and not (key_tiles > 32 and t <= 4):
             assert rows * -(-key_tiles // (2 * t)) < want            # and twice as many tiles would leave too few
 
 
