@@ -885,6 +885,28 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
       f_s[p] = mp == -INFINITY ? 0.f : expf(mp - M);
     }
     __syncthreads();
+    if (hd <= (int)blockDim.x) {
+      // a column a thread (the usual head sizes): 32 partitions' loads at a time, so that a long context's dozens of
+      // partitions cost two or three trips to memory and not one per eight
+      for (int q0 = 0; q0 < n; q0 += 32) {
+        float lv[32], ov[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool ok = q0 + i < n && f_s[q0 + i] != 0.f;
+          lv[i] = ok ? tmp_l[row0 + p0 + q0 + i] : 0.f;
+          ov[i] = ok && tid < hd ? tmp_out[(row0 + p0 + q0 + i) * hd + tid] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {               // partitions in index order
+          const float f = q0 + i < n ? f_s[q0 + i] : 0.f;
+          if (f != 0.f) {
+            lt += f * lv[i];
+            acc[0] += f * ov[i];
+          }
+        }
+      }
+      continue;
+    }
     for (int q0 = 0; q0 < n; q0 += 8) {
       float lv[8], ov[4][8];
 #pragma unroll
