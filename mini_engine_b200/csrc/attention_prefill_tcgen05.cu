@@ -385,7 +385,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
   unsigned char* q_s = smem;
   unsigned char* k_s = q_s + Q_BYTES;
   unsigned char* v_s = k_s + RING * KV_BYTES;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = tc5::uniform_warp_index(), lane = threadIdx.x & 31;
 
   const int G = nh / nkv, packs = G / gp, tq = TA_ROWS / gp;
   const int tile = gridDim.y - 1 - blockIdx.y;
@@ -471,49 +471,49 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
         tma::load_2d(dst0 + s * KV_BYTES + hf * KB_BYTES + pg * page_size * 128, &kv_map, hf * 64, first_row, &full[s]);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = tc5::instr_desc_bf16(TA_ROWS, KEYS);
-      constexpr uint32_t idesc_o = tc5::instr_desc_bf16(TA_ROWS, HD, true);
-      ok = tma::mbar_wait(&q_bar, 0);
-      // S(it) = Q K(it)^T into S buffer it % 3, which held S and then P of tile it - 3: P V (it - 3) was issued an
-      // iteration ago, and the tensor core runs this thread's products in the order of their issue.
-      auto issue_qk = [&](int it) -> bool {
-        const int s = it % RING;
-        if (!tma::mbar_wait(&k_full[s], (it / RING) & 1)) return false;
-        tc5::fence_after_sync();
+    // The issuing warp: all lanes run the loop with the same values, an elected lane issues.
+    constexpr uint32_t idesc_s = tc5::instr_desc_bf16(TA_ROWS, KEYS);
+    constexpr uint32_t idesc_o = tc5::instr_desc_bf16(TA_ROWS, HD, true);
+    const tc5::DescWords q_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(q_s));
+    const tc5::DescWords k_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(k_s));
+    const tc5::DescWords v_desc = tc5::words_of(tc5::smem_desc_mn_major_sw128(v_s, KB_BYTES));
+    ok = tc5::mbar_wait_warp(&q_bar, 0);
+    // S(it) = Q K(it)^T into S buffer it % 3, which held S and then P of tile it - 3: P V (it - 3) was issued an
+    // iteration ago, and the tensor core runs this warp's products in the order of their issue.
+    auto issue_qk = [&](int it) -> bool {
+      const int s = it % RING;
+      if (!tc5::mbar_wait_warp(&k_full[s], (it / RING) & 1)) return false;
+      tc5::fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < HALVES; ++c) {
-          const uint64_t a_desc = tc5::smem_desc_k_major_sw128(q_s + c * HALF_BYTES);
-          const uint64_t b_desc = tc5::smem_desc_k_major_sw128(k_s + s * KV_BYTES + c * KB_BYTES);
+      for (int c = 0; c < HALVES; ++c) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc5::mma_f16(tmem_s + s * KEYS, a_desc + 2 * k, b_desc + 2 * k, idesc_s, c > 0 || k > 0);
-        }
-        tc5::commit(&s_ready[s]);
-        tc5::commit(&k_empty[s]);
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
-      if (ok && n_tiles > 1) ok = issue_qk(1);
-      for (int it = 0; it < n_tiles && ok; ++it) {
-        const int s = it % RING, g = it & 1;
-        if (it + 2 < n_tiles) {                            // two tiles ahead: one for each softmax group
-          ok = issue_qk(it + 2);
-          if (!ok) break;
-        }
-        ok = tma::mbar_wait(&p_ready[g], (it >> 1) & 1);   // P(it) is in tensor memory, O is rescaled if it had to be
-        if (ok) ok = tma::mbar_wait(&v_full[s], (it / RING) & 1);
-        if (!ok) break;
-        tc5::fence_after_sync();
-        // O += P V: A = P, 8 columns of tensor memory for the 16 keys of a step; B = V [KEYS][HD], MN-major: 16 keys
-        // are 2048 bytes further in every 64-column half, the halves are KB_BYTES apart.
-#pragma unroll
-        for (int k = 0; k < KEYS / 16; ++k) {
-          const uint64_t b_desc = tc5::smem_desc_mn_major_sw128(v_s + s * KV_BYTES + k * 2048, KB_BYTES);
-          tc5::mma_f16_a_in_tmem(tmem_o, tmem_s + s * KEYS + k * 8, b_desc, idesc_o, it > 0 || k > 0);
-        }
-        tc5::commit(&o_ready[g]);                          // P V (it) and everything before it are done
-        tc5::commit(&v_empty[s]);
+        for (int k = 0; k < 4; ++k)                          // (offsets in units of 16 bytes)
+          tc5::mma_f16_elect(tmem_s + s * KEYS, q_desc, (c * HALF_BYTES >> 4) + 2 * k, k_desc,
+                             ((s * KV_BYTES + c * KB_BYTES) >> 4) + 2 * k, idesc_s, c > 0 || k > 0);
       }
+      tc5::commit_elect(&s_ready[s]);
+      tc5::commit_elect(&k_empty[s]);
+      return true;
+    };
+    if (ok) ok = issue_qk(0);
+    if (ok && n_tiles > 1) ok = issue_qk(1);
+    for (int it = 0; it < n_tiles && ok; ++it) {
+      const int s = it % RING, g = it & 1;
+      if (it + 2 < n_tiles) {                              // two tiles ahead: one for each softmax group
+        ok = issue_qk(it + 2);
+        if (!ok) break;
+      }
+      ok = tc5::mbar_wait_warp(&p_ready[g], (it >> 1) & 1);  // P(it) is in tensor memory, O is rescaled if it had to be
+      if (ok) ok = tc5::mbar_wait_warp(&v_full[s], (it / RING) & 1);
+      if (!ok) break;
+      tc5::fence_after_sync();
+      // O += P V: A = P, 8 columns of tensor memory for the 16 keys of a step; B = V [KEYS][HD], MN-major: 16 keys
+      // are 2048 bytes further in every 64-column half, the halves are KB_BYTES apart.
+#pragma unroll
+      for (int k = 0; k < KEYS / 16; ++k)
+        tc5::mma_f16_a_in_tmem_elect(tmem_o, tmem_s + s * KEYS + k * 8, v_desc, (s * KV_BYTES + k * 2048) >> 4, idesc_o, it > 0 || k > 0);
+      tc5::commit_elect(&o_ready[g]);                      // P V (it) and everything before it are done
+      tc5::commit_elect(&v_empty[s]);
     }
   } else {
     const int lane_base = (warp & 3) * 32, g = (warp - 2) >> 2;
@@ -547,9 +547,12 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
         if (__all_sync(0xffffffffu, c_max < c0 || c_min > c0 + 31)) return 1;
         return 2;
       };
+      // The thread's whole row of S, 128 scores, stays in registers from the maximum to the exponentials: tensor
+      // memory is read once, and the reads' latency is paid once a tile.
+      float s_lo[64], s_hi[64];
+      auto piece = [](float (&half)[64], int q) -> float (&)[32] { return *reinterpret_cast<float(*)[32]>(&half[32 * q]); };
       if (ok) {
         tc5::fence_after_sync();
-        float a[32], c[32];
         auto piece_max = [&](const float (&sv)[32], int c0) {
           const int kind = piece_kind(c0);
           if (kind == 0) {
@@ -561,14 +564,14 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
               if (seen(c0 + jj)) mx = fmaxf(mx, sv[jj]);
           }
         };
-#pragma unroll
-        for (int c0 = 0; c0 < KEYS; c0 += 64) {
-          tc5::ld_32cols(t_s + c0, a);
-          tc5::ld_32cols(t_s + c0 + 32, c);
-          tc5::wait_ld();
-          piece_max(a, c0);
-          piece_max(c, c0 + 32);
-        }
+        tc5::ld_64cols(t_s, s_lo);
+        tc5::wait_ld();
+        tc5::ld_64cols(t_s + 64, s_hi);                      // on its way while the first half is worked on
+        piece_max(piece(s_lo, 0), 0);
+        piece_max(piece(s_lo, 1), 32);
+        tc5::wait_ld();
+        piece_max(piece(s_hi, 0), 64);
+        piece_max(piece(s_hi, 1), 96);
       }
       // reference(it - 1) from the other group, reference(it) to it
       float m_prev = neg_inf;
@@ -594,13 +597,13 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
             tc5::fence_after_sync();
             const float alpha = raise ? ex2((m_prev - m_new) * scale_log2) : 1.f;      // m_prev = -inf gives 0
 #pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 32) {
-              float v[32];
-              tc5::ld_32cols(tmem_o + t_row + c0, v);
+            for (int c0 = 0; c0 < HD; c0 += 16) {             // (a rare path: small pieces, the row of S is held meanwhile)
+              float v[16];
+              tc5::ld_16cols(tmem_o + t_row + c0, v);
               tc5::wait_ld();
 #pragma unroll
-              for (int jj = 0; jj < 32; ++jj) v[jj] *= alpha;
-              tc5::st_32cols(tmem_o + t_row + c0, v);
+              for (int jj = 0; jj < 16; ++jj) v[jj] *= alpha;
+              tc5::st_16cols(tmem_o + t_row + c0, *reinterpret_cast<uint32_t(*)[16]>(v));
             }
             tc5::wait_st();
           }
@@ -647,19 +650,10 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
           }
           tc5::st_16cols(t_s + (c >> 1), pk);
         };
-        float a[32], c[32];
-        tc5::ld_32cols(t_s, a);
-        tc5::wait_ld();
-        tc5::ld_32cols(t_s + 32, c);                         // on its way while the piece before is worked on
-        piece_of_p(a, 0);
-        tc5::wait_ld();
-        tc5::ld_32cols(t_s + 64, a);
-        piece_of_p(c, 32);
-        tc5::wait_ld();
-        tc5::ld_32cols(t_s + 96, c);
-        piece_of_p(a, 64);
-        tc5::wait_ld();
-        piece_of_p(c, 96);
+        piece_of_p(piece(s_lo, 0), 0);
+        piece_of_p(piece(s_lo, 1), 32);
+        piece_of_p(piece(s_hi, 0), 64);
+        piece_of_p(piece(s_hi, 1), 96);
         tc5::wait_st();
         fence_async_smem();                                  // the zeroed rows of V were written by ordinary stores
         tc5::fence_before_sync();

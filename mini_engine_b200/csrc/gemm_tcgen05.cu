@@ -69,7 +69,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
   __shared__ uint32_t tmem_slot;
   unsigned char* smem = tg_smem_raw + ((1024u - (tma::smem_addr(tg_smem_raw) & 1023u)) & 1023u);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = tc5::uniform_warp_index(), lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * OUT_COLS;
   const int kb0 = blockIdx.z * kb_per_split;
   const int num_kb = min(kb_per_split, (K + TG_BK - 1) / TG_BK - kb0);
@@ -121,22 +121,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = tc5::instr_desc_bf16(TG_BM, BN);
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        ok = tma::mbar_wait(&full_bar[s], (kb / STAGES) & 1);
-        if (!ok) break;
-        tc5::fence_after_sync();
-        const uint64_t a_desc = tc5::smem_desc_k_major_sw128(smem + s * STAGE_BYTES);
-        const uint64_t b_desc = tc5::smem_desc_k_major_sw128(smem + s * STAGE_BYTES + TG_A_BYTES);
+    // all lanes run the loop, an elected one issues
+    constexpr uint32_t idesc = tc5::instr_desc_bf16(TG_BM, BN);
+    const tc5::DescWords a_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(smem));
+    const tc5::DescWords b_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(smem + TG_A_BYTES));
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % STAGES;
+      ok = tc5::mbar_wait_warp(&full_bar[s], (kb / STAGES) & 1);
+      if (!ok) break;
+      tc5::fence_after_sync();
+      const uint32_t stage = (uint32_t)(s * STAGE_BYTES) >> 4;
 #pragma unroll
-        for (int k = 0; k < TG_BK / 16; ++k)       // 32 bytes further along K per step: +2 in units of 16 bytes
-          tc5::mma_f16(tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > 0 || k > 0);
-        tc5::commit(&empty_bar[s]);                // the stage is free once these MMAs have read it
-      }
-      tc5::commit(&done_bar);                      // the accumulator is complete
+      for (int k = 0; k < TG_BK / 16; ++k)         // 32 bytes further along K per step: +2 in units of 16 bytes
+        tc5::mma_f16_elect(tmem, a_desc, stage + 2 * k, b_desc, stage + 2 * k, idesc, kb > 0 || k > 0);
+      tc5::commit_elect(&empty_bar[s]);            // the stage is free once these MMAs have read it
     }
+    tc5::commit_elect(&done_bar);                  // the accumulator is complete
   } else {
     // Epilogue: warp w reads lanes 32 (w % 4) .. +31 of tensor memory; a lane is a row of the tile.
     ok = tma::mbar_wait(&done_bar, 0);
@@ -215,7 +215,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
   __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_slot;
   unsigned char* smem = tg_smem_raw + ((1024u - (tma::smem_addr(tg_smem_raw) & 1023u)) & 1023u);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = tc5::uniform_warp_index(), lane = threadIdx.x & 31;
   const int m_tiles = (M + TG_BM - 1) / TG_BM, n_tiles = (N + OUT_COLS - 1) / OUT_COLS, num_kb = (K + TG_BK - 1) / TG_BK;
   const int tiles = m_tiles * n_tiles;
   const int my_tiles = blockIdx.x < tiles ? (tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
@@ -280,28 +280,31 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = tc5::instr_desc_bf16(TG_BM, BN);
-      long long item = 0;
-      for (int i = 0; i < my_tiles; ++i) {
-        const int buf = i & 1;
-        if (i >= 2 && ok) ok = tma::mbar_wait(&acc_empty[buf], (uint32_t)(((i >> 1) - 1) & 1));      // read out by the epilogue
+    // all lanes run the loop, an elected one issues
+    constexpr uint32_t idesc = tc5::instr_desc_bf16(TG_BM, BN);
+    const tc5::DescWords a_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(smem));
+    const tc5::DescWords b_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(smem + TG_A_BYTES));
+    uint32_t s = 0, phase = 0;                       // the ring's stage and the parity of its round
+    for (int i = 0; i < my_tiles; ++i) {
+      const int buf = i & 1;
+      if (i >= 2 && ok) ok = tc5::mbar_wait_warp(&acc_empty[buf], (uint32_t)(((i >> 1) - 1) & 1));      // read out by the epilogue
+      tc5::fence_after_sync();
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (ok) ok = tc5::mbar_wait_warp(&full_bar[s], phase);
         tc5::fence_after_sync();
-        for (int kb = 0; kb < num_kb; ++kb, ++item) {
-          const int s = (int)(item % STAGES);
-          if (ok) ok = tma::mbar_wait(&full_bar[s], (uint32_t)((item / STAGES) & 1));
-          tc5::fence_after_sync();
-          if (ok) {
-            const uint64_t a_desc = tc5::smem_desc_k_major_sw128(smem + s * STAGE_BYTES);
-            const uint64_t b_desc = tc5::smem_desc_k_major_sw128(smem + s * STAGE_BYTES + TG_A_BYTES);
+        if (ok) {
+          const uint32_t stage = (s * (uint32_t)STAGE_BYTES) >> 4;
 #pragma unroll
-            for (int k = 0; k < TG_BK / 16; ++k)     // 32 bytes further along K per step: +2 in units of 16 bytes
-              tc5::mma_f16(tmem + buf * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > 0 || k > 0);
-          }
-          tc5::commit(&empty_bar[s]);                // the stage is free once these MMAs have read it
+          for (int k = 0; k < TG_BK / 16; ++k)       // 32 bytes further along K per step: +2 in units of 16 bytes
+            tc5::mma_f16_elect(tmem + buf * BN, a_desc, stage + 2 * k, b_desc, stage + 2 * k, idesc, kb > 0 || k > 0);
         }
-        tc5::commit(&acc_full[buf]);                 // the tile's sums are complete
+        tc5::commit_elect(&empty_bar[s]);            // the stage is free once these MMAs have read it
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
       }
+      tc5::commit_elect(&acc_full[buf]);             // the tile's sums are complete
     }
   } else {
     // Epilogue: warp w reads lanes 32 (w % 4) .. +31 of tensor memory; a lane is a row of the tile.

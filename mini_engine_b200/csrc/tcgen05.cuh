@@ -79,6 +79,41 @@ __device__ __forceinline__ void commit(unsigned long long* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tma::smem_addr(bar)) : "memory");
 }
 
+// ---- issue by a whole warp ------------------------------------------------------------------------------------
+// The warp that issues the products runs its loop with all 32 lanes, every lane holding the same values, and one
+// elected lane issues.  A loop inside ``if (lane == 0)`` is divergent code to the compiler, which then computes
+// descriptors and addresses in ordinary registers and moves them over for every product; the issuing thread, not
+// the tensor core, set the pace that way (measured on a B200: eight products of 128 x 128 x 16 from shared memory in
+// 890 clocks from one lane, 700 from a warp with the descriptors' low words computed and the high words held).
+// The warp's index must be known to be the same in all lanes: take it through ``uniform_warp_index()``.
+__device__ __forceinline__ int uniform_warp_index() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
+// A shared-memory descriptor as two words: tiles, stages and K steps differ in the low word (start address / 16) only.
+struct DescWords { uint32_t lo, hi; };
+__device__ __forceinline__ DescWords words_of(uint64_t desc) { return {(uint32_t)desc, (uint32_t)(desc >> 32)}; }
+// D[tmem] (+)= A[smem] * B[smem]^T; ``a_off`` and ``b_off`` (units of 16 bytes) are added to the start addresses.
+__device__ __forceinline__ void mma_f16_elect(uint32_t d_tmem, DescWords a, uint32_t a_off, DescWords b, uint32_t b_off, uint32_t idesc,
+                                              bool accumulate) {
+  asm volatile("{\n.reg .pred p, q;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, %6, 0;\n"
+               "elect.sync _|q, 0xffffffff;\n@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+               ::"r"(d_tmem), "r"(a.lo + a_off), "r"(a.hi), "r"(b.lo + b_off), "r"(b.hi), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+// The same with A in tensor memory.
+__device__ __forceinline__ void mma_f16_a_in_tmem_elect(uint32_t d_tmem, uint32_t a_tmem, DescWords b, uint32_t b_off, uint32_t idesc,
+                                                        bool accumulate) {
+  asm volatile("{\n.reg .pred p, q;\n.reg .b64 db;\nmov.b64 db, {%2, %3};\nsetp.ne.b32 p, %5, 0;\n"
+               "elect.sync _|q, 0xffffffff;\n@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n"
+               ::"r"(d_tmem), "r"(a_tmem), "r"(b.lo + b_off), "r"(b.hi), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+// One arrival when every MMA the warp's elected lane issued so far has finished (the election names the same lane every time).
+__device__ __forceinline__ void commit_elect(unsigned long long* bar) {
+  asm volatile("{\n.reg .pred q;\nelect.sync _|q, 0xffffffff;\n@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n"
+               ::"r"(tma::smem_addr(bar)) : "memory");
+}
+// A bounded wait of all lanes of a warp on one barrier, with one answer for the warp.
+__device__ __forceinline__ bool mbar_wait_warp(unsigned long long* bar, uint32_t phase) {
+  return __all_sync(0xffffffffu, tma::mbar_wait(bar, phase));
+}
+
 // 32 consecutive float32 columns of this thread's lane.
 __device__ __forceinline__ void ld_32cols(uint32_t taddr, float (&v)[32]) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
