@@ -242,41 +242,52 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 
   if (warp == 0) {
     if (lane == 0) {
-      auto place = [&](long long item, int& m0, int& n0, int& k0) {
-        const int tile = blockIdx.x + (int)(item / num_kb) * gridDim.x;
-        m0 = (tile % m_tiles) * TG_BM;
-        n0 = (tile / m_tiles) * OUT_COLS;
-        k0 = (int)(item % num_kb) * TG_BK;
+      // A place in this block's sequence of stages, moved on without a division (one thread feeds the whole SM).
+      struct Walk { int tile, kb, m0, n0, s; uint32_t phase; };
+      auto start = [&](Walk& w) {
+        w.tile = blockIdx.x;
+        w.kb = 0;
+        w.m0 = (w.tile % m_tiles) * TG_BM;
+        w.n0 = (w.tile / m_tiles) * OUT_COLS;
+        w.s = 0;
+        w.phase = 0;
       };
-      auto issue_w = [&](long long item) {
-        int m0, n0, k0;
-        place(item, m0, n0, k0);
-        const int s = (int)(item % STAGES);
-        unsigned char* b_dst = smem + s * STAGE_BYTES + TG_A_BYTES;
-        tma::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        if (EPI == 1) {
-          tma::load_2d(b_dst, &map_w, k0, n0, &full_bar[s]);
-          tma::load_2d(b_dst + B_BYTES / 2, &map_w, k0, N + n0, &full_bar[s]);
-        } else {
-          tma::load_2d(b_dst, &map_w, k0, n0, &full_bar[s]);
+      auto step = [&](Walk& w) {
+        if (++w.kb == num_kb) {
+          w.kb = 0;
+          w.tile += gridDim.x;
+          w.m0 = (w.tile % m_tiles) * TG_BM;
+          w.n0 = (w.tile / m_tiles) * OUT_COLS;
+        }
+        if (++w.s == STAGES) {
+          w.s = 0;
+          w.phase ^= 1;
         }
       };
-      auto issue_a = [&](long long item) {
-        int m0, n0, k0;
-        place(item, m0, n0, k0);
-        const int s = (int)(item % STAGES);
-        tma::load_2d(smem + s * STAGE_BYTES, &map_a, k0, m0, &full_bar[s]);
+      auto issue_w = [&](const Walk& w) {
+        unsigned char* b_dst = smem + w.s * STAGE_BYTES + TG_A_BYTES;
+        tma::mbar_expect_tx(&full_bar[w.s], STAGE_BYTES);
+        if (EPI == 1) {
+          tma::load_2d(b_dst, &map_w, w.kb * TG_BK, w.n0, &full_bar[w.s]);
+          tma::load_2d(b_dst + B_BYTES / 2, &map_w, w.kb * TG_BK, N + w.n0, &full_bar[w.s]);
+        } else {
+          tma::load_2d(b_dst, &map_w, w.kb * TG_BK, w.n0, &full_bar[w.s]);
+        }
       };
+      auto issue_a = [&](const Walk& w) { tma::load_2d(smem + w.s * STAGE_BYTES, &map_a, w.kb * TG_BK, w.m0, &full_bar[w.s]); };
       // The weights are no output of the kernel before this one; the activations are.
       const long long ahead = total < STAGES ? total : STAGES;
-      for (long long item = 0; item < ahead; ++item) issue_w(item);
+      Walk ww, wa;
+      start(ww);
+      start(wa);
+      for (long long item = 0; item < ahead; ++item, step(ww)) issue_w(ww);
       pdl_wait();
-      for (long long item = 0; item < ahead; ++item) issue_a(item);
-      for (long long item = ahead; item < total && ok; ++item) {
-        ok = tma::mbar_wait(&empty_bar[item % STAGES], (uint32_t)(((item / STAGES) & 1) ^ 1));
+      for (long long item = 0; item < ahead; ++item, step(wa)) issue_a(wa);
+      for (long long item = ahead; item < total && ok; ++item, step(ww)) {
+        ok = tma::mbar_wait(&empty_bar[ww.s], ww.phase ^ 1);      // the products of the round before have read the stage
         if (!ok) break;
-        issue_w(item);
-        issue_a(item);
+        issue_w(ww);
+        issue_a(ww);
       }
     }
   } else if (warp == 1) {
@@ -353,6 +364,315 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
   if (warp == 1) tc5::tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// ---- work shared out evenly ---------------------------------------------------------------------------------
+// The persistent form gives a block whole tiles: with 1.3 or 2.2 tiles an SM most SMs idle through the last round.  Here
+// a block takes whole tiles in that same order (tile blockIdx.x, + gridDim.x, ...) for all rounds but the last one or
+// two; the stages of the tiles that remain (at least one tile a block where there are that many, fewer than two; 64 of K
+// a stage, tile after tile) are one sequence, cut into gridDim.x ranges of the same length: there a block computes the
+// end of one tile and the beginning of the next.  (All tiles in one such sequence was tried first: the blocks then work on
+// 148 different tiles of W at a time, which L2 does not hold, and the products ran a third slower.)  The block with a
+// tile's beginning owns the tile: it adds what the blocks after it computed of it, in the order of the blocks (float32
+// sums through ``partials``, a flag for each of a block's four epilogue warps once they are written), and applies the
+// epilogue.  A contributing block's part is the FIRST thing it computes in the shared rounds and the owner wants it at the
+// END of its own range, so no block waits long, and none waits for a block that waits for it; the waits are bounded.
+// The owner's epilogue warps bring a contributor's sums into the (by then idle) ring of stages with one bulk copy a warp and
+// add them from shared memory: read by plain loads, 32 columns at a time, they took 10 us and more of a product of 30.
+// partials: gridDim.x x 4 x BN / 32 x 8 x 32 float4 (block, epilogue warp, 32 columns, four of them, row); flags: 4 ints a
+// block, zero between launches.
+template <int BN, int EPI, typename TO>
+__global__ void __launch_bounds__(TG_THREADS, 1)
+gemm_tcgen05_shared_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                           TO* __restrict__ C, int64_t ldc, int M, int N, int K, float* __restrict__ partials,
+                           int* __restrict__ flags, int* __restrict__ err) {
+  constexpr int STAGES = tp_stages<BN>();
+  constexpr int B_BYTES = BN * TG_BK * 2, STAGE_BYTES = TG_A_BYTES + B_BYTES;
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
+  constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators
+  constexpr int CHUNKS = BN / 32, WARP_VECS = CHUNKS * 8 * 32;      // what an epilogue warp leaves: 32 rows x BN columns as float4
+  extern __shared__ unsigned char tg_smem_raw[];
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2], fix_bar[4];
+  __shared__ uint32_t tmem_slot;
+  unsigned char* smem = tg_smem_raw + ((1024u - (tma::smem_addr(tg_smem_raw) & 1023u)) & 1023u);
+  const int warp = tc5::uniform_warp_index(), lane = threadIdx.x & 31;
+  const int m_tiles = (M + TG_BM - 1) / TG_BM, n_tiles = (N + OUT_COLS - 1) / OUT_COLS, num_kb = (K + TG_BK - 1) / TG_BK;
+  const int tiles = m_tiles * n_tiles, G = (int)gridDim.x;
+  const int whole_rounds = tiles / G > 1 ? tiles / G - 1 : 0;                  // rounds in which a block takes a whole tile
+  const int first_shared = whole_rounds * G;                                   // the tiles from here on are shared out
+  const long long shared_total = (long long)(tiles - first_shared) * num_kb;   // their stages
+  auto begin_of = [&](int block) { return shared_total * block / (long long)G; };
+  const long long s0 = begin_of(blockIdx.x), s1 = begin_of(blockIdx.x + 1);
+  const long long whole_items = (long long)whole_rounds * num_kb, my_items = whole_items + (s1 - s0);
+  // the part of a tile that starts at this block's stage ``idx``: K blocks kb0 .. kb1 - 1 of ``tile``
+  auto segment = [&](long long idx, int& tile, int& kb0, int& kb1) {
+    if (idx < whole_items) {
+      const int round = (int)(idx / num_kb);
+      tile = round * G + (int)blockIdx.x;
+      kb0 = (int)(idx - (long long)round * num_kb);
+      kb1 = num_kb;
+    } else {
+      const long long at = s0 + (idx - whole_items);
+      const int t = (int)(at / num_kb);
+      tile = first_shared + t;
+      kb0 = (int)(at - (long long)t * num_kb);
+      kb1 = (int)(s1 - at < (long long)(num_kb - kb0) ? kb0 + (s1 - at) : num_kb);
+    }
+  };
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tma::mbar_init(&full_bar[s], 1);
+      tma::mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tma::mbar_init(&acc_full[i], 1);
+      tma::mbar_init(&acc_empty[i], 4);
+    }
+    for (int i = 0; i < 4; ++i) tma::mbar_init(&fix_bar[i], 1);
+    tma::mbar_fence_init();
+    tma::prefetch_map(&map_a);
+    tma::prefetch_map(&map_w);
+  }
+  if (warp == 1) tc5::tmem_alloc(&tmem_slot, TMEM_COLS);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // A place in this block's sequence of stages, moved on without a division inside a segment (one thread feeds the SM).
+      struct Walk { long long idx; int kb, kb1, m0, n0, s; uint32_t phase; };
+      auto enter = [&](Walk& w) {                      // the segment that starts at w.idx
+        int tile;
+        segment(w.idx, tile, w.kb, w.kb1);
+        w.m0 = (tile % m_tiles) * TG_BM;
+        w.n0 = (tile / m_tiles) * OUT_COLS;
+      };
+      auto start = [&](Walk& w) {
+        w.idx = 0;
+        w.s = 0;
+        w.phase = 0;
+        if (my_items > 0) enter(w);
+      };
+      auto step = [&](Walk& w) {
+        ++w.idx;
+        if (++w.kb == w.kb1 && w.idx < my_items) enter(w);
+        if (++w.s == STAGES) {
+          w.s = 0;
+          w.phase ^= 1;
+        }
+      };
+      auto issue_w = [&](const Walk& w) {
+        unsigned char* b_dst = smem + w.s * STAGE_BYTES + TG_A_BYTES;
+        tma::mbar_expect_tx(&full_bar[w.s], STAGE_BYTES);
+        if (EPI == 1) {
+          tma::load_2d(b_dst, &map_w, w.kb * TG_BK, w.n0, &full_bar[w.s]);
+          tma::load_2d(b_dst + B_BYTES / 2, &map_w, w.kb * TG_BK, N + w.n0, &full_bar[w.s]);
+        } else {
+          tma::load_2d(b_dst, &map_w, w.kb * TG_BK, w.n0, &full_bar[w.s]);
+        }
+      };
+      auto issue_a = [&](const Walk& w) { tma::load_2d(smem + w.s * STAGE_BYTES, &map_a, w.kb * TG_BK, w.m0, &full_bar[w.s]); };
+      // The weights are no output of the kernel before this one; the activations are.
+      const long long ahead = my_items < STAGES ? my_items : STAGES;
+      Walk ww, wa;
+      start(ww);
+      start(wa);
+      for (long long i = 0; i < ahead; ++i, step(ww)) issue_w(ww);
+      pdl_wait();
+      for (long long i = 0; i < ahead; ++i, step(wa)) issue_a(wa);
+      for (long long i = ahead; i < my_items && ok; ++i, step(ww)) {
+        ok = tma::mbar_wait(&empty_bar[ww.s], ww.phase ^ 1);      // the products of the round before have read the stage
+        if (!ok) break;
+        issue_w(ww);
+        issue_a(ww);
+      }
+    }
+  } else if (warp == 1) {
+    // all lanes run the loop, an elected one issues
+    constexpr uint32_t idesc = tc5::instr_desc_bf16(TG_BM, BN);
+    const tc5::DescWords a_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(smem));
+    const tc5::DescWords b_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(smem + TG_A_BYTES));
+    uint32_t s = 0, phase = 0;                       // the ring's stage and the parity of its round
+    int seg = 0;
+    for (long long idx = 0; idx < my_items; ++seg) {
+      int tile, kb0, kb1;
+      segment(idx, tile, kb0, kb1);
+      const int buf = seg & 1;
+      if (seg >= 2 && ok) ok = tc5::mbar_wait_warp(&acc_empty[buf], (uint32_t)(((seg >> 1) - 1) & 1));      // read out by the epilogue
+      tc5::fence_after_sync();
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (ok) ok = tc5::mbar_wait_warp(&full_bar[s], phase);
+        tc5::fence_after_sync();
+        if (ok) {
+          const uint32_t stage = (s * (uint32_t)STAGE_BYTES) >> 4;
+#pragma unroll
+          for (int k = 0; k < TG_BK / 16; ++k)       // 32 bytes further along K per step: +2 in units of 16 bytes
+            tc5::mma_f16_elect(tmem + buf * BN, a_desc, stage + 2 * k, b_desc, stage + 2 * k, idesc, kb > kb0 || k > 0);
+        }
+        tc5::commit_elect(&empty_bar[s]);            // the stage is free once these MMAs have read it
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+      tc5::commit_elect(&acc_full[buf]);             // the segment's sums are complete
+      idx += kb1 - kb0;
+    }
+  } else {
+    // Epilogue: warp w reads lanes 32 (w % 4) .. +31 of tensor memory; a lane is a row of the tile.
+    const int quad = warp & 3, lane_base = quad * 32, row = lane_base + lane;
+    int seg = 0;
+    for (long long idx = 0; idx < my_items; ++seg) {
+      int tile, kb0, kb1;
+      segment(idx, tile, kb0, kb1);
+      idx += kb1 - kb0;
+      const int buf = seg & 1;
+      const int m0 = (tile % m_tiles) * TG_BM, n0 = (tile / m_tiles) * OUT_COLS;
+      const int m = m0 + row;
+      if (ok) ok = tma::mbar_wait(&acc_full[buf], (uint32_t)((seg >> 1) & 1));
+      tc5::fence_after_sync();
+      const uint32_t acc = tmem + ((uint32_t)lane_base << 16) + buf * BN;
+      if (kb0 > 0) {
+        // the tile's beginning is another block's: leave the sums for it
+        if (ok) {
+          float4* dst = reinterpret_cast<float4*>(partials) + ((size_t)blockIdx.x * 4 + quad) * WARP_VECS + lane;
+#pragma unroll 1
+          for (int c = 0; c < CHUNKS; ++c) {
+            float v[32];
+            tc5::ld_32cols(acc + c * 32, v);
+            tc5::wait_ld();
+#pragma unroll
+            for (int q = 0; q < 8; ++q) dst[(c * 8 + q) * 32] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          }
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(flags + blockIdx.x * 4 + quad), "r"(1) : "memory");
+        }
+      } else {
+        // the blocks after this one that hold the rest of the tile (none if it ends here)
+        int c_end = blockIdx.x + 1;
+        if (kb1 < num_kb)
+          while (c_end < G && begin_of(c_end) < (long long)(tile - first_shared + 1) * num_kb) ++c_end;
+        // This is the block's last segment and its products are over: the ring of stages is idle, and this warp's quarter
+        // of its first 128 KB is where the contributors' sums of the warp's 32 rows land, one contributor at a time.
+        const float4* land = reinterpret_cast<const float4*>(smem + quad * (WARP_VECS * 16)) + lane;
+        int landed = 0;                                      // copies this warp has waited for
+        auto bring = [&](int cc) {                           // wait for block cc's sums, copy them in, wait for the copy
+          const int* f = flags + cc * 4 + quad;
+          bool there = false;
+          for (unsigned i = 0; i < (1u << 21) && !there; ++i) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(f) : "memory");
+            there = v != 0;
+            if (!there) __nanosleep(64);
+          }
+          ok = __all_sync(0xffffffffu, there);
+          if (!ok) return;
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // (this warp's loads of the copy before are over)
+          __syncwarp();
+          if (lane == 0) {
+            tma::mbar_expect_tx(&fix_bar[quad], WARP_VECS * 16);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                         ::"r"(tma::smem_addr(smem + quad * (WARP_VECS * 16))),
+                           "l"(reinterpret_cast<const float4*>(partials) + ((size_t)cc * 4 + quad) * WARP_VECS), "r"(WARP_VECS * 16),
+                           "r"(tma::smem_addr(&fix_bar[quad])) : "memory");
+          }
+          ok = __all_sync(0xffffffffu, tma::mbar_wait(&fix_bar[quad], landed & 1));
+          ++landed;
+        };
+        auto add_landed = [&](int chunk, float (&v)[32]) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 t = land[(chunk * 8 + q) * 32];
+            v[q * 4] += t.x;
+            v[q * 4 + 1] += t.y;
+            v[q * 4 + 2] += t.z;
+            v[q * 4 + 3] += t.w;
+          }
+        };
+        // all contributors but the last are added into tensor memory, in their order; the last one on the way out
+        for (int cc = blockIdx.x + 1; cc + 1 < c_end && ok; ++cc) {
+          bring(cc);
+          if (!ok) break;
+#pragma unroll 1
+          for (int c = 0; c < CHUNKS; ++c) {
+            float v[32];
+            tc5::ld_32cols(acc + c * 32, v);
+            tc5::wait_ld();
+            add_landed(c, v);
+            tc5::st_32cols(acc + c * 32, v);
+          }
+          tc5::wait_st();
+        }
+        const bool last = c_end > (int)blockIdx.x + 1;
+        if (last && ok) bring(c_end - 1);
+        // 32 columns (from ``col`` on) of this thread's row
+        auto sums = [&](int col, float (&v)[32]) {
+          tc5::ld_32cols(acc + col, v);
+          tc5::wait_ld();
+          if (last) add_landed(col / 32, v);
+        };
+        const bool vec = (ldc * sizeof(TO)) % 16 == 0 && (n0 * sizeof(TO)) % 16 == 0 && ((uintptr_t)C & 15) == 0;
+        if (ok) {
+          if (EPI == 1) {
+#pragma unroll 1
+            for (int c = 0; c < OUT_COLS; c += 32) {
+              float g[32], u[32];
+              sums(c, g);
+              sums(OUT_COLS + c, u);
+              if (m < M && n0 + c < N) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
+                store_row32(C + (int64_t)m * ldc + n0 + c, g, N - n0 - c, vec);
+              }
+            }
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < OUT_COLS; c += 32) {
+              float v[32];
+              sums(c, v);
+              if (m < M && n0 + c < N) store_row32(C + (int64_t)m * ldc + n0 + c, v, N - n0 - c, vec);
+            }
+          }
+          __syncwarp();
+          if (lane == 0)
+            for (int cc = blockIdx.x + 1; cc < c_end; ++cc) flags[cc * 4 + quad] = 0;      // zero again for the next launch
+        }
+      }
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tma::smem_addr(&acc_empty[buf])) : "memory");
+    }
+  }
+  if (!ok) atomicOr(err + 1, 1);
+  pdl_launch_dependents();
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tc5::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+template <int BN, int EPI, typename TO>
+int launch_ts(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, float* partials, int* flags, int* err,
+              cudaStream_t stream) {
+  const size_t smem = (size_t)tp_stages<BN>() * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_shared_kernel<BN, EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ME_REQUIRE(e == cudaSuccess, "me_gemm_tcgen05: cannot raise shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
+  const long long tiles = (long long)((N + OUT_COLS - 1) / OUT_COLS) * ((M + TG_BM - 1) / TG_BM);
+  ME_REQUIRE(tiles < (1ll << 30), "me_gemm_tcgen05: too many tiles");
+  const long long total = tiles * ((K + TG_BK - 1) / TG_BK);
+  const int blocks = (int)(total < me_sm_count() ? total : me_sm_count());
+  me_launch(gemm_tcgen05_shared_kernel<BN, EPI, TO>, dim3(blocks), dim3(TG_THREADS), smem, stream,
+            *reinterpret_cast<const CUtensorMap*>(map_a), *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, partials,
+            flags, err);
+  return 0;
+}
+
 template <int BN, int EPI, typename TO>
 int launch_tp(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, int* err, cudaStream_t stream) {
   const size_t smem = (size_t)tp_stages<BN>() * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
@@ -402,6 +722,33 @@ ME_API int me_gemm_tcgen05_persistent(const void* map_a, const void* map_w, void
 #undef ME_TP_CASE
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_gemm_tcgen05_persistent");
+  return 0;
+}
+
+// The form that shares the work out evenly over the SMs (same operands as the persistent form): ``partials`` has room for
+// me_gemm_tcgen05_shared_partial_floats() floats, ``flags`` for me_gemm_tcgen05_shared_flag_ints() ints that are zero
+// between launches (the kernel leaves them so unless a bounded wait runs out).  Launches that share them must not overlap.
+ME_API int me_gemm_tcgen05_shared_partial_floats() { return me_sm_count() * 256 * 128; }
+ME_API int me_gemm_tcgen05_shared_flag_ints() { return 4 * me_sm_count(); }
+ME_API int me_gemm_tcgen05_shared(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, int M, int N,
+                                  int K, int epi, int bn, float* partials, int* flags, int* err, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  ME_REQUIRE(M > 0 && N > 0 && K > 0 && K % 8 == 0, "me_gemm_tcgen05_shared: bad sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
+  ME_REQUIRE(map_a != nullptr && map_w != nullptr && err != nullptr && partials != nullptr && flags != nullptr,
+             "me_gemm_tcgen05_shared: tensor maps, work buffers and the error word are required");
+  ME_REQUIRE(epi == 0 || (epi == 1 && c_dtype == ME_BF16), "me_gemm_tcgen05_shared: epilogue %d", epi);
+  ME_REQUIRE(bn == 128 || bn == 256, "me_gemm_tcgen05_shared: tile width %d is not 128 or 256", bn);
+  int rc = 1;
+#define ME_TS_CASE(BN_)                                                                                                    \
+  if (bn == BN_) {                                                                                                         \
+    if (epi == 1) rc = launch_ts<BN_, 1, bf16>(map_a, map_w, C, ldc, M, N, K, partials, flags, err, stream);              \
+    else if (c_dtype == ME_BF16) rc = launch_ts<BN_, 0, bf16>(map_a, map_w, C, ldc, M, N, K, partials, flags, err, stream); \
+    else rc = launch_ts<BN_, 0, float>(map_a, map_w, C, ldc, M, N, K, partials, flags, err, stream);                      \
+  }
+  ME_TS_CASE(128) ME_TS_CASE(256)
+#undef ME_TS_CASE
+  if (rc) return rc;
+  ME_LAUNCH_CHECK("me_gemm_tcgen05_shared");
   return 0;
 }
 

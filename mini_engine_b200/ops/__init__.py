@@ -35,6 +35,7 @@ _PROTOS = {
     "me_gemm_stream": [_I, _P, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _L, _P, _P],
     "me_gemm_tcgen05_persistent": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
+    "me_gemm_tcgen05_shared": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -364,11 +365,24 @@ def _stream_work_buffers(device) -> tuple[torch.Tensor, torch.Tensor]:
     return ws
 
 
+_shared_ws: dict = {}
+
+
+def _tcgen05_shared_buffers(device) -> tuple[torch.Tensor, torch.Tensor]:
+    """The same for the work-sharing form of csrc/gemm_tcgen05.cu: a 128 x 256 tile of float32 sums a block, four flags a block."""
+    ws = _shared_ws.get(device)
+    if ws is None:
+        lib = _lib or require_extension()
+        ws = _shared_ws[device] = (torch.empty(lib.me_gemm_tcgen05_shared_partial_floats(), dtype=torch.float32, device=device),
+                                   torch.zeros(lib.me_gemm_tcgen05_shared_flag_ints(), dtype=torch.int32, device=device))
+    return ws
+
+
 def reset_stream_work_buffers() -> None:
-    """Clear the flags of csrc/gemm_stream.cu's work buffers.  Every launch leaves them zero, except one whose bounded
-    wait ran out (flag 1 of the error word): the caller that reports that error calls this, so that a later launch does
-    not take a stale flag for a neighbour's finished sums."""
-    for _, flags in _stream_ws.values():
+    """Clear the flags of the work buffers of csrc/gemm_stream.cu and of the work-sharing tcgen05 product.  Every launch
+    leaves them zero, except one whose bounded wait ran out (flag 1 of the error word): the caller that reports that
+    error calls this, so that a later launch does not take a stale flag for a neighbour's finished sums."""
+    for _, flags in list(_stream_ws.values()) + list(_shared_ws.values()):
         flags.zero_()
 
 
@@ -474,14 +488,46 @@ def tcgen05_persistent_pays(M: int, N: int, K: int, epi: int) -> bool:
     return tiles >= 2 * sm_count() or (K <= 1024 and 10 * tiles >= 17 * sm_count())
 
 
+tcgen05_share = "auto"          # the work-sharing form of the tcgen05 product: "auto" or False (for comparisons)
+
+
+def tcgen05_share_pays(M: int, N: int, K: int, epi: int) -> bool:
+    """Whether a product of M rows and N output columns runs the work-sharing form of the tcgen05 kernel (the last
+    rounds' stages cut into one equal range an SM, partial sums added by the tile's owner).  It pays where whole tiles
+    leave SMs idle: a last round that is less than half full (1.1 or 2.2 tiles of 128 x 256 an SM: q|k|v of 1,024 rows at
+    the 8B sizes 52 against 66 us, o_proj of 1,024 rows at the 32B sizes 79 against 124), or fewer tiles than SMs with a
+    long K (q|k|v of 256 rows at the 32B sizes 55 against 75 us).  It does not pay with the SiLU epilogue (many tiles
+    anyway), nor where the blocks that share a tile of W, now at different places along K, push each other's part of it
+    out of L2 (down_proj of 1,024 rows at the 8B sizes: 124 against 90 us), hence the bound on the operands' bytes."""
+    if epi:
+        return False
+    sms = sm_count()
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    if tiles >= sms:
+        rounds = -(-tiles // sms)
+        return tiles <= 0.75 * rounds * sms and (M + N) * K * 2 <= 96 << 20
+    return 5 * tiles >= sms and K >= 5120
+
+
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str, err: torch.Tensor,
-                   tile_n: Optional[int] = None, splits: int = 1, persistent: Optional[bool] = None) -> None:
+                   tile_n: Optional[int] = None, splits: int = 1, persistent: Optional[bool] = None,
+                   share: Optional[bool] = None) -> None:
     """The tcgen05 product of csrc/gemm_tcgen05.cu: TMA -> swizzled shared memory -> tcgen05.mma -> tensor memory.
 
-    With ``splits`` > 1 ``out`` is float32 [tcgen05_splits(K, splits), M, N]: partial results over parts of K."""
+    With ``splits`` > 1 ``out`` is float32 [tcgen05_splits(K, splits), M, N]: partial results over parts of K.
+    ``share``: the form that cuts the stages of all tiles into one equal range an SM (``tile_n`` 128 or 256)."""
     M, K = x.shape
     epi = {"none": 0, "silu_mul": 1}[epilogue]
     N = weight.shape[0] // 2 if epi else weight.shape[0]
+    if share is None and tile_n is None and persistent is None and splits == 1 and tcgen05_share == "auto" and tcgen05_takes(x, weight):
+        share = tcgen05_share_pays(M, N, K, epi)
+    if share:
+        bn = tile_n or 256
+        _need(tcgen05_takes(x, weight) and splits == 1 and bn in (128, 256), "linear_tcgen05: operands not taken by the work-sharing form")
+        partials, flags = _tcgen05_shared_buffers(x.device)
+        _call("me_gemm_tcgen05_shared", matrix_tensor_map(x, 128).ptr, matrix_tensor_map(weight, bn // 2 if epi else bn).ptr,
+              out.data_ptr(), _dt(out), out.stride(0), M, N, K, epi, bn, partials.data_ptr(), flags.data_ptr(), err.data_ptr(), _stream())
+        return
     if tile_n is None:
         # The widest accumulator that still leaves enough tiles: about two an SM where a tile is short (K up to 3,072),
         # one for every other SM where it is long (measured at the 8B and 32B sizes: with 512 rows the 256-wide tile is a

@@ -219,6 +219,38 @@ def test_tcgen05_products(ops, M, N, K, tile_n, persistent):
         close(out, ref, torch.bfloat16, scale=4)
 
 
+@pytest.mark.parametrize("M, N, K", [(128, 256, 64), (129, 200, 136), (300, 4096, 1024), (256, 512, 8192), (1000, 1032, 3072),
+                                     (2048, 5000, 520), (3000, 9000, 264), (40000, 256, 64)])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_tcgen05_products_with_the_work_shared_out_evenly(ops, M, N, K, tile_n):
+    # the stages of the last rounds' tiles cut into one range an SM: a tile shared by two blocks and by six, tiles that
+    # no block shares, fewer stages than SMs, a block with whole tiles before its share, edges in M, N and K; twice, so that
+    # the second run finds the flags as the first left them
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    for od in (torch.bfloat16, torch.float32, torch.bfloat16):
+        out, ref = torch.full((M, N), float("nan"), dtype=od, device=DEV), torch.empty(M, N, dtype=od, device=DEV)
+        ops.linear_tcgen05(x, w, out, "none", err, tile_n=tile_n, share=True)
+        plain_ops.linear(x, w, ref)
+        assert err.tolist() == [0, 0, 0, 0]
+        close(out, ref, od, scale=4)
+    I = N // 2
+    out, ref = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV), torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    ops.linear_tcgen05(x, w, out, "silu_mul", err, tile_n=tile_n, share=True)
+    plain_ops.linear(x, w, ref, epilogue="silu_mul")
+    assert err.tolist() == [0, 0, 0, 0]
+    close(out, ref, torch.bfloat16, scale=4)
+    assert all(int(f.sum()) == 0 for _, f in ops._shared_ws.values())
+
+
+def test_which_tcgen05_products_share_their_work(ops):
+    sms = ops.sm_count()
+    assert ops.tcgen05_share_pays(1024, 6144, 4096, 0) == (sms == 148)          # 192 tiles: a second round a third full
+    assert not ops.tcgen05_share_pays(1024, 6144, 4096, 1)                      # never with the SiLU epilogue
+    assert not ops.tcgen05_share_pays(8192, 6144, 4096, 0)                      # 1,536 tiles: the last round hardly matters
+    assert not ops.tcgen05_share_pays(256, 4096, 1024, 0)                       # few tiles, short K: nothing to share
+
+
 @pytest.fixture
 def decode_kernel(ops, request):
     """Which of the two decode product kernels ``ops.decode_linear`` runs: one block over all of K (csrc/gemm_decode.cu)
