@@ -504,8 +504,9 @@ def tcgen05_share_pays(M: int, N: int, K: int, epi: int) -> bool:
     sms = sm_count()
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     if tiles >= sms:
+        # (K: handing a tile's sums over costs 3 to 5 us, a tile of K = 1,024 takes 5: at the 0.6B sizes it never paid)
         rounds = -(-tiles // sms)
-        return tiles <= 0.75 * rounds * sms and (M + N) * K * 2 <= 96 << 20
+        return K >= 4096 and tiles <= 0.75 * rounds * sms and (M + N) * K * 2 <= 96 << 20
     return 5 * tiles >= sms and K >= 5120
 
 

@@ -249,6 +249,7 @@ def test_which_tcgen05_products_share_their_work(ops):
     assert not ops.tcgen05_share_pays(1024, 6144, 4096, 1)                      # never with the SiLU epilogue
     assert not ops.tcgen05_share_pays(8192, 6144, 4096, 0)                      # 1,536 tiles: the last round hardly matters
     assert not ops.tcgen05_share_pays(256, 4096, 1024, 0)                       # few tiles, short K: nothing to share
+    assert not ops.tcgen05_share_pays(1280, 4096, 1024, 0)                      # a short K: handing sums over costs what a tile takes
 
 
 @pytest.fixture
