@@ -68,9 +68,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   const int G = nh / nkv, packs = G / gp, tq = TA_ROWS / gp;
   // grid.x runs over the head packs and grid.y over the query tiles from the last to the first, so blocks are
   // handed out with the most keys first across all heads.
-  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int tile = gridDim.y - 1 - blockIdx.y;
   const int b = tiles[2 * tile], q0 = tiles[2 * tile + 1];
-  const int kvh = blockIdx.y / packs, head0 = kvh * G + (blockIdx.y % packs) * gp;
+  const int kvh = blockIdx.x / packs, head0 = kvh * G + (blockIdx.x % packs) * gp;
   const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0;
   const int L = context_lens[b], start = L - q_len;
   const int n_tok = min(tq, q_len - q0);
@@ -388,9 +388,9 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
   const int warp = tc5::uniform_warp_index(), lane = threadIdx.x & 31;
 
   const int G = nh / nkv, packs = G / gp, tq = TA_ROWS / gp;
-  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int tile = gridDim.y - 1 - blockIdx.y;
   const int b = tiles[2 * tile], q0 = tiles[2 * tile + 1];
-  const int kvh = blockIdx.y / packs, head0 = kvh * G + (blockIdx.y % packs) * gp;
+  const int kvh = blockIdx.x / packs, head0 = kvh * G + (blockIdx.x % packs) * gp;
   const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0;
   const int L = context_lens[b], start = L - q_len;
   const int n_tok = min(tq, q_len - q0);
@@ -732,10 +732,10 @@ int launch_ta(const void* q_map, const void* kv_map, void* out, int64_t out_row_
     ME_REQUIRE(e == cudaSuccess, "me_attn_prefill_tcgen05: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  // Tiles fastest, heads slowest: the blocks that run at one time then read the keys and values of one or two heads, which
-  // stay in L2 however long the context (with heads fastest, eight heads' keys of a 16,384-token prompt are 67 MB a layer;
-  // at that length the two orders measured the same, 49.9 and 50.2 ms a prefill).
-  dim3 grid(num_tiles, nkv * (nh / nkv / gp));
+  // Heads fastest, tiles (the ones with the most keys first) slowest: the long tiles of all heads start in the first round.
+  // (Tiles fastest, so that the blocks of a round share one or two heads' keys in L2, measured the same at 16,384 tokens
+  // and 16% slower at 2,048, where the last round then holds long tiles.)
+  dim3 grid(nkv * (nh / nkv / gp), num_tiles);
   me_launch(kernel, grid, dim3(TA_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(q_map),
             *reinterpret_cast<const CUtensorMap*>(kv_map), (bf16*)out, out_row_stride, block_tables, bt_stride, cu_seqlens,
             context_lens, tiles, nh, nkv, gp, page_size, scale * 1.4426950408889634f, window, err);
