@@ -5,8 +5,8 @@
 //
 // One block computes a 128 x BN tile.  Warp 0: one thread streams A and W tiles of 64 K-elements
 // through a ring of shared-memory stages by TMA (128-byte swizzle, zero fill at the edges).
-// Warp 1: allocates BN columns of tensor memory; one thread issues tcgen05.mma (M 128, N BN, K 16,
-// four per stage) and hands stages back through tcgen05.commit.  Warps 2..5: when the accumulator is
+// Warp 1: allocates BN columns of tensor memory; all its lanes run the loop and an elected lane issues
+// tcgen05.mma (M 128, N BN, K 16, four per stage) and hands stages back through tcgen05.commit.  Warps 2..5: when the accumulator is
 // complete, each thread reads its row from tensor memory (tcgen05.ld), applies the epilogue and writes
 // it.  Every wait is bounded; a wait that gives up sets flag 1 of ``err`` and the block still frees its
 // tensor memory and exits.
