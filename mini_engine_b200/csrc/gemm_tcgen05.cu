@@ -55,6 +55,97 @@ __device__ __forceinline__ void store_row32(float* dst, const float (&v)[32], in
   }
 }
 
+// The epilogue of one warp: its 32 rows of a tile (a lane a row) go out OUT_COLS columns wide.  ``load(col, v)`` asks for 32
+// accumulator columns of the lane's row from ``col`` on (tcgen05.ld, not waited for), ``fix(col, v)`` is applied to them once
+// they are there (the work-sharing form adds the other blocks' sums).  A thread holds a row, so stores straight from the
+// registers would touch 32 different lines each (270 clocks a store instruction, 9,800 a 128 x 256 tile: as long as the
+// tile's products at K = 1,024); the results go through ``stage`` (4 KB of shared memory of the warp's own, 128-byte
+// aligned) in groups of 128 bytes a row, swizzled by 16-byte pieces, and leave with whole lines: a store instruction
+// writes four rows' 128 bytes.  Without 16-byte alignment of the rows of C (``vec`` false) they leave one by one.
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+template <int EPI, typename TO, int OUT_COLS, typename Load, typename Fix>
+__device__ __forceinline__ void write_rows(Load&& load, Fix&& fix, unsigned char* stage, TO* __restrict__ C, int64_t ldc, int M, int N,
+                                           int m0, int n0, int lane_base, int lane, bool vec) {
+  const int m = m0 + lane_base + lane;
+  // 32 results of the lane's row from output column ``c`` on
+  auto results = [&](int c, float (&g)[32]) {
+    if (EPI == 1) {
+      float u[32];
+      load(c, g);
+      load(OUT_COLS + c, u);
+      tc5::wait_ld();
+      fix(c, g);
+      fix(OUT_COLS + c, u);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) g[j] = silu_mul(g[j], u[j]);
+    } else {
+      load(c, g);
+      tc5::wait_ld();
+      fix(c, g);
+    }
+  };
+  if (!vec) {
+#pragma unroll 1
+    for (int c = 0; c < OUT_COLS; c += 32) {
+      float g[32];
+      results(c, g);
+      if (m < M && n0 + c < N) store_row32(C + (int64_t)m * ldc + n0 + c, g, N - n0 - c, false);
+    }
+    return;
+  }
+  constexpr int GROUP = 128 / (int)sizeof(TO), PER = 16 / (int)sizeof(TO);       // columns a 128-byte group, a 16-byte piece
+  const int rows_left = M - (m0 + lane_base);
+#pragma unroll 1
+  for (int c = 0; c < OUT_COLS; c += GROUP) {
+    uint4 pk[8];
+#pragma unroll
+    for (int h = 0; h < GROUP / 32; ++h) {
+      if (c + 32 * h < OUT_COLS) {                           // (a tile of 32 output columns is half a group of bfloat16)
+        float g[32];
+        results(c + 32 * h, g);
+        if (sizeof(TO) == 2) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk[h * 4 + q]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(g[q * 8 + 2 * j], g[q * 8 + 2 * j + 1]);
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) pk[q] = make_uint4(__float_as_uint(g[q * 4]), __float_as_uint(g[q * 4 + 1]), __float_as_uint(g[q * 4 + 2]),
+                                                         __float_as_uint(g[q * 4 + 3]));
+        }
+      }
+    }
+    const int cols_left = min(N - n0, OUT_COLS) - c;         // columns of this group that are the tile's and the product's
+    if (rows_left > 0 && cols_left > 0) {                    // (the same in all lanes)
+#pragma unroll
+      for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(stage + lane * 128 + ((q ^ (lane & 7)) << 4)) = pk[q];
+      __syncwarp();
+      const int piece = lane & 7;
+      TO* dst0 = C + (int64_t)(m0 + lane_base) * ldc + n0 + c + piece * PER;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = i * 4 + (lane >> 3);
+        if (row < rows_left && piece * PER < cols_left) {
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 128 + ((piece ^ (row & 7)) << 4));
+          TO* dst = dst0 + (int64_t)row * ldc;
+          if (piece * PER + PER <= cols_left) {
+            *reinterpret_cast<uint4*>(dst) = v;
+          } else {
+            const TO* e = reinterpret_cast<const TO*>(&v);
+#pragma unroll
+            for (int j = 0; j < PER; ++j)
+              if (j < cols_left - piece * PER) dst[j] = e[j];
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
 // gridDim.z blocks share a tile: block z takes ``kb_per_split`` blocks of 64 along K from z * kb_per_split on and writes
 // its partial result ``split_stride`` elements after the one before (float32 results that the next kernel adds).
 template <int BN, int EPI, typename TO, bool DEEP>
@@ -142,31 +233,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     ok = tma::mbar_wait(&done_bar, 0);
     tc5::fence_after_sync();
     const int lane_base = (warp & 3) * 32;
-    const int m = m0 + lane_base + lane;
     const bool vec = (ldc * sizeof(TO)) % 16 == 0 && (n0 * sizeof(TO)) % 16 == 0 && ((uintptr_t)C & 15) == 0;
     if (ok) {
-      if (EPI == 1) {
-#pragma unroll 1
-        for (int c = 0; c < OUT_COLS; c += 32) {
-          float g[32], u[32];
-          tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + c, g);
-          tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + OUT_COLS + c, u);
-          tc5::wait_ld();
-          if (m < M && n0 + c < N) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
-            store_row32(C + (int64_t)m * ldc + n0 + c, g, N - n0 - c, vec);
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < OUT_COLS; c += 32) {
-          float v[32];
-          tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + c, v);
-          tc5::wait_ld();
-          if (m < M && n0 + c < N) store_row32(C + (int64_t)m * ldc + n0 + c, v, N - n0 - c, vec);
-        }
-      }
+      // every product is over and every load has been read: the ring's first 16 KB are the four warps' staging rows
+      auto load = [&](int col, float (&v)[32]) { tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + col, v); };
+      auto fix = [](int, float (&)[32]) {};
+      write_rows<EPI, TO, OUT_COLS>(load, fix, smem + (warp & 3) * 4096, C, ldc, M, N, m0, n0, lane_base, lane, vec);
     }
   }
   if (!ok) atomicOr(err + 1, 1);
@@ -323,34 +395,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     for (int i = 0; i < my_tiles; ++i) {
       const int tile = blockIdx.x + i * gridDim.x, buf = i & 1;
       const int m0 = (tile % m_tiles) * TG_BM, n0 = (tile / m_tiles) * OUT_COLS;
-      const int m = m0 + lane_base + lane;
       if (ok) ok = tma::mbar_wait(&acc_full[buf], (uint32_t)((i >> 1) & 1));
       tc5::fence_after_sync();
       const uint32_t acc = tmem + ((uint32_t)lane_base << 16) + buf * BN;
       const bool vec = (ldc * sizeof(TO)) % 16 == 0 && (n0 * sizeof(TO)) % 16 == 0 && ((uintptr_t)C & 15) == 0;
       if (ok) {
-        if (EPI == 1) {
-#pragma unroll 1
-          for (int c = 0; c < OUT_COLS; c += 32) {
-            float g[32], u[32];
-            tc5::ld_32cols(acc + c, g);
-            tc5::ld_32cols(acc + OUT_COLS + c, u);
-            tc5::wait_ld();
-            if (m < M && n0 + c < N) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
-              store_row32(C + (int64_t)m * ldc + n0 + c, g, N - n0 - c, vec);
-            }
-          }
-        } else {
-#pragma unroll 1
-          for (int c = 0; c < OUT_COLS; c += 32) {
-            float v[32];
-            tc5::ld_32cols(acc + c, v);
-            tc5::wait_ld();
-            if (m < M && n0 + c < N) store_row32(C + (int64_t)m * ldc + n0 + c, v, N - n0 - c, vec);
-          }
-        }
+        auto load = [&](int col, float (&v)[32]) { tc5::ld_32cols(acc + col, v); };
+        auto fix = [](int, float (&)[32]) {};
+        write_rows<EPI, TO, OUT_COLS>(load, fix, smem + STAGES * STAGE_BYTES + (warp & 3) * 4096, C, ldc, M, N, m0, n0, lane_base, lane, vec);
       }
       tc5::fence_before_sync();
       __syncwarp();
@@ -521,7 +573,7 @@ gemm_tcgen05_shared_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     }
   } else {
     // Epilogue: warp w reads lanes 32 (w % 4) .. +31 of tensor memory; a lane is a row of the tile.
-    const int quad = warp & 3, lane_base = quad * 32, row = lane_base + lane;
+    const int quad = warp & 3, lane_base = quad * 32;
     int seg = 0;
     for (long long idx = 0; idx < my_items; ++seg) {
       int tile, kb0, kb1;
@@ -529,7 +581,6 @@ gemm_tcgen05_shared_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
       idx += kb1 - kb0;
       const int buf = seg & 1;
       const int m0 = (tile % m_tiles) * TG_BM, n0 = (tile / m_tiles) * OUT_COLS;
-      const int m = m0 + row;
       if (ok) ok = tma::mbar_wait(&acc_full[buf], (uint32_t)((seg >> 1) & 1));
       tc5::fence_after_sync();
       const uint32_t acc = tmem + ((uint32_t)lane_base << 16) + buf * BN;
@@ -607,34 +658,14 @@ gemm_tcgen05_shared_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         }
         const bool last = c_end > (int)blockIdx.x + 1;
         if (last && ok) bring(c_end - 1);
-        // 32 columns (from ``col`` on) of this thread's row
-        auto sums = [&](int col, float (&v)[32]) {
-          tc5::ld_32cols(acc + col, v);
-          tc5::wait_ld();
+        auto load = [&](int col, float (&v)[32]) { tc5::ld_32cols(acc + col, v); };
+        auto fix = [&](int col, float (&v)[32]) {
           if (last) add_landed(col / 32, v);
         };
         const bool vec = (ldc * sizeof(TO)) % 16 == 0 && (n0 * sizeof(TO)) % 16 == 0 && ((uintptr_t)C & 15) == 0;
         if (ok) {
-          if (EPI == 1) {
-#pragma unroll 1
-            for (int c = 0; c < OUT_COLS; c += 32) {
-              float g[32], u[32];
-              sums(c, g);
-              sums(OUT_COLS + c, u);
-              if (m < M && n0 + c < N) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
-                store_row32(C + (int64_t)m * ldc + n0 + c, g, N - n0 - c, vec);
-              }
-            }
-          } else {
-#pragma unroll 1
-            for (int c = 0; c < OUT_COLS; c += 32) {
-              float v[32];
-              sums(c, v);
-              if (m < M && n0 + c < N) store_row32(C + (int64_t)m * ldc + n0 + c, v, N - n0 - c, vec);
-            }
-          }
+          // (the staging rows lie behind the ring: the last contributor's sums are still being read from the ring itself)
+          write_rows<EPI, TO, OUT_COLS>(load, fix, smem + STAGES * STAGE_BYTES + quad * 4096, C, ldc, M, N, m0, n0, lane_base, lane, vec);
           __syncwarp();
           if (lane == 0)
             for (int cc = blockIdx.x + 1; cc < c_end; ++cc) flags[cc * 4 + quad] = 0;      // zero again for the next launch
@@ -655,7 +686,7 @@ gemm_tcgen05_shared_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
 template <int BN, int EPI, typename TO>
 int launch_ts(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, float* partials, int* flags, int* err,
               cudaStream_t stream) {
-  const size_t smem = (size_t)tp_stages<BN>() * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
+  const size_t smem = (size_t)tp_stages<BN>() * (TG_A_BYTES + BN * TG_BK * 2) + 4 * 4096 + 1024;      // the ring, the epilogue warps' staging rows
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_shared_kernel<BN, EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -675,7 +706,7 @@ int launch_ts(const void* map_a, const void* map_w, void* C, int64_t ldc, int M,
 
 template <int BN, int EPI, typename TO>
 int launch_tp(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, int* err, cudaStream_t stream) {
-  const size_t smem = (size_t)tp_stages<BN>() * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
+  const size_t smem = (size_t)tp_stages<BN>() * (TG_A_BYTES + BN * TG_BK * 2) + 4 * 4096 + 1024;      // the ring, the epilogue warps' staging rows
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
