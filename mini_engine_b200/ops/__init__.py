@@ -510,6 +510,16 @@ def tcgen05_share_pays(M: int, N: int, K: int, epi: int) -> bool:
     return 5 * tiles >= sms and K >= 5120
 
 
+def tcgen05_one_round_width(M: int, N: int) -> int:
+    """The tile width (256 or 128) at which a product of M rows and N columns has about one tile an SM, or 0."""
+    sms, m_tiles = sm_count(), (M + 127) // 128
+    if 0.85 * sms <= m_tiles * ((N + 255) // 256) <= sms:
+        return 256
+    if 0.8 * sms <= m_tiles * ((N + 127) // 128) < 2 * sms:
+        return 128
+    return 0
+
+
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str, err: torch.Tensor,
                    tile_n: Optional[int] = None, splits: int = 1, persistent: Optional[bool] = None,
                    share: Optional[bool] = None) -> None:
@@ -538,6 +548,12 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epi
         m_tiles = (M + 127) // 128
         if persistent is None and tcgen05_persistent == "auto" and splits == 1 and tcgen05_persistent_pays(M, N, K, epi):
             tile_n, persistent = 256, True
+        elif persistent is None and tcgen05_persistent == "auto" and splits == 1 and not epi and K <= 3072 and (
+                tcgen05_one_round_width(M, N)):
+            # about one tile an SM and a short K (o_proj and down_proj of 2,048 and 4,096 rows at the 0.6B sizes): a block that
+            # has the SM to itself, with the persistent form's deeper ring, beats two blocks an SM on narrower tiles (10.0 and
+            # 13.2 us against 11.4 and 15.3 at 2,048 rows, 14.6 and 19.2 against 15.1 and 21.0 at 4,096)
+            tile_n, persistent = tcgen05_one_round_width(M, N), True
         elif epi:
             tile_n = 256 if (M >= 4096 or K >= 4096) and m_tiles * ((N + 127) // 128) <= 10000 else 128
         else:

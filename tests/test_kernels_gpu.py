@@ -252,6 +252,14 @@ def test_which_tcgen05_products_share_their_work(ops):
     assert not ops.tcgen05_share_pays(1280, 4096, 1024, 0)                      # a short K: handing sums over costs what a tile takes
 
 
+def test_which_tcgen05_products_get_a_block_an_sm_for_one_round(ops):
+    if ops.sm_count() != 148:
+        pytest.skip("the rule's examples are for 148 SMs")
+    assert ops.tcgen05_one_round_width(2048, 1024) == 128          # 16 x 8 tiles of 128 columns
+    assert ops.tcgen05_one_round_width(4096, 1024) == 256          # 32 x 4 tiles of 256 columns
+    assert ops.tcgen05_one_round_width(512, 1024) == 0             # a third of the SMs either way
+
+
 @pytest.fixture
 def decode_kernel(ops, request):
     """Which of the two decode product kernels ``ops.decode_linear`` runs: one block over all of K (csrc/gemm_decode.cu)
