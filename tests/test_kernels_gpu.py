@@ -197,11 +197,12 @@ def test_small_batch_products(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M, N, K", [(128, 64, 64), (128, 128, 64), (129, 200, 136), (300, 4096, 1024), (2048, 1024, 2048),
-                                     (1000, 1032, 3072), (64, 151936 // 16, 1024), (3000, 9000, 264)])
+                                     (1000, 1032, 3072), (64, 151936 // 16, 1024), (3000, 9000, 264), (300, 1002, 264)])
 @pytest.mark.parametrize("tile_n, persistent", [(64, False), (128, False), (256, False), (128, True), (256, True)])
 def test_tcgen05_products(ops, M, N, K, tile_n, persistent):
     # the tcgen05 kernels by name: every tile width, edges in M, N and K, bfloat16 and float32 results, SiLU epilogue;
-    # one tile a block, and the persistent form (a block walks tiles: none, one, or half a dozen with the last shape)
+    # one tile a block, and the persistent form (a block walks tiles: none, one, or half a dozen with the shape before the
+    # last); the last shape's rows of results are not 16-byte aligned and leave element by element
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5)
     err = torch.zeros(4, dtype=torch.int32, device=DEV)
     for od in (torch.bfloat16, torch.float32):
@@ -220,7 +221,7 @@ def test_tcgen05_products(ops, M, N, K, tile_n, persistent):
 
 
 @pytest.mark.parametrize("M, N, K", [(128, 256, 64), (129, 200, 136), (300, 4096, 1024), (256, 512, 8192), (1000, 1032, 3072),
-                                     (2048, 5000, 520), (3000, 9000, 264), (40000, 256, 64)])
+                                     (2048, 5000, 520), (3000, 9000, 264), (40000, 256, 64), (300, 1002, 264)])
 @pytest.mark.parametrize("tile_n", [128, 256])
 def test_tcgen05_products_with_the_work_shared_out_evenly(ops, M, N, K, tile_n):
     # the stages of the last rounds' tiles cut into one range an SM: a tile shared by two blocks and by six, tiles that
