@@ -496,9 +496,12 @@ def tcgen05_share_pays(M: int, N: int, K: int, epi: int) -> bool:
     rounds' stages cut into one equal range an SM, partial sums added by the tile's owner).  It pays where whole tiles
     leave SMs idle: a last round that is less than half full (1.1 or 2.2 tiles of 128 x 256 an SM: q|k|v of 1,024 rows at
     the 8B sizes 52 against 66 us, o_proj of 1,024 rows at the 32B sizes 79 against 124), or fewer tiles than SMs with a
-    long K (q|k|v of 256 rows at the 32B sizes 55 against 75 us).  It does not pay with the SiLU epilogue (many tiles
-    anyway), nor where the blocks that share a tile of W, now at different places along K, push each other's part of it
-    out of L2 (down_proj of 1,024 rows at the 8B sizes: 124 against 90 us), hence the bound on the operands' bytes."""
+    long K and up to 512 rows (q|k|v of 256 rows at the 32B sizes 55 against 75 us, down_proj of 512 rows at the 8B sizes
+    74 against 90).  It does not pay with the SiLU epilogue (many tiles anyway), nor where the blocks that share a tile of
+    W, now at different places along K, push each other's part of it out of L2: down_proj of 1,024 rows at the 8B sizes
+    (eight tiles to a tile of W, 128 tiles for 148 SMs) took 124 against 90 us and read 670 MB from DRAM for operands of
+    126 MB; hence the bound on the rows there, and on the operands' bytes where there are more tiles than SMs (wins were
+    measured up to 117 MB: q|k|v of 512 and 1,024 rows at the 32B sizes 61 against 97 and 117 against 134 us)."""
     if epi:
         return False
     sms = sm_count()
@@ -506,8 +509,8 @@ def tcgen05_share_pays(M: int, N: int, K: int, epi: int) -> bool:
     if tiles >= sms:
         # (K: handing a tile's sums over costs 3 to 5 us, a tile of K = 1,024 takes 5: at the 0.6B sizes it never paid)
         rounds = -(-tiles // sms)
-        return K >= 4096 and tiles <= 0.75 * rounds * sms and (M + N) * K * 2 <= 96 << 20
-    return 5 * tiles >= sms and K >= 5120
+        return K >= 4096 and tiles <= 0.75 * rounds * sms and (M + N) * K * 2 <= 128 << 20
+    return 5 * tiles >= sms and K >= 5120 and M <= 512
 
 
 def tcgen05_one_round_width(M: int, N: int) -> int:

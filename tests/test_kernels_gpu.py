@@ -251,6 +251,8 @@ def test_which_tcgen05_products_share_their_work(ops):
     assert not ops.tcgen05_share_pays(8192, 6144, 4096, 0)                      # 1,536 tiles: the last round hardly matters
     assert not ops.tcgen05_share_pays(256, 4096, 1024, 0)                       # few tiles, short K: nothing to share
     assert not ops.tcgen05_share_pays(1280, 4096, 1024, 0)                      # a short K: handing sums over costs what a tile takes
+    assert not ops.tcgen05_share_pays(1024, 4096, 12288, 0)                     # eight tiles to a tile of W, at different places along K
+    assert ops.tcgen05_share_pays(512, 4096, 12288, 0) == (sms == 148)          # 64 tiles, a long K
 
 
 def test_which_tcgen05_products_get_a_block_an_sm_for_one_round(ops):
