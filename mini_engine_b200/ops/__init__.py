@@ -309,7 +309,7 @@ def linear_partials(x: torch.Tensor, weight: torch.Tensor, workspace, name: str,
         part = workspace(name, (splits, M, N), torch.float32)
         _call("me_gemm_skinny", x.data_ptr(), x.stride(0), weight.data_ptr(), 0, 0, 0, part.data_ptr(), M, N, K, 0, _stream())
         return part
-    if err is not None and use_tcgen05_gemm and M >= TCGEN05_MIN_ROWS and tcgen05_takes(x, weight) and weight.is_contiguous():
+    if err is not None and use_tcgen05_gemm and tcgen05_takes(x, weight) and weight.is_contiguous():
         bn, parts = tcgen05_split_plan(M, N, K)
         if parts >= 2:
             part = workspace(name, (parts, M, N), torch.float32)
@@ -447,7 +447,18 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
 
 
 TCGEN05_MIN_ROWS = 128    # rows from which bfloat16 products run csrc/gemm_tcgen05.cu (17..127: cuBLAS)
+# ... and from 48 rows on where the weight is small (up to 8 M elements: every product of a layer at the 0.6B sizes).  There a
+# decode step of 64 requests takes 2.39 ms against 2.44 with the library's products and a SiLU kernel, one of 96 requests 3.36
+# against 3.50 (32 requests: level); at the 8B and 32B sizes, where such a product streams 30 to 260 MB of weights over a
+# half-empty tile of rows, the library is 5 to 12% ahead and keeps them.
+TCGEN05_SMALL_MIN_ROWS = 48
+TCGEN05_SMALL_MAX_WEIGHT_ELEMENTS = 8 << 20
 use_tcgen05_gemm = True   # False: such products go to cuBLAS instead (a switch for comparisons)
+
+
+def tcgen05_min_rows(weight_elements: int) -> int:
+    """Rows from which a product with a weight of that many elements runs the tcgen05 kernels."""
+    return min(TCGEN05_MIN_ROWS, TCGEN05_SMALL_MIN_ROWS) if weight_elements <= TCGEN05_SMALL_MAX_WEIGHT_ELEMENTS else TCGEN05_MIN_ROWS
 
 
 def matrix_tensor_map(t: torch.Tensor, box_rows: int) -> "TensorMap":
@@ -469,7 +480,7 @@ def matrix_tensor_map(t: torch.Tensor, box_rows: int) -> "TensorMap":
 
 def tcgen05_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
     M, K = x.shape
-    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M >= TCGEN05_MIN_ROWS
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M >= tcgen05_min_rows(weight.numel())
             and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
@@ -563,7 +574,7 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epi
             need = 200 if K < 4096 else 64
             tile_n = next((bn for bn in (256, 128) if m_tiles * ((N + bn - 1) // bn) >= need), 64)
     bn = tile_n
-    _need(tcgen05_takes(x, weight) or M < TCGEN05_MIN_ROWS, "linear_tcgen05: operands not taken")
+    _need(tcgen05_takes(x, weight) or M < tcgen05_min_rows(weight.numel()), "linear_tcgen05: operands not taken")
     box_w = bn // 2 if epi else bn
     if splits > 1:
         _need(out.dim() == 3 and out.shape[0] == tcgen05_splits(K, splits) and out.dtype == torch.float32 and out.is_contiguous(),
@@ -597,7 +608,7 @@ def tcgen05_split_plan(M: int, N: int, K: int) -> tuple[int, int]:
     A product of a few hundred rows by a thousand columns has a handful of tiles for 148 SMs; shared out along K
     four ways it ran 25 to 40% faster (o_proj and down_proj of the 0.6B shape at 512 and 1,024 rows), at 2,048 rows
     no faster once the partial results are added."""
-    if not (TCGEN05_MIN_ROWS <= M <= TCGEN05_SPLIT_MAX_ROWS):
+    if not (tcgen05_min_rows(N * K) <= M <= TCGEN05_SPLIT_MAX_ROWS):
         return 0, 1
     m_tiles = (M + 127) // 128
     bn = 64 if m_tiles * ((N + 127) // 128) * 4 < 128 else 128
