@@ -446,7 +446,7 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
           _ptr(fetch_ahead), fetch_ahead.numel() * fetch_ahead.element_size() if fetch_ahead is not None else 0, _stream())
 
 
-TCGEN05_MIN_ROWS = 128    # rows from which bfloat16 products run csrc/gemm_tcgen05.cu (17..127: cuBLAS)
+TCGEN05_MIN_ROWS = 128    # rows from which bfloat16 products run csrc/gemm_tcgen05.cu whatever the weight (fewer: cuBLAS) ...
 # ... and from 48 rows on where the weight is small (up to 8 M elements: every product of a layer at the 0.6B sizes).  There a
 # decode step of 64 requests takes 2.39 ms against 2.44 with the library's products and a SiLU kernel, one of 96 requests 3.36
 # against 3.50 (32 requests: level); at the 8B and 32B sizes, where such a product streams 30 to 260 MB of weights over a
@@ -626,8 +626,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: s
     float32 operands (and any mix of dtypes) run the CUDA-core kernel of csrc/gemm_simt.cu: plain
     FMA, no reduced-precision matrix mode.  bfloat16 x bfloat16 products of up to 16 rows run csrc/gemm_stream.cu
     where the weight has 32 MB and more (the vocabulary product of a decode step) and csrc/gemm_skinny.cu else
-    (the layers' own products in decode do not come here: ``decode_linear``); 128 rows and more run the tcgen05 kernels
-    of csrc/gemm_tcgen05.cu; 17 to 127 rows, and shapes those refuse (K no multiple of 8), go to cuBLAS, as all the
+    (the layers' own products in decode do not come here: ``decode_linear``); 128 rows and more, and 48 rows and more
+    where the weight is small (``tcgen05_min_rows``), run the tcgen05 kernels of csrc/gemm_tcgen05.cu; the rows between,
+    and shapes those refuse (K no multiple of 8), go to cuBLAS, as all the
     reference's products do through ``F.linear`` (layers/linear.py:26,45), with SiLU-and-multiply as a kernel of ours
     behind it.
 
