@@ -26,33 +26,16 @@ constexpr int TG_A_BYTES = TG_BM * TG_BK * 2;
 // is the bytes a block has on their way from L2.
 template <int BN> constexpr int tg_stages(bool deep) { return (BN <= 64 ? 4 : (BN <= 128 ? 3 : 2)) * (deep ? 2 : 1); }
 
-// 32 consecutive results of one row: 16-byte stores where the row's place allows, else one by one.
-__device__ __forceinline__ void store_row32(bf16* dst, const float (&v)[32], int n_left, bool vec) {
-  if (vec && n_left >= 32) {
+// 32 consecutive results of one row, one by one (rows of C that are not 16-byte aligned).
+__device__ __forceinline__ void store_row32(bf16* dst, const float (&v)[32], int n_left) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint4 pk;
-      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
-      *reinterpret_cast<uint4*>(dst + q * 8) = pk;
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < n_left) dst[j] = __float2bfloat16_rn(v[j]);
-  }
+  for (int j = 0; j < 32; ++j)
+    if (j < n_left) dst[j] = __float2bfloat16_rn(v[j]);
 }
-__device__ __forceinline__ void store_row32(float* dst, const float (&v)[32], int n_left, bool vec) {
-  if (vec && n_left >= 32) {
+__device__ __forceinline__ void store_row32(float* dst, const float (&v)[32], int n_left) {
 #pragma unroll
-    for (int q = 0; q < 8; ++q)
-      *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < n_left) dst[j] = v[j];
-  }
+  for (int j = 0; j < 32; ++j)
+    if (j < n_left) dst[j] = v[j];
 }
 
 // The epilogue of one warp: its 32 rows of a tile (a lane a row) go out OUT_COLS columns wide.  ``load(col, v)`` asks for 32
@@ -90,7 +73,7 @@ __device__ __forceinline__ void write_rows(Load&& load, Fix&& fix, unsigned char
     for (int c = 0; c < OUT_COLS; c += 32) {
       float g[32];
       results(c, g);
-      if (m < M && n0 + c < N) store_row32(C + (int64_t)m * ldc + n0 + c, g, N - n0 - c, false);
+      if (m < M && n0 + c < N) store_row32(C + (int64_t)m * ldc + n0 + c, g, N - n0 - c);
     }
     return;
   }
