@@ -6,10 +6,15 @@
 // One block computes a 128 x BN tile.  Warp 0: one thread streams A and W tiles of 64 K-elements
 // through a ring of shared-memory stages by TMA (128-byte swizzle, zero fill at the edges).
 // Warp 1: allocates BN columns of tensor memory; all its lanes run the loop and an elected lane issues
-// tcgen05.mma (M 128, N BN, K 16, four per stage) and hands stages back through tcgen05.commit.  Warps 2..5: when the accumulator is
-// complete, each thread reads its row from tensor memory (tcgen05.ld), applies the epilogue and writes
-// it.  Every wait is bounded; a wait that gives up sets flag 1 of ``err`` and the block still frees its
-// tensor memory and exits.
+// tcgen05.mma (M 128, N BN, K 16, four per stage) and hands stages back through tcgen05.commit.
+// Warps 2..5: when the accumulator is complete, each thread reads its row from tensor memory
+// (tcgen05.ld) and applies the epilogue; the rows leave through shared memory in whole lines
+// (write_rows).  Every wait is bounded; a wait that gives up sets flag 1 of ``err`` and the block still
+// frees its tensor memory and exits.
+//
+// Three forms: a tile a block (gemm_tcgen05_kernel, with K shared out over gridDim.z blocks where the
+// caller adds float32 partial results), blocks that walk whole tiles (gemm_tcgen05_persistent_kernel), and
+// blocks that share the last rounds' stages out evenly (gemm_tcgen05_shared_kernel).
 //
 // EPI 1: W has rows gate | up; a stage's W tile holds BN/2 gate rows and the matching BN/2 up rows, so
 // the accumulator's first half is gate and its second half up, and the block writes BN/2 columns of
